@@ -1,0 +1,291 @@
+"""Python face of the CUDA kernels: one function per kernel entry point.
+
+Every function checks shapes, types and contiguity, passes raw device pointers and
+the current CUDA stream to the C entry point, and raises `KernelError` on a
+non-zero status.  Nothing here falls back to a library or to the CPU: without a
+CUDA device or without the compiled kernels these functions fail.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+GEMM_WORKSPACE_BYTES = 64 << 20
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"storage type {dtype} is not supported (float32 and bfloat16 only)") from None
+
+
+def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        detail = {-2: "invalid argument", -3: "shared memory need exceeds the device limit"}.get(status, "")
+        raise KernelError(f"{what} failed with status {status} {detail}".rstrip())
+
+
+def _need(t: torch.Tensor, dtype, name: str, dims: Optional[int] = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on the CUDA device")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dimensions, got shape {tuple(t.shape)}")
+
+
+# ------------------------------------------------------------------ elementwise library
+def _elementwise():
+    lib = load_library("elementwise.cu")
+    if not getattr(lib, "_typed", False):
+        lib.cisr_embedding.restype = ctypes.c_int
+        lib.cisr_add_rmsnorm.restype = ctypes.c_int
+        lib.cisr_swiglu.restype = ctypes.c_int
+        lib.cisr_rotary_tables.restype = ctypes.c_int
+        lib.cisr_rope_store.restype = ctypes.c_int
+        lib.cisr_page_copy.restype = ctypes.c_int
+        lib.cisr_table_update.restype = ctypes.c_int
+        lib._typed = True
+    return lib
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, :] = table[ids[t], :] widened to float."""
+    _need(table, None, "table", 2); _need(ids, torch.int32, "ids", 1); _need(out, torch.float32, "out", 2)
+    tokens, hidden = out.shape
+    if ids.numel() != tokens or table.shape[1] != hidden:
+        raise KernelError("embedding: shapes of ids, table and out disagree")
+    _check(_elementwise().cisr_embedding(_p(table), dtype_code(table.dtype), _p(ids), _p(out), tokens, hidden,
+                                         table.shape[0], _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None, write_back: bool = True) -> torch.Tensor:
+    """x += delta (when given), out = rmsnorm(x) * weight; `rows` selects which rows of x become rows of out."""
+    _need(x, torch.float32, "x", 2); _need(weight, None, "weight", 1); _need(out, None, "out", 2)
+    hidden = x.shape[1]
+    if delta is not None:
+        _need(delta, torch.float32, "delta", 2)
+        if delta.shape != x.shape:
+            raise KernelError("add_rmsnorm: delta and x differ in shape")
+    n_rows = out.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows", 1)
+        if rows.numel() != n_rows:
+            raise KernelError("add_rmsnorm: one row index per output row is needed")
+    elif n_rows != x.shape[0]:
+        raise KernelError("add_rmsnorm: out and x differ in rows")
+    if weight.numel() != hidden or out.shape[1] != hidden:
+        raise KernelError("add_rmsnorm: width mismatch")
+    _check(_elementwise().cisr_add_rmsnorm(_p(x), _p(delta), _p(weight), dtype_code(weight.dtype), _p(out),
+                                           dtype_code(out.dtype), _p(rows), n_rows, hidden, ctypes.c_float(eps),
+                                           int(write_back), _stream()), "add_rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _need(gate_up, torch.float32, "gate_up", 2); _need(out, None, "out", 2)
+    tokens, inter = out.shape
+    if gate_up.shape != (tokens, 2 * inter):
+        raise KernelError("swiglu: gate_up must be [tokens, 2 * intermediate]")
+    _check(_elementwise().cisr_swiglu(_p(gate_up), _p(out), dtype_code(out.dtype), tokens, inter, _stream()), "swiglu")
+    return out
+
+
+def rotary_tables(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+    _need(positions, torch.int32, "positions", 1); _need(inv_freq, torch.float64, "inv_freq", 1)
+    _need(cos, torch.float32, "cos", 2); _need(sin, torch.float32, "sin", 2)
+    tokens, half = cos.shape
+    if positions.numel() != tokens or inv_freq.numel() != half or sin.shape != cos.shape:
+        raise KernelError("rotary_tables: shapes disagree")
+    _check(_elementwise().cisr_rotary_tables(_p(positions), _p(inv_freq), _p(cos), _p(sin), tokens, half, _stream()),
+           "rotary_tables")
+
+
+def rope_store(proj: torch.Tensor, k_col: int, v_col: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+               rot_half: int, interleaved: bool, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+               v_cache: Optional[torch.Tensor], token_req: torch.Tensor, positions: torch.Tensor,
+               req_slot: torch.Tensor, block_table: torch.Tensor, page_size: int, hq: int, hkv: int, dim: int) -> None:
+    """Rotate q (and k), write q to q_out and k, v into their cache pages (k_col < 0: queries only)."""
+    _need(proj, torch.float32, "proj", 2); _need(q_out, None, "q_out")
+    tokens = proj.shape[0]
+    if rot_half:
+        _need(cos, torch.float32, "cos", 2); _need(sin, torch.float32, "sin", 2)
+        if cos.shape != (tokens, rot_half) or sin.shape != cos.shape:
+            raise KernelError("rope_store: rotary tables must be [tokens, rot_half]")
+    if q_out.numel() != tokens * hq * dim:
+        raise KernelError("rope_store: q_out must hold [tokens, heads, head_dim]")
+    cache_code = F32
+    if k_col >= 0:
+        _need(k_cache, None, "k_cache", 4); _need(v_cache, k_cache.dtype, "v_cache", 4)
+        if tuple(k_cache.shape[1:]) != (hkv, page_size, dim) or v_cache.shape != k_cache.shape:
+            raise KernelError("rope_store: cache must be [pages, kv_heads, page_size, head_dim]")
+        if proj.shape[1] < v_col + hkv * dim or proj.shape[1] < k_col + hkv * dim:
+            raise KernelError("rope_store: projection row is too short for its key and value columns")
+        cache_code = dtype_code(k_cache.dtype)
+    _need(token_req, torch.int32, "token_req", 1); _need(positions, torch.int32, "positions", 1)
+    _need(block_table, torch.int32, "block_table", 2); _need(req_slot, torch.int32, "req_slot", 1)
+    _check(_elementwise().cisr_rope_store(
+        _p(proj), proj.shape[1], k_col, v_col, _p(cos if rot_half else None), _p(sin if rot_half else None), rot_half,
+        int(interleaved), _p(q_out), dtype_code(q_out.dtype), _p(k_cache), _p(v_cache), cache_code, _p(token_req),
+        _p(positions), _p(req_slot), _p(block_table), block_table.shape[1], page_size, hq, hkv, dim, tokens, _stream()),
+        "rope_store")
+
+
+def page_copy(pool: torch.Tensor, pairs: torch.Tensor, n_planes: int, plane_bytes: int, page_bytes: int) -> None:
+    """Copy pages (src, dst) in every plane of a pool laid out [planes, pages, page bytes]."""
+    _need(pairs, torch.int32, "pairs", 2)
+    _check(_elementwise().cisr_page_copy(_p(pool), _p(pairs), pairs.shape[0], n_planes, ctypes.c_longlong(plane_bytes),
+                                         ctypes.c_longlong(page_bytes), _stream()), "page_copy")
+
+
+def table_update(table: torch.Tensor, idx: torch.Tensor, val: torch.Tensor) -> None:
+    """table.view(-1)[idx[i]] = val[i] for every i with idx[i] >= 0."""
+    _need(table, torch.int32, "table"); _need(idx, torch.int32, "idx", 1); _need(val, torch.int32, "val", 1)
+    _check(_elementwise().cisr_table_update(_p(table), _p(idx), _p(val), idx.numel(), _stream()), "table_update")
+
+
+# ------------------------------------------------------------------ attention (one library per head size and storage)
+_attention_libs = {}
+
+
+def attention_library(head_dim: int, dtype: torch.dtype):
+    if head_dim % 16 or not 16 <= head_dim <= 256:
+        raise KernelError(f"attention kernels take head sizes that are multiples of 16 from 16 to 256, not {head_dim}")
+    key = (head_dim, dtype)
+    lib = _attention_libs.get(key)
+    if lib is None:
+        lib = load_library("attention.cu", {"HEAD_DIM": head_dim, "STORAGE_BF16": dtype_code(dtype)})
+        for name in ("cisr_attn_prefill", "cisr_attn_decode", "cisr_attn_head_dim", "cisr_attn_prefill_tile"):
+            getattr(lib, name).restype = ctypes.c_int
+        assert lib.cisr_attn_head_dim() == head_dim
+        _attention_libs[key] = lib
+    return lib
+
+
+def attention_jobs(head_dim: int, dtype: torch.dtype):
+    """The build job of the attention library for this head size and storage type."""
+    return ("attention.cu", {"HEAD_DIM": head_dim, "STORAGE_BF16": dtype_code(dtype)}, ())
+
+
+PREFILL_TILE = 64
+
+
+def attn_prefill(q, out, k_cache, v_cache, req_slot, block_table, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv,
+                 page_size, scale, window) -> None:
+    """Attention of portions: q, out [tokens, hq, D]; tiles list (request, first query of the tile)."""
+    dim = k_cache.shape[-1]
+    _need(q, k_cache.dtype, "q"); _need(out, k_cache.dtype, "out"); _need(k_cache, None, "k_cache", 4)
+    _need(v_cache, k_cache.dtype, "v_cache", 4)
+    for name, t in (("req_slot", req_slot), ("block_table", block_table), ("tile_req", tile_req), ("tile_q0", tile_q0), ("q_start", q_start),
+                    ("q_len", q_len), ("ctx_len", ctx_len)):
+        _need(t, torch.int32, name)
+    lib = attention_library(dim, k_cache.dtype)
+    _check(lib.cisr_attn_prefill(_p(q), _p(out), _p(k_cache), _p(v_cache), _p(req_slot), _p(block_table), block_table.shape[1],
+                                 _p(tile_req), _p(tile_q0), tile_req.numel(), _p(q_start), _p(q_len), _p(ctx_len),
+                                 hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), _stream()), "attn_prefill")
+
+
+def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, q_start, ctx_len, partial, stats, hq, hkv,
+                page_size, scale, window, split_size, n_splits) -> None:
+    """Attention of single new tokens, split over key ranges of `split_size`, merged into out."""
+    dim = k_cache.shape[-1]
+    _need(q, k_cache.dtype, "q"); _need(out, k_cache.dtype, "out"); _need(k_cache, None, "k_cache", 4)
+    _need(v_cache, k_cache.dtype, "v_cache", 4); _need(partial, torch.float32, "partial"); _need(stats, torch.float32, "stats")
+    for name, t in (("req_slot", req_slot), ("block_table", block_table), ("dec_req", dec_req), ("q_start", q_start), ("ctx_len", ctx_len)):
+        _need(t, torch.int32, name)
+    if partial.numel() < n_dec * hq * n_splits * dim or stats.numel() < n_dec * hq * n_splits * 2:
+        raise KernelError("attn_decode: scratch for partial sums is too small")
+    lib = attention_library(dim, k_cache.dtype)
+    _check(lib.cisr_attn_decode(_p(q), _p(out), _p(k_cache), _p(v_cache), _p(req_slot), _p(block_table), block_table.shape[1],
+                                _p(dec_req), n_dec, _p(q_start), _p(ctx_len), _p(partial), _p(stats), hq, hkv, page_size,
+                                ctypes.c_float(scale), int(window or 0), split_size, n_splits, _stream()), "attn_decode")
+
+
+# ------------------------------------------------------------------ sampling
+def _sampling():
+    lib = load_library("sampling.cu")
+    if not getattr(lib, "_typed", False):
+        lib.cisr_sample.restype = ctypes.c_int
+        lib.cisr_uniform_host.restype = ctypes.c_float
+        lib.cisr_uniform_host.argtypes = [ctypes.c_longlong, ctypes.c_longlong]
+        lib._typed = True
+    return lib
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Optional[torch.Tensor],
+           counter: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    """Token per row: argmax where temperature <= 0 (or None), else inverse-CDF sampling."""
+    _need(logits, torch.float32, "logits", 2); _need(out, torch.int32, "out", 1)
+    rows, vocab = logits.shape
+    if temperature is not None:
+        _need(temperature, torch.float32, "temperature", 1); _need(seed, torch.int64, "seed", 1)
+        _need(counter, torch.int32, "counter", 1)
+    _check(_sampling().cisr_sample(_p(logits), rows, vocab, _p(temperature), _p(seed), _p(counter), _p(out), _stream()),
+           "sample")
+    return out
+
+
+def uniform_host(seed: int, counter: int) -> float:
+    """The uniform the device sampler draws for (seed, counter), computed on the host by the same code."""
+    return float(_sampling().cisr_uniform_host(seed, counter))
+
+
+# ------------------------------------------------------------------ library matrix product
+_gemm_state = {}
+
+
+def _gemm_library():
+    lib = _gemm_state.get("lib")
+    if lib is None:
+        lib = load_library("gemm_library.cu", extra=("-lcublas",))
+        lib.cisr_gemm_library_init.restype = ctypes.c_int
+        lib.cisr_gemm_library.restype = ctypes.c_int
+        workspace = torch.empty(GEMM_WORKSPACE_BYTES, dtype=torch.uint8, device="cuda")
+        _check(lib.cisr_gemm_library_init(_p(workspace), ctypes.c_longlong(GEMM_WORKSPACE_BYTES)), "gemm library init")
+        _gemm_state["lib"], _gemm_state["workspace"] = lib, workspace
+    return lib
+
+
+def gemm_library(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] (float) = a[M, K] @ w[N, K]^T by the vendor library, float accumulation."""
+    _need(a, None, "a", 2); _need(w, a.dtype, "w", 2); _need(out, torch.float32, "out", 2)
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n):
+        raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
+    _check(_gemm_library().cisr_gemm_library(_p(a), _p(w), dtype_code(a.dtype), _p(out), m, n, k, _stream()), "gemm")
+    return out
+
+
+def gemm_jobs(dtype: torch.dtype):
+    """Build jobs of the libraries `gemm` may launch for operands of this dtype."""
+    return [("gemm_library.cu", {}, ("-lcublas",))]
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] (float) = a[M, K] @ w[N, K]^T; picks the kernel for the shape and dtype."""
+    return gemm_library(a, w, out)

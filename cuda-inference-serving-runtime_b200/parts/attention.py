@@ -1,0 +1,84 @@
+"""Grouped-query attention over the paged cache.
+
+Parity: runtime/model.py:110-115 (q, k, v projections without bias, rotation of q
+and k, keys cached rotated, attention, output projection), runtime/reference.py:18-27
+(consecutive query heads share a key/value head; scores scaled by 1/sqrt(D); causal
+by construction).  q_proj, k_proj and v_proj are stacked into one matrix at load.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..config.spec import CacheUse
+from ..ops import kernels
+from .base import MIXERS, POSITIONS, Mixer, TensorNeed, build_part, register
+from .linear import linear
+
+
+@register(MIXERS, "gqa_attention")
+class GQAAttention(Mixer):
+    """params: hidden_size, num_heads, num_kv_heads, head_dim, position (PartSpec), window (None or int), scale."""
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        self.hidden = int(spec["hidden_size"])
+        self.hq = int(spec["num_heads"])
+        self.hkv = int(spec["num_kv_heads"])
+        self.dim = int(spec["head_dim"])
+        self.window = spec.get("window")
+        self.scale = float(spec.get("scale", self.dim ** -0.5))
+        if self.hq % self.hkv:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if self.dim % 16 or not 16 <= self.dim <= 256:
+            raise ValueError(f"head_dim {self.dim} is not supported: the attention kernels take multiples of 16 "
+                             "from 16 to 256")
+        self.position = build_part(POSITIONS, spec["position"], dtype, "position encoding")
+        self.qkv = None
+        self.o = None
+
+    def tensor_needs(self) -> Dict[str, TensorNeed]:
+        return {"q_proj.weight": TensorNeed((self.hq * self.dim, self.hidden)),
+                "k_proj.weight": TensorNeed((self.hkv * self.dim, self.hidden)),
+                "v_proj.weight": TensorNeed((self.hkv * self.dim, self.hidden)),
+                "o_proj.weight": TensorNeed((self.hidden, self.hq * self.dim))}
+
+    def load(self, tensors):
+        self.qkv = torch.cat((tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]), dim=0).contiguous()
+        self.o = tensors["o_proj.weight"].contiguous()
+
+    def kernel_jobs(self):
+        return ([("elementwise.cu", {}, ()), kernels.attention_jobs(self.dim, self.dtype)]
+                + kernels.gemm_jobs(self.dtype) + self.position.kernel_jobs())
+
+    def cache_use(self) -> CacheUse:
+        return CacheUse("pages", kv_heads=self.hkv, head_dim=self.dim, window=self.window)
+
+    def forward(self, h, ctx, cache):
+        tokens = h.shape[0]
+        hq, hkv, dim = self.hq, self.hkv, self.dim
+        if cache.write:
+            proj = linear(h, self.qkv)
+            k_col, v_col = hq * dim, (hq + hkv) * dim
+        else:  # this run entry reads another entry's keys and values: queries only
+            proj = linear(h, self.qkv[: hq * dim])
+            k_col = v_col = -1
+        rot = self.position.rotation(ctx)
+        q = torch.empty((tokens, hq, dim), dtype=self.dtype, device=h.device)
+        kernels.rope_store(proj, k_col, v_col, rot.cos if rot else None, rot.sin if rot else None,
+                           rot.rot_half if rot else 0, rot.interleaved if rot else False, q,
+                           cache.k if cache.write else None, cache.v if cache.write else None,
+                           ctx.token_req, ctx.positions, ctx.req_slot, cache.block_table, cache.page_size, hq, hkv, dim)
+        out = torch.empty((tokens, hq, dim), dtype=self.dtype, device=h.device)
+        if ctx.n_tiles:
+            kernels.attn_prefill(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, ctx.tile_req, ctx.tile_q0, ctx.q_start,
+                                 ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, self.scale, self.window)
+        if ctx.n_decode:
+            split_size, n_splits = ctx.decode_splits(hkv)
+            partial = torch.empty((ctx.n_decode, hq, n_splits, dim), dtype=torch.float32, device=h.device)
+            stats = torch.empty((ctx.n_decode, hq, n_splits, 2), dtype=torch.float32, device=h.device)
+            kernels.attn_decode(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, ctx.dec_req, ctx.n_decode, ctx.q_start,
+                                ctx.ctx_len, partial, stats, hq, hkv, cache.page_size, self.scale, self.window,
+                                split_size, n_splits)
+        return linear(out.view(tokens, hq * dim), self.o)

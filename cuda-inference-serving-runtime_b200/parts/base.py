@@ -1,0 +1,120 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+A part is built from a `PartSpec` (its registered kind plus sizes and constants)
+and the compute dtype.  It says which tensors it needs under local names
+(`tensor_needs`), receives them (`load`), and runs on the device (`forward`).
+No part knows which model or which layer it is in: checkpoint names are made by
+the model from the layer's prefix and the local name.
+
+Registries: NORMS, POSITIONS, MIXERS, FEED_FORWARDS, ARRANGEMENTS, EMBEDDINGS, HEADS.
+`register(registry, kind)` is a class decorator; registering a kind twice is an error.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+from ..config.spec import CacheUse, PartSpec
+
+
+@dataclass(frozen=True)
+class TensorNeed:
+    """A tensor a part loads: shape, and how it is kept.
+
+    role "matrix": a GEMM operand, kept in the compute dtype.
+    role "vector": a small per-channel tensor, kept as stored when stored in 32-bit, else in the compute dtype.
+    role "table": an integer table, kept as int32.
+    `alias` names a tensor (by full checkpoint name) to use when this one is absent (a tied head).
+    """
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+    alias: Optional[str] = None
+
+
+class Part:
+    def __init__(self, spec: PartSpec, dtype: torch.dtype):
+        self.spec = spec
+        self.dtype = dtype
+
+    def tensor_needs(self) -> Dict[str, TensorNeed]:
+        return {}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
+
+    def kernel_jobs(self) -> List[tuple]:
+        """Build jobs (source, defines, extra flags) of the kernel libraries this part launches."""
+        return []
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
+                rows: Optional[torch.Tensor] = None, write_back: bool = True) -> torch.Tensor:
+        """x += delta in place (if given), then return norm(x) in `out_dtype`; `rows` picks rows of x."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotation(self, ctx) -> Optional["Rotation"]:
+        """Per-token rotation tables for this step, or None when the encoding does not rotate."""
+        raise NotImplementedError
+
+
+@dataclass
+class Rotation:
+    cos: torch.Tensor      # [tokens, rot_half] float
+    sin: torch.Tensor
+    rot_half: int          # 2 * rot_half leading coordinates of each head are rotated
+    interleaved: bool      # pairs (2i, 2i+1) instead of (i, i + rot_half)
+
+
+class Mixer(Part):
+    def cache_use(self) -> CacheUse:
+        return CacheUse("none")
+
+    def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
+        """h [tokens, hidden] in the compute dtype -> float [tokens, hidden] to add to the residual stream."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """int32 [tokens] -> float residual stream [tokens, hidden]."""
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        """[rows, hidden] in the compute dtype -> float logits [rows, vocab]."""
+        raise NotImplementedError
+
+
+NORMS: Dict[str, type] = {}
+POSITIONS: Dict[str, type] = {}
+MIXERS: Dict[str, type] = {}
+FEED_FORWARDS: Dict[str, type] = {}
+ARRANGEMENTS: Dict[str, type] = {}
+EMBEDDINGS: Dict[str, type] = {}
+HEADS: Dict[str, type] = {}
+
+
+def register(registry: Dict[str, type], kind: str):
+    def wrap(cls):
+        if kind in registry:
+            raise ValueError(f"part kind {kind!r} is already registered")
+        registry[kind] = cls
+        return cls
+    return wrap
+
+
+def build_part(registry: Dict[str, type], spec: PartSpec, dtype: torch.dtype, what: str) -> Any:
+    if spec.kind not in registry:
+        raise KeyError(f"no {what} registered as {spec.kind!r}; known: {', '.join(sorted(registry)) or 'none'}")
+    return registry[spec.kind](spec, dtype)
