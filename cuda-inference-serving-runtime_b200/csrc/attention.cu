@@ -369,7 +369,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ partial, const float
                 den = fmaf(w, l, den);
             }
         }
-        out[((size_t)tok * hq + head) * D + d] = from_float<st_t>(num / den);
+        out[((size_t)tok * hq + head) * D + d] = from_float<st_t>(den > 0.f ? num / den : 0.f);  // no keys at all: a padding row
     }
 }
 }  // namespace

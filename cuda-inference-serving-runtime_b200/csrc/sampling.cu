@@ -87,6 +87,27 @@ CISR_EXPORT int cisr_sample(const float* logits, int rows, int vocab, const floa
     return launch_status();
 }
 
+// After a decode step whose tokens were chosen on the device: feed each live row's token back as its next
+// input and move its position, context length and sample counter on by one, so the next step can run without
+// the host.  Rows with live == 0 (padding) stay as they are.
+__global__ void decode_advance_kernel(int* token_ids, int* positions, int* ctx_len, int* counter,
+                                      const int* __restrict__ sampled, const int* __restrict__ live, int rows) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows || !live[i]) return;
+    token_ids[i] = sampled[i];
+    positions[i] += 1;
+    ctx_len[i] += 1;
+    counter[i] += 1;
+}
+
+CISR_EXPORT int cisr_decode_advance(int* token_ids, int* positions, int* ctx_len, int* counter, const int* sampled,
+                                    const int* live, int rows, void* stream) {
+    if (rows <= 0) return 0;
+    decode_advance_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>(token_ids, positions, ctx_len, counter,
+                                                                                 sampled, live, rows);
+    return launch_status();
+}
+
 CISR_EXPORT float cisr_uniform_host(long long seed, long long counter) {
     return cisr_uniform((unsigned long long)seed, (unsigned long long)counter);
 }

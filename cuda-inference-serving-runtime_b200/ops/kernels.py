@@ -230,6 +230,7 @@ def _sampling():
     lib = load_library("sampling.cu")
     if not getattr(lib, "_typed", False):
         lib.cisr_sample.restype = ctypes.c_int
+        lib.cisr_decode_advance.restype = ctypes.c_int
         lib.cisr_uniform_host.restype = ctypes.c_float
         lib.cisr_uniform_host.argtypes = [ctypes.c_longlong, ctypes.c_longlong]
         lib._typed = True
@@ -247,6 +248,15 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Opti
     _check(_sampling().cisr_sample(_p(logits), rows, vocab, _p(temperature), _p(seed), _p(counter), _p(out), _stream()),
            "sample")
     return out
+
+
+def decode_advance(token_ids, positions, ctx_len, counter, sampled, live) -> None:
+    """Feed sampled tokens back as the next inputs of live rows and advance their positions, lengths and counters."""
+    for name, t in (("token_ids", token_ids), ("positions", positions), ("ctx_len", ctx_len), ("counter", counter),
+                    ("sampled", sampled), ("live", live)):
+        _need(t, torch.int32, name, 1)
+    _check(_sampling().cisr_decode_advance(_p(token_ids), _p(positions), _p(ctx_len), _p(counter), _p(sampled), _p(live),
+                                           token_ids.numel(), _stream()), "decode_advance")
 
 
 def uniform_host(seed: int, counter: int) -> float:

@@ -1,0 +1,64 @@
+"""The plain implementation against the reference's own CPU model (tests/golden/) and against simple facts."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+import tiny_models as tm
+
+GOLDEN = Path(__file__).resolve().parent / "golden" / "reference_logits.npz"
+
+
+@pytest.mark.parametrize("case,cfg,seed", [("tiny_a", tm.TINY_A, 11), ("tiny_b", tm.TINY_B, 12), ("tiny_c", tm.TINY_C, 13)])
+def test_plain_matches_reference_model(case, cfg, seed):
+    golden = np.load(GOLDEN)
+    tokens = golden[case + "_tokens"].tolist()
+    assert tokens == tm.random_tokens(cfg, len(tokens), {"tiny_a": 101, "tiny_b": 102, "tiny_c": 103}[case])
+    weights = tm.torch_weights(tm.make_weights(cfg, seed))
+    ours = pl.forward(cfg, weights, tokens, torch.float64).numpy()
+    ref = golden[case + "_logits"].astype(np.float64)
+    # the reference's own bound between its paged and dense paths (tests/test_model.py:26)
+    np.testing.assert_allclose(ours, ref, atol=4e-6, rtol=3e-5)
+
+
+def test_softmax_is_finite_for_large_scores_and_uniform_for_equal_ones():
+    q = torch.full((3, 2, 4), 1e3, dtype=torch.float64)
+    k = torch.full((3, 1, 4), 1e3, dtype=torch.float64)
+    v = torch.arange(12, dtype=torch.float64).reshape(3, 1, 4)
+    out = pl.causal_attention(q, k, v)
+    assert torch.isfinite(out).all()
+    torch.testing.assert_close(out[2, 0], v[:, 0].mean(dim=0))   # equal scores: the mean of the values
+    torch.testing.assert_close(out[0, 1], v[0, 0])               # the first token sees only itself
+
+
+def test_rotary_preserves_norm_and_is_identity_at_position_zero():
+    x = torch.randn(5, 3, 8, dtype=torch.float64)
+    y = pl.rotary(x, torch.arange(5), 10000.0)
+    torch.testing.assert_close(y.norm(dim=-1), x.norm(dim=-1))
+    torch.testing.assert_close(y[0], x[0])
+
+
+def test_rms_norm_of_zeros_is_zero_and_scales():
+    w = torch.ones(6, dtype=torch.float64)
+    assert torch.equal(pl.rms_norm(torch.zeros(2, 6, dtype=torch.float64), w, 1e-5), torch.zeros(2, 6, dtype=torch.float64))
+    x = torch.randn(2, 6, dtype=torch.float64)
+    torch.testing.assert_close(pl.rms_norm(3 * x, w, 0.0), pl.rms_norm(x, w, 0.0))
+
+
+def test_window_limits_what_a_token_sees():
+    t, d = 6, 4
+    q = torch.randn(t, 1, d, dtype=torch.float64)
+    k = torch.randn(t, 1, d, dtype=torch.float64)
+    v = torch.randn(t, 1, d, dtype=torch.float64)
+    full = pl.causal_attention(q, k, v)
+    win = pl.causal_attention(q, k, v, window=2)
+    torch.testing.assert_close(win[:2], full[:2])                 # the first two tokens see everything anyway
+    torch.testing.assert_close(win[5], pl.causal_attention(q[4:6], k[4:6], v[4:6])[1])
+
+
+def test_greedy_takes_the_lowest_index_on_ties_and_inverse_cdf_walks_the_distribution():
+    assert pl.greedy(torch.tensor([1.0, 3.0, 3.0, 2.0])) == 1
+    logits = torch.log(torch.tensor([0.1, 0.2, 0.3, 0.4]))
+    assert [pl.sample_inverse_cdf(logits, 1.0, u) for u in (0.0, 0.09, 0.11, 0.59, 0.61, 0.999)] == [0, 0, 1, 2, 3, 3]
