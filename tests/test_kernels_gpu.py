@@ -1,0 +1,348 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the engine's."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+
+
+def dev():
+    return torch.device("cuda")
+
+
+def kernels():
+    from cisr_b200.ops import kernels as k
+    return k
+
+
+def close(a, b, atol, rtol, what=""):
+    torch.testing.assert_close(a.double().cpu(), b.double().cpu(), atol=atol, rtol=rtol, msg=lambda m: f"{what}: {m}")
+
+
+@pytest.mark.parametrize("hidden", [10, 64, 130, 576, 5000])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(hidden, dtype):
+    k = kernels()
+    g = torch.Generator().manual_seed(hidden)
+    x = torch.randn(7, hidden, generator=g) * 3
+    delta = torch.randn(7, hidden, generator=g)
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dtype)
+    eps = 3e-6
+    xd, dd = x.to(dev()), delta.to(dev())
+    out = torch.empty(7, hidden, dtype=dtype, device=dev())
+    k.add_rmsnorm(xd, dd, w.to(dev()), eps, out)
+    ref_x = x.double() + delta.double()
+    ref = pl.rms_norm(ref_x, w.double(), eps)
+    close(xd, ref_x, 1e-6, 1e-6, "residual sum")
+    if dtype == torch.float32:
+        close(out, ref, 2e-6, 2e-6, "norm")
+    else:
+        close(out, ref, 0, 2 ** -8, "norm rounded once to bfloat16")
+    # selected rows, no delta, nothing written back
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=dev())
+    before = xd.clone()
+    out2 = torch.empty(3, hidden, dtype=torch.float32, device=dev())
+    k.add_rmsnorm(xd, None, w.float().to(dev()), eps, out2, rows=rows, write_back=False)
+    assert torch.equal(xd, before)
+    close(out2, pl.rms_norm(ref_x[[5, 0, 5]], w.double(), eps), 3e-6, 3e-6, "selected rows")
+    zero = torch.zeros(2, hidden, device=dev())
+    outz = torch.ones(2, hidden, device=dev())
+    k.add_rmsnorm(zero, None, w.float().to(dev()), eps, outz)
+    assert torch.equal(outz, torch.zeros_like(outz))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_swiglu(dtype):
+    k = kernels()
+    g = torch.Generator().manual_seed(3)
+    table = torch.randn(301, 70, generator=g).to(dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32)
+    out = torch.empty(5, 70, device=dev())
+    k.embedding(table.to(dev()), ids.to(dev()), out)
+    assert torch.equal(out.cpu(), pl.embed(table, ids.tolist()).float())
+    gate_up = torch.randn(9, 2 * 333, generator=g) * 4
+    gate_up[0, 0], gate_up[0, 1] = 90.0, -90.0            # far tails of the sigmoid stay finite
+    act = torch.empty(9, 333, dtype=dtype, device=dev())
+    k.swiglu(gate_up.to(dev()), act)
+    gt, up = gate_up[:, :333].double(), gate_up[:, 333:].double()
+    ref = gt / (1 + torch.exp(-gt)) * up
+    assert torch.isfinite(act).all()
+    close(act, ref, 1e-6 if dtype == torch.float32 else 0, 3e-6 if dtype == torch.float32 else 2 ** -8, "swiglu")
+
+
+@pytest.mark.parametrize("m,n,kk", [(1, 7, 13), (5, 576, 64), (33, 100, 257), (64, 3072, 576), (130, 49, 1536)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm(m, n, kk, dtype):
+    k = kernels()
+    g = torch.Generator().manual_seed(m * n)
+    a = torch.randn(m, kk, generator=g).to(dtype)
+    w = torch.randn(n, kk, generator=g).to(dtype)
+    out = torch.empty(m, n, device=dev())
+    k.gemm(a.to(dev()), w.to(dev()), out)
+    ref = a.double() @ w.double().T
+    scale = math.sqrt(kk)
+    close(out, ref, (2e-6 if dtype == torch.float32 else 2e-6) * scale, 1e-5, f"gemm {m}x{n}x{kk}")
+
+
+def test_float32_products_are_true_32_bit():
+    """A reduced-precision matrix mode (TF32 keeps 10 mantissa bits) would lose the small term below."""
+    k = kernels()
+    a = torch.tensor([[1.0, 2.0 ** -12] + [0.0] * 62], device=dev())
+    w = torch.tensor([[1.0, 1.0] + [0.0] * 62] * 8, device=dev())
+    out = torch.empty(1, 8, device=dev())
+    k.gemm(a, w, out)
+    assert out[0, 0].item() == 1.0 + 2.0 ** -12
+
+
+def paged(k_dense, v_dense, page_size, n_pages, seed, dtype):
+    """Scatter dense [T, Hkv, D] keys and values into shuffled pages; returns caches and a table row."""
+    t, hkv, d = k_dense.shape
+    need = -(-t // page_size)
+    perm = np.random.default_rng(seed).permutation(n_pages)[:need]
+    kc = torch.full((n_pages, hkv, page_size, d), float("nan"), dtype=dtype)
+    vc = torch.full((n_pages, hkv, page_size, d), float("nan"), dtype=dtype)
+    for pos in range(t):
+        page, off = perm[pos // page_size], pos % page_size
+        kc[page, :, off] = k_dense[pos].to(dtype)
+        vc[page, :, off] = v_dense[pos].to(dtype)
+    return kc, vc, perm.astype(np.int32)
+
+
+def run_attention(q_all, k_all, v_all, q_lens, page_size, dtype, window=None, split_size=None, seed=0, width=64):
+    """Requests given as whole sequences; the last q_lens[r] positions of each are this step's queries."""
+    k = kernels()
+    R = len(q_all)
+    hq, d = q_all[0].shape[1:]
+    hkv = k_all[0].shape[1]
+    n_pages = sum(-(-x.shape[0] // page_size) for x in k_all) + 3
+    kc = torch.zeros((n_pages, hkv, page_size, d), dtype=dtype)
+    vc = torch.zeros_like(kc)
+    table = np.full((R + 1, width), -1, dtype=np.int32)
+    perm = np.random.default_rng(seed).permutation(n_pages)
+    used = 0
+    for r in range(R):
+        t = k_all[r].shape[0]
+        need = -(-t // page_size)
+        pages = perm[used:used + need]; used += need
+        table[r + 1, :need] = pages                      # request r sits in slot r + 1
+        for pos in range(t):
+            kc[pages[pos // page_size], :, pos % page_size] = k_all[r][pos].to(dtype)
+            vc[pages[pos // page_size], :, pos % page_size] = v_all[r][pos].to(dtype)
+    q = torch.cat([q_all[r][-q_lens[r]:] for r in range(R)]).to(dtype)
+    total = q.shape[0]
+    q_start = np.cumsum([0] + q_lens[:-1]).astype(np.int32)
+    ctx = np.asarray([x.shape[0] for x in k_all], dtype=np.int32)
+    tile_req, tile_q0, dec_req = [], [], []
+    for r, n in enumerate(q_lens):
+        if n == 1:
+            dec_req.append(r)
+        else:
+            for q0 in range(0, n, k.PREFILL_TILE):
+                tile_req.append(r); tile_q0.append(q0)
+    i32 = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32), device=dev())
+    out = torch.full((total, hq, d), float("nan"), dtype=dtype, device=dev())
+    args = dict(hq=hq, hkv=hkv, page_size=page_size, scale=d ** -0.5, window=window)
+    kcd, vcd, qd = kc.to(dev()), vc.to(dev()), q.to(dev()).contiguous()
+    req_slot = i32(np.arange(1, R + 1)); tab = i32(table)
+    if tile_req:
+        k.attn_prefill(qd, out, kcd, vcd, req_slot, tab, i32(tile_req), i32(tile_q0), i32(q_start), i32(q_lens), i32(ctx), **args)
+    if dec_req:
+        max_ctx = int(max(ctx[r] for r in dec_req))
+        size = split_size or 64
+        n_splits = -(-max_ctx // size)
+        partial = torch.full((len(dec_req), hq, n_splits, d), float("nan"), device=dev())
+        stats = torch.full((len(dec_req), hq, n_splits, 2), float("nan"), device=dev())
+        k.attn_decode(qd, out, kcd, vcd, req_slot, tab, i32(dec_req), len(dec_req), i32(q_start), i32(ctx), partial, stats,
+                      split_size=size, n_splits=n_splits, **args)
+    refs = []
+    for r in range(R):
+        qq = q_all[r].to(dtype).double(); kk = k_all[r].to(dtype).double(); vv = v_all[r].to(dtype).double()
+        refs.append(pl.causal_attention(qq, kk, vv, window)[-q_lens[r]:])
+    return out, torch.cat(refs)
+
+
+def random_qkv(t, hq, hkv, d, seed, sharp=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(t, hq, d, generator=g) * sharp, torch.randn(t, hkv, d, generator=g), torch.randn(t, hkv, d, generator=g))
+
+
+ATT_TOL = {torch.float32: (3e-6, 1e-5), torch.bfloat16: (2e-2, 2e-2)}
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(64, 9, 3), (128, 4, 4), (48, 5, 1), (16, 2, 2)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_mixed_portions_and_decode(d, hq, hkv, dtype):
+    """Whole prompts, portions with earlier context, and single tokens in one launch pair; pages of 8 in shuffled order."""
+    lens, q_lens = [200, 77, 130, 1, 301, 65], [200, 13, 1, 1, 1, 2]
+    data = [random_qkv(t, hq, hkv, d, 10 * d + i, sharp=2.0) for i, t in enumerate(lens)]
+    out, ref = run_attention([x[0] for x in data], [x[1] for x in data], [x[2] for x in data], q_lens, 8, dtype, seed=d)
+    assert torch.isfinite(out).all()
+    close(out, ref, *ATT_TOL[dtype], "attention")
+
+
+@pytest.mark.parametrize("needle", [0, 15, 16, 63, 64, 255, 256, 511, 640])
+@pytest.mark.parametrize("q_len", [1, 5])
+def test_attention_finds_one_far_key_among_hundreds(needle, q_len):
+    """One key is made to stand out for the last query; the output must be that key's value (page and split edges)."""
+    t, hq, hkv, d = 700, 6, 2, 64
+    q, k_, v = random_qkv(t, hq, hkv, d, needle)
+    q[-1] = q[-1] / q[-1].norm(dim=-1, keepdim=True) * 6
+    for h in range(hkv):
+        k_[needle, h] = q[-1, h * 3] * 4          # aligned with the first query head of each group
+    v[needle] = 100.0
+    out, ref = run_attention([q], [k_], [v], [q_len], 16, torch.float32, split_size=64, seed=needle)
+    close(out, ref, 2e-4, 1e-5, f"needle at {needle}")
+    assert out[-1, 0, 0].item() > 99.0 and out[-1, 3, 0].item() > 99.0
+
+
+@pytest.mark.parametrize("window", [1, 16, 17, 100])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_window_edge(window, dtype):
+    """Keys at the window's edge are made large: one position too many or too few changes the result visibly."""
+    t, hq, hkv, d = 260, 4, 2, 32
+    q, k_, v = random_qkv(t, hq, hkv, d, window)
+    for pos in (t - 1 - window, t - window, 40 - window, 41 - window):
+        if pos >= 0:
+            v[pos] = 50.0 * (1 + pos % 3)
+    lens_q = [[t], [1], [t - 40]]
+    for q_lens in lens_q:
+        out, ref = run_attention([q], [k_], [v], q_lens, 16, dtype, window=window, seed=window)
+        close(out, ref, 5e-5 if dtype == torch.float32 else 0.3, 1e-5 if dtype == torch.float32 else 2e-2, f"window {window}")
+
+
+def test_attention_ignores_pages_that_the_window_has_passed():
+    """Entries of passed pages are -1 in the table; the kernels must not follow them."""
+    k = kernels()
+    t, hq, hkv, d, window, page = 100, 2, 1, 16, 20, 8
+    q, k_, v = random_qkv(t, hq, hkv, d, 5)
+    kc, vc, pages = paged(k_, v, page, 20, 1, torch.float32)
+    table = np.full((1, 16), -1, dtype=np.int32)
+    table[0, :len(pages)] = pages
+    dead = (t - window + 1) // page
+    table[0, :dead] = -1
+    i32 = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32), device=dev())
+    for q_len in (1, 3):
+        out = torch.empty(q_len, hq, d, device=dev())
+        common = (q[-q_len:].contiguous().to(dev()), out, kc.to(dev()), vc.to(dev()), i32([0]), i32(table))
+        if q_len == 1:
+            partial = torch.empty(1, hq, 2, d, device=dev()); stats = torch.empty(1, hq, 2, 2, device=dev())
+            k.attn_decode(*common, i32([0]), 1, i32([0]), i32([t]), partial, stats, hq, hkv, page, d ** -0.5, window, 64, 2)
+        else:
+            k.attn_prefill(*common, i32([0]), i32([0]), i32([0]), i32([q_len]), i32([t]), hq, hkv, page, d ** -0.5, window)
+        ref = pl.causal_attention(q.double(), k_.double(), v.double(), window)[-q_len:]
+        close(out, ref, 3e-6, 1e-5, "window with freed pages")
+
+
+@pytest.mark.parametrize("interleaved,rot", [(False, 32), (True, 32), (False, 16)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_store(interleaved, rot, dtype):
+    """Rotation of q and k, and keys and values landing on the right page and offset."""
+    k = kernels()
+    t, hq, hkv, d, page, theta = 11, 3, 2, 32, 4, 25000.0
+    g = torch.Generator().manual_seed(1)
+    proj = torch.randn(t, (hq + 2 * hkv) * d, generator=g)
+    positions = torch.tensor([5, 6, 7, 8, 0, 1, 2, 3, 40, 41, 42], dtype=torch.int32)
+    token_req = torch.tensor([0] * 4 + [1] * 4 + [2] * 3, dtype=torch.int32)
+    req_slot = torch.tensor([2, 0, 1], dtype=torch.int32)
+    table = torch.full((3, 16), -1, dtype=torch.int32)
+    table[2, :3] = torch.tensor([7, 3, 9]); table[0, :1] = 5; table[1, 10] = 1
+    half = rot // 2
+    inv = theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / rot)
+    cos = torch.empty(t, half, device=dev()); sin = torch.empty(t, half, device=dev())
+    k.rotary_tables(positions.to(dev()), inv.to(dev()), cos, sin)
+    angle = positions.double()[:, None] * inv[None]
+    close(cos, torch.cos(angle), 1e-7, 0, "cos table"); close(sin, torch.sin(angle), 1e-7, 0, "sin table")
+    q_out = torch.empty(t, hq, d, dtype=dtype, device=dev())
+    kc = torch.zeros(12, hkv, page, d, dtype=dtype, device=dev()); vc = torch.zeros_like(kc)
+    k.rope_store(proj.to(dev()), hq * d, (hq + hkv) * d, cos, sin, half, interleaved, q_out, kc, vc, token_req.to(dev()),
+                 positions.to(dev()), req_slot.to(dev()), table.to(dev()), page, hq, hkv, d)
+
+    def rotate(x):
+        x = x.double()
+        out = x.clone()
+        c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        if interleaved:
+            a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+            out[..., 0:rot:2], out[..., 1:rot:2] = a * c - b * s, b * c + a * s
+        else:
+            a, b = x[..., :half], x[..., half:rot]
+            out[..., :half], out[..., half:rot] = a * c - b * s, b * c + a * s
+        return out
+
+    if not interleaved and rot == d:
+        close(rotate(proj[:, :hq * d].reshape(t, hq, d)), pl.rotary(proj[:, :hq * d].reshape(t, hq, d).double(), positions, theta), 1e-12, 0, "test's own rotation")
+    tol = (2e-6, 2e-6) if dtype == torch.float32 else (0, 2 ** -8)
+    close(q_out, rotate(proj[:, :hq * d].reshape(t, hq, d)), *tol, "q")
+    k_ref = rotate(proj[:, hq * d:(hq + hkv) * d].reshape(t, hkv, d))
+    v_ref = proj[:, (hq + hkv) * d:].reshape(t, hkv, d).double()
+    written = 0
+    for i in range(t):
+        page_id = int(table[int(req_slot[int(token_req[i])]), int(positions[i]) // page])
+        off = int(positions[i]) % page
+        close(kc[page_id, :, off], k_ref[i], *tol, "k in cache"); close(vc[page_id, :, off], v_ref[i], *tol, "v in cache")
+        written += 1
+    assert int((kc.float().abs().sum(dim=(1, 3)) > 0).sum()) == written     # nothing else was touched
+
+
+def test_table_update_and_page_copy():
+    k = kernels()
+    table = torch.full((4, 8), -1, dtype=torch.int32, device=dev())
+    idx = torch.tensor([0, 9, 31, -1], dtype=torch.int32, device=dev())
+    val = torch.tensor([5, 6, 7, 99], dtype=torch.int32, device=dev())
+    k.table_update(table, idx, val)
+    expect = torch.full((32,), -1, dtype=torch.int32); expect[0], expect[9], expect[31] = 5, 6, 7
+    assert torch.equal(table.cpu().view(-1), expect)
+    pool = torch.randn(3, 2, 6, 2, 4, 8, device=dev())            # [entries, k|v, pages, kv_heads, page, dim]
+    before = pool.clone()
+    pairs = torch.tensor([[1, 4], [0, 5]], dtype=torch.int32, device=dev())
+    page_bytes = 2 * 4 * 8 * 4
+    k.page_copy(pool, pairs, 6, 6 * page_bytes, page_bytes)
+    assert torch.equal(pool[:, :, 4], before[:, :, 1]) and torch.equal(pool[:, :, 5], before[:, :, 0])
+    assert torch.equal(pool[:, :, :4], before[:, :, :4])
+
+
+def test_greedy_sampling_takes_the_lowest_index_on_ties():
+    from cisr_b200.sampling import sample_tokens
+    logits = torch.randn(5, 1000, device=dev())
+    logits[0, 700] = logits[0, 300] = 50.0
+    logits[1, 999] = 60.0
+    logits[2, 0] = 60.0
+    got = sample_tokens(logits).cpu().tolist()
+    assert got[:3] == [300, 999, 0] and got[3:] == logits[3:].argmax(dim=-1).cpu().tolist()
+
+
+@pytest.mark.parametrize("vocab", [5, 301, 49152])
+def test_temperature_sampling_is_an_inverse_cdf_of_softmax(vocab):
+    from cisr_b200.sampling import sample_tokens, uniform
+    g = torch.Generator().manual_seed(vocab)
+    rows = 64
+    logits = (torch.randn(rows, vocab, generator=g) * 3).to(dev())
+    temp = torch.full((rows,), 0.8, device=dev()); temp[0] = 0.0
+    seed = torch.arange(rows, dtype=torch.int64, device=dev()) * 7919 + 3
+    counter = torch.arange(rows, dtype=torch.int32, device=dev())
+    got = sample_tokens(logits, temp, seed, counter).cpu().tolist()
+    again = sample_tokens(logits, temp, seed, counter).cpu().tolist()
+    assert got == again and got[0] == int(logits[0].argmax())
+    for r in range(1, rows):
+        u = uniform(int(seed[r]), int(counter[r]))
+        assert 0.0 <= u < 1.0
+        cdf = torch.cumsum(pl.temperature_probabilities(logits[r].cpu(), 0.8), dim=0)
+        lo = cdf[got[r] - 1].item() if got[r] else 0.0
+        assert lo - 1e-5 <= u <= cdf[got[r]].item() + 1e-5, f"row {r}: token {got[r]} does not hold u={u}"
+    us = [uniform(11, c) for c in range(2000)]
+    assert abs(np.mean(us) - 0.5) < 0.03 and len(set(us)) > 1990
+    # the batch does not matter: one row alone draws the same token
+    alone = sample_tokens(logits[5:6].contiguous(), temp[5:6].contiguous(), seed[5:6].contiguous(), counter[5:6].contiguous())
+    assert alone.cpu().tolist() == [got[5]]
+
+
+def test_unsupported_head_size_is_refused_clearly():
+    k = kernels()
+    with pytest.raises(k.KernelError, match="multiples of 16"):
+        k.attention_library(40, torch.float32)
+    with pytest.raises(k.KernelError, match="multiples of 16"):
+        k.attention_library(272, torch.bfloat16)

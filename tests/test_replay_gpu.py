@@ -1,0 +1,151 @@
+"""The engine against the plain implementation under every way of cutting and batching the work.
+
+The same requests are replayed whole, with the last 32 tokens decoded one by one, in
+portions of changing size, and mixed with other requests with so few pages that pages are
+used again, in float32 and in bfloat16, in process and through bin/trace_run.
+"""
+import numpy as np
+import pytest
+import torch
+
+import replay
+import tiny_models as tm
+
+pytestmark = pytest.mark.gpu
+
+CASES = {"tiny_a": (tm.TINY_A, 11), "tiny_b": (tm.TINY_B, 12), "tiny_c": (tm.TINY_C, 13)}
+LENGTHS = {"a": 150, "b": 70, "c": 33, "d": 200, "e": 90, "f": 3}
+_cache = {}
+
+
+def setup(case, dtype, tmp_path_factory, sharpen=1.0):
+    key = (case, dtype, sharpen)
+    if key not in _cache:
+        from cisr_b200 import Model
+
+        cfg, seed = CASES[case]
+        weights = tm.make_weights(cfg, seed, scale=0.08, bf16_exact=True)
+        if sharpen != 1.0:
+            for name in weights:
+                if "q_proj" in name or "k_proj" in name:
+                    weights[name] = (weights[name] * sharpen).astype(np.float32)
+        path = tm.write_model_dir(tmp_path_factory.mktemp(f"{case}_{dtype}"), cfg, weights)
+        model = Model.from_pretrained(path, dtype=dtype)
+        requests = {rid: tm.random_tokens(cfg, n, 100 + i) for i, (rid, n) in enumerate(LENGTHS.items())}
+        reference = {rid: replay.plain_logits(cfg, weights, tokens) for rid, tokens in requests.items()}
+        _cache[key] = (cfg, weights, path, model, requests, reference)
+    return _cache[key]
+
+
+def stepper_for(model, steps, slack_pages=0):
+    from cisr_b200 import Stepper
+    return Stepper(model, n_pages=replay.max_live_tokens(steps) // 16 + slack_pages, page_size=16, max_slots=4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", list(CASES))
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_replay_matches_plain(case, dtype, mode, tmp_path_factory):
+    cfg, weights, path, model, requests, reference = setup(case, dtype, tmp_path_factory)
+    steps = {"whole": lambda: replay.trace_whole(requests), "tail": lambda: replay.trace_tail_decode(requests, 32),
+             "portions": lambda: replay.trace_portions(requests, (7, 2, 13, 5, 2, 31, 64, 3)),
+             "mixed": lambda: replay.trace_mixed(requests, seed=7)}[mode]()
+    stepper = stepper_for(model, steps)
+    got = replay.run_steps(stepper, steps)
+    assert len(got) == sum(LENGTHS.values())
+    replay.compare(got, requests, reference, dtype)
+    pool = stepper.cache.page_groups[0].pool
+    assert pool.n_free == pool.n_pages and not stepper.cache.requests
+    if mode == "mixed":
+        assert pool.peak == pool.n_pages or pool.n_pages * 16 < sum(LENGTHS.values())   # pages were used again
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sharp_attention_depends_on_single_far_keys(dtype, tmp_path_factory):
+    """With queries and keys scaled up, softmax is peaked: a wrong or missing key anywhere shows in the logits."""
+    cfg, weights, path, model, requests, reference = setup("tiny_b", dtype, tmp_path_factory, sharpen=6.0)
+    for steps in (replay.trace_whole(requests), replay.trace_mixed(requests, seed=3), replay.trace_tail_decode(requests, 40)):
+        got = replay.run_steps(stepper_for(model, steps), steps)
+        replay.compare(got, requests, reference, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_crosses_many_pages(dtype, tmp_path_factory):
+    cfg, weights, path, model, _, _ = setup("tiny_a", dtype, tmp_path_factory)
+    tokens = tm.random_tokens(cfg, 400, 77)
+    reference = {"long": replay.plain_logits(cfg, weights, tokens)}
+    steps = [{"step": 0, "entries": [{"id": "long", "tokens": tokens[:3], "want": [0, 1, 2]}], "end": []}]
+    steps += [{"step": i - 2, "entries": [{"id": "long", "tokens": [tokens[i]], "want": [0]}], "end": []} for i in range(3, 400)]
+    got = replay.run_steps(stepper_for(model, steps), steps)
+    replay.compare(got, {"long": tokens}, reference, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(dtype, tmp_path_factory):
+    """Prompts of one, two and three tokens, alone and side by side, and logits wanted only at some places."""
+    cfg, weights, path, model, _, _ = setup("tiny_c", dtype, tmp_path_factory)
+    requests = {f"s{n}": tm.random_tokens(cfg, n, n) for n in (1, 2, 3, 17)}
+    reference = {rid: replay.plain_logits(cfg, weights, t) for rid, t in requests.items()}
+    side_by_side = [{"step": 0, "entries": [{"id": rid, "tokens": t, "want": [len(t) - 1]} for rid, t in requests.items()],
+                     "end": list(requests)}]
+    got = replay.run_steps(stepper_for(model, side_by_side), side_by_side)
+    assert sorted(got) == sorted((rid, len(t) - 1) for rid, t in requests.items())
+    replay.compare(got, requests, reference, dtype)
+    one_by_one = replay.trace_portions(requests, (1,))
+    replay.compare(replay.run_steps(stepper_for(model, one_by_one), one_by_one), requests, reference, dtype)
+    nothing_wanted = [{"step": 0, "entries": [{"id": "s17", "tokens": requests["s17"][:9], "want": []}], "end": []},
+                      {"step": 1, "entries": [{"id": "s17", "tokens": requests["s17"][9:], "want": [7]}], "end": ["s17"]}]
+    got = replay.run_steps(stepper_for(model, nothing_wanted), nothing_wanted)
+    assert list(got) == [("s17", 16)]
+    replay.compare(got, requests, reference, dtype)
+
+
+@pytest.mark.parametrize("dtype,case", [("float32", "tiny_a"), ("bfloat16", "tiny_b")])
+def test_trace_run_program(dtype, case, tmp_path_factory, tmp_path):
+    """bin/trace_run as a user drives it: JSON lines in, <step>.f32 and 'done <step>' out."""
+    cfg, weights, path, model, requests, reference = setup(case, dtype, tmp_path_factory)
+    steps = replay.trace_mixed(requests, seed=11)
+    got = replay.run_trace_program(path, dtype, steps, tmp_path / "out", replay.max_live_tokens(steps), cfg["vocab_size"])
+    assert len(got) == sum(LENGTHS.values())
+    replay.compare(got, requests, reference, dtype)
+
+
+def test_step_refuses_bad_batches_and_runs_out_of_pages_without_side_effects(tmp_path_factory):
+    from cisr_b200 import StepEntry, Stepper
+    from cisr_b200.cache import OutOfPages
+
+    cfg, weights, path, model, requests, reference = setup("tiny_a", "float32", tmp_path_factory)
+    stepper = Stepper(model, n_pages=2, page_size=16, max_slots=2)
+    stepper.create("a"); stepper.create("b")
+    for bad, error in (([], ValueError), ([StepEntry("a", [1]), StepEntry("a", [2])], ValueError),
+                       ([StepEntry("zz", [1])], KeyError), ([StepEntry("a", [])], ValueError),
+                       ([StepEntry("a", [cfg["vocab_size"]])], ValueError), ([StepEntry("a", [1, 2], [2])], ValueError)):
+        with pytest.raises(error):
+            stepper.step(bad)
+    tokens = requests["a"]
+    first = stepper.step([StepEntry("a", tokens[:20], [19])]).cpu().numpy()
+    with pytest.raises(OutOfPages):
+        stepper.step([StepEntry("a", tokens[20:30], [9]), StepEntry("b", tokens[:8], [7])])
+    assert stepper.cache.length("a") == 20 and stepper.cache.length("b") == 0
+    stepper.cache.check()
+    second = stepper.step([StepEntry("a", tokens[20:30], [9])]).cpu().numpy()
+    replay.compare({("a", 19): first[0], ("a", 29): second[0]}, requests, reference, "float32")
+
+
+def test_fork_shares_a_prefix_and_copies_on_write(tmp_path_factory):
+    from cisr_b200 import StepEntry, Stepper
+
+    cfg, weights, path, model, requests, _ = setup("tiny_a", "float32", tmp_path_factory)
+    prefix = requests["a"][:21]                      # one full page and a partly filled one
+    tails = {"x": requests["b"][:9], "y": requests["c"][:9]}
+    stepper = Stepper(model, n_pages=6, page_size=16, max_slots=3)
+    stepper.create("x")
+    stepper.step([StepEntry("x", prefix, [])])
+    stepper.fork("x", "y")
+    logits = stepper.step([StepEntry("x", tails["x"], list(range(9))), StepEntry("y", tails["y"], list(range(9)))]).cpu().numpy()
+    stepper.cache.check()
+    assert stepper.cache.requests["x"].tables[0][0] == stepper.cache.requests["y"].tables[0][0]
+    assert stepper.cache.requests["x"].tables[0][1] != stepper.cache.requests["y"].tables[0][1]
+    for i, rid in enumerate(("x", "y")):
+        ref = replay.plain_logits(cfg, weights, prefix + tails[rid])[21:]
+        replay.compare({(rid, 21 + j): logits[9 * i + j] for j in range(9)}, None, {rid: np.concatenate([np.zeros((21, ref.shape[1])), ref])}, "float32")
