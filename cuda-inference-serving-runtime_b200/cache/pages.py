@@ -22,6 +22,7 @@ class PagePool:
         self.refs = np.zeros(n_pages, dtype=np.int32)
         self.free: List[int] = list(reversed(range(n_pages)))
         self.peak = 0
+        self.taken = 0      # pages handed out so far, counting a page again each time it is reused
 
     @property
     def n_free(self) -> int:
@@ -39,6 +40,7 @@ class PagePool:
         for page in pages:
             self.refs[page] = 1
         self.peak = max(self.peak, self.n_used)
+        self.taken += count
         return pages
 
     def retain(self, page: int) -> None:

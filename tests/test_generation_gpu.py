@@ -54,8 +54,9 @@ def test_eos_stops_generation(tiny):
     prompt = tm.random_tokens(cfg, 9, 5)
     full = pl.generate_greedy(cfg, tm.torch_weights(weights), prompt, 8)
     engine = Engine.for_model(Model.from_pretrained(path, dtype="float32"), pages=8)
-    engine.submit(Request("e", prompt, max_new_tokens=8, eos_token_id=[full[2], 999]))
-    assert engine.run()[0].generated == full[:3]
+    eos = full[2]
+    engine.submit(Request("e", prompt, max_new_tokens=8, eos_token_id=[eos, 999]))
+    assert engine.run()[0].generated == full[:full.index(eos) + 1]
 
 
 def test_temperature_sampling_is_reproducible_and_independent_of_batching(tiny):

@@ -19,6 +19,16 @@ def close(a, b, atol, rtol):
     torch.testing.assert_close(a.double().cpu(), b.double().cpu(), atol=atol, rtol=rtol)
 
 
+def close_for(dtype, a, b):
+    """float32: element by element; bfloat16: relative RMS error of the whole result and no single wild element."""
+    if dtype == torch.float32:
+        return close(a, b, *TOL[dtype])
+    a, b = a.double().cpu(), b.double().cpu()
+    assert torch.isfinite(a).all()
+    assert float(((a - b) ** 2).mean().sqrt() / (b ** 2).mean().sqrt()) < 0.02
+    assert float((a - b).abs().max()) < 0.1 * float(b.abs().max())
+
+
 TOL = {torch.float32: (3e-6, 2e-5), torch.bfloat16: (3e-2, 3e-2)}
 
 
@@ -47,7 +57,7 @@ def test_swiglu_embedding_and_head_parts(dtype):
     out = ffn.forward(h.to(DEV), None)
     ref = pl.swiglu_mlp(h.double(), ws["gate_proj.weight"].double(), ws["up_proj.weight"].double(), ws["down_proj.weight"].double())
     assert out.dtype == torch.float32
-    close(out, ref, *TOL[dtype])
+    close_for(dtype, out, ref)
 
     emb = part("EMBEDDINGS", "token_embedding", {"vocab_size": 300, "hidden_size": 70}, dtype)
     table = torch.randn(300, 70, generator=g).to(dtype)
@@ -127,7 +137,7 @@ def test_attention_part_over_portions(dtype, window):
     for k in ("a", "b"):
         weights = {"L.self_attn." + n: w.double() for n, w in ws.items()}
         ref = pl.attention_block(h[k].double(), weights, "L.", torch.arange(total), cfg, window)
-        close(torch.cat(got[k]), ref, *TOL[dtype])
+        close_for(dtype, torch.cat(got[k]), ref)
     if window is not None:
         assert mini.cache.page_groups[0].pool.n_used <= 2 * (-(-window // 8) + 1)     # passed pages came back
 
@@ -163,7 +173,7 @@ def test_pre_norm_block_arrangement(dtype):
     mini.run(lambda ctx, cache: block.forward(stream, ctx, cache), [("a", 21)])
     cfg = {"num_attention_heads": hq, "num_key_value_heads": hkv, "head_dim": d, "hidden_size": hidden, "rope_theta": 10000.0, "rms_norm_eps": 1e-5}
     ref = pl.decoder_layer((x + pending).double(), weights, 0, torch.arange(21), cfg)
-    close(stream.x + stream.pending, ref, *TOL[dtype])
+    close_for(dtype, stream.x + stream.pending, ref)
 
 
 def test_unknown_parts_are_named_in_the_error():

@@ -103,8 +103,8 @@ def make_weights(seed):
         w[p + "ffn.gate_proj.weight"] = 0.15 * torch.randn(INTER, HIDDEN, generator=g)
         w[p + "ffn.up_proj.weight"] = 0.15 * torch.randn(INTER, HIDDEN, generator=g)
         w[p + "ffn.down_proj.weight"] = 0.15 * torch.randn(HIDDEN, INTER, generator=g)
-    w["blocks.0.mixer.q_proj.weight"] = 0.3 * torch.randn(HEADS * DIM, HIDDEN, generator=g)
-    w["blocks.0.mixer.k_proj.weight"] = 0.3 * torch.randn(KV * DIM, HIDDEN, generator=g)
+    w["blocks.0.mixer.q_proj.weight"] = 0.15 * torch.randn(HEADS * DIM, HIDDEN, generator=g)
+    w["blocks.0.mixer.k_proj.weight"] = 0.15 * torch.randn(KV * DIM, HIDDEN, generator=g)
     w["blocks.0.mixer.v_proj.weight"] = 0.3 * torch.randn(KV * DIM, HIDDEN, generator=g)
     w["blocks.0.mixer.o_proj.weight"] = 0.3 * torch.randn(HIDDEN, HEADS * DIM, generator=g)
     w["blocks.1.mixer.mix.weight"] = 0.3 * torch.randn(HIDDEN, HIDDEN, generator=g)
