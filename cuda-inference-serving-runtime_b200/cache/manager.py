@@ -68,7 +68,7 @@ class PageGroup:
             # [entries, key|value, pages, kv_heads, page_size, head_dim]
             self.storage = torch.zeros((len(entries), 2, n_pages, use.kv_heads, page_size, use.head_dim), dtype=dtype,
                                        device=device)
-            self.device_table = torch.full((max_slots, width), -1, dtype=torch.int32, device=device)
+            self.device_table = torch.full((max_slots + 1, width), -1, dtype=torch.int32, device=device)   # last row: the null slot
         self.host_table = np.full((max_slots, width), -1, dtype=np.int32)
         self.updates: List[Tuple[int, int]] = []   # (flat index into the table, page id)
         self.copies: List[Tuple[int, int]] = []    # (source page, destination page) to run before the next step
@@ -87,7 +87,7 @@ class StateGroup:
         self.entry_slot = {e: i for i, e in enumerate(entries)}
         self.storage = None
         if device is not None:
-            self.storage = torch.zeros((len(entries), max_slots) + tuple(use.state_shape),
+            self.storage = torch.zeros((len(entries), max_slots + 1) + tuple(use.state_shape),
                                        dtype=getattr(torch, use.state_dtype), device=device)
 
 
@@ -134,6 +134,11 @@ class CacheManager:
                 raise ValueError(f"unknown cache use {use.kind!r}")
         self.requests: Dict[object, _Request] = {}
         self.free_slots: List[int] = list(reversed(range(max_slots)))
+
+    @property
+    def null_slot(self) -> int:
+        """A slot no request ever holds: its block table row stays empty.  Padding rows of a fixed-size batch point here."""
+        return self.max_slots
 
     # ---------------------------------------------------------------- requests
     def create(self, key) -> int:

@@ -1,0 +1,172 @@
+"""Decode steps replayed from captured CUDA graphs.
+
+A step in which every request brings exactly one token and wants its logits has a
+fixed shape once the batch is padded to a bucket size, so the whole step (table
+updates, embedding, every layer, final norm, head, sampling, and the feed-back of the
+sampled tokens) is captured once per (batch bucket, context bucket) and replayed with
+new contents in fixed buffers.
+
+Parity: runtime/execution.py:1-6,24-61,102-129 (`ModelProgram`: one program per batch
+size, inputs rebound by content into stable buffers, replay instead of recapture, an
+LRU of programs).  Differences: padding rows point at a null slot whose block table is
+empty, so warm-up and padding never touch a live page (the reference saves and restores
+KV slot 0 around its warm-up, runtime/execution.py:49-59); sampling is inside the graph;
+after a replay the graph's own buffers already hold the next step's inputs, so several
+steps can run back to back without the host (`run_ahead`).
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..ops import kernels
+from ..sampling import sample_tokens
+from .batch import HostBatch, StepContext, StepEntry
+
+MIN_CONTEXT_BUCKET = 256
+
+
+def bucket_of(n: int, minimum: int = 1) -> int:
+    b = minimum
+    while b < n:
+        b *= 2
+    return b
+
+
+def _align(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class DecodeGraph:
+    """One captured decode step for `rows` padded rows and contexts up to `ctx_bucket`."""
+
+    def __init__(self, stepper, rows: int, ctx_bucket: int):
+        self.stepper, self.rows, self.ctx_bucket = stepper, rows, ctx_bucket
+        cache = stepper.cache
+        device = stepper.model.device
+        self.n_updates = 2 * rows
+        names = ["token_ids", "positions", "token_req", "req_slot", "q_start", "q_len", "ctx_len", "dec_req", "logit_rows",
+                 "temperature", "counter", "live"]
+        sizes = {n: rows for n in names}
+        sizes["seed"] = 2 * rows
+        names.append("seed")
+        for g in cache.page_groups:
+            for kind in ("upd_idx", "upd_val"):
+                sizes[f"{kind}{g.index}"] = self.n_updates
+                names.append(f"{kind}{g.index}")
+        self.offsets: Dict[str, Tuple[int, int]] = {}
+        total = 0
+        for n in names:
+            self.offsets[n] = (total, sizes[n])
+            total += _align(sizes[n])
+        self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=device)
+        arange = np.arange(rows, dtype=np.int32)
+        for n in ("token_req", "q_start", "dec_req", "logit_rows"):
+            self.h(n)[:] = arange
+        self.h("q_len")[:] = 1
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.tokens = torch.zeros(rows, dtype=torch.int32, device=device)
+        self.replays = 0
+        self.launches = {"own": 0, "library": 0}
+
+    def h(self, name: str) -> np.ndarray:
+        start, size = self.offsets[name]
+        return self.host_np[start:start + size]
+
+    def d(self, name: str) -> torch.Tensor:
+        start, size = self.offsets[name]
+        return self.dev[start:start + size]
+
+    def fill(self, slots, tokens, positions, temperature, seed, counter, updates) -> None:
+        """Write one step's contents into the pinned buffer (rows beyond the live ones become padding)."""
+        n, rows = len(slots), self.rows
+        null = self.stepper.cache.null_slot
+        self.h("token_ids")[:n] = tokens; self.h("token_ids")[n:] = 0
+        self.h("positions")[:n] = positions; self.h("positions")[n:] = 0
+        self.h("req_slot")[:n] = slots; self.h("req_slot")[n:] = null
+        self.h("ctx_len")[:n] = np.asarray(positions) + 1; self.h("ctx_len")[n:] = 0
+        self.h("live")[:n] = 1; self.h("live")[n:] = 0
+        self.h("temperature").view(np.float32)[:n] = temperature; self.h("temperature")[n:] = 0
+        self.h("seed").view(np.int64)[:n] = seed
+        self.h("counter")[:n] = counter; self.h("counter")[n:] = 0
+        for g, (idx, val) in zip(self.stepper.cache.page_groups, updates):
+            hi, hv = self.h(f"upd_idx{g.index}"), self.h(f"upd_val{g.index}")
+            hi[:] = -1
+            hi[:idx.size] = idx
+            hv[:idx.size] = val
+
+    def upload(self) -> None:
+        self.dev.copy_(self.host, non_blocking=True)
+
+    def _run(self, advance: bool) -> None:
+        stepper = self.stepper
+        cache, model = stepper.cache, stepper.model
+        for g in cache.page_groups:
+            kernels.table_update(g.device_table, self.d(f"upd_idx{g.index}"), self.d(f"upd_val{g.index}"))
+        host = HostBatch([None] * self.rows, [cache.null_slot] * self.rows, list(range(self.rows)), [1] * self.rows,
+                         [0] * self.rows, self.rows, list(range(self.rows)))
+        ctx = StepContext(model.device, host)
+        ctx.token_ids, ctx.positions, ctx.token_req = self.d("token_ids"), self.d("positions"), self.d("token_req")
+        ctx.req_slot, ctx.q_start, ctx.q_len, ctx.ctx_len = self.d("req_slot"), self.d("q_start"), self.d("q_len"), self.d("ctx_len")
+        ctx.tile_req = ctx.tile_q0 = self.d("dec_req")[:0]
+        ctx.dec_req, ctx.n_tiles, ctx.n_decode = self.d("dec_req"), 0, self.rows
+        ctx.logit_rows = self.d("logit_rows")
+        ctx.max_decode_ctx = self.ctx_bucket
+        self.logits = model.forward(ctx, cache)
+        sample_tokens(self.logits, self.d("temperature").view(torch.float32), self.d("seed").view(torch.int64),
+                      self.d("counter"), out=self.tokens)
+        if advance:
+            kernels.decode_advance(self.d("token_ids"), self.d("positions"), self.d("ctx_len"), self.d("counter"),
+                                   self.tokens, self.d("live"))
+
+    def capture(self) -> None:
+        """Warm up once outside the graph (library set-up, kernel attributes), then capture."""
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            self._run(advance=False)
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        before = dict(kernels.LAUNCHES)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._run(advance=True)
+        self.launches = {k: kernels.LAUNCHES[k] - before[k] for k in before}   # kernels one replay launches
+
+    def replay(self) -> None:
+        self.graph.replay()
+        self.replays += 1
+
+
+class DecodeGraphs:
+    """The graphs of one stepper, kept by (batch bucket, context bucket), least recently used evicted first."""
+
+    def __init__(self, stepper, capacity: int = 8):
+        self.stepper, self.capacity = stepper, capacity
+        self.graphs: "OrderedDict[Tuple[int, int], DecodeGraph]" = OrderedDict()
+        self.hits = self.misses = self.evictions = 0
+
+    def get(self, n_rows: int, max_ctx: int) -> Tuple[DecodeGraph, bool]:
+        key = (bucket_of(n_rows), bucket_of(max_ctx, MIN_CONTEXT_BUCKET))
+        graph = self.graphs.get(key)
+        if graph is not None:
+            self.graphs.move_to_end(key)
+            self.hits += 1
+            return graph, False
+        self.misses += 1
+        graph = DecodeGraph(self.stepper, *key)
+        self.graphs[key] = graph
+        while len(self.graphs) > self.capacity:
+            self.graphs.popitem(last=False)
+            self.evictions += 1
+        return graph, True
+
+    def report(self) -> dict:
+        return {"entries": len(self.graphs), "hits": self.hits, "misses": self.misses, "evictions": self.evictions,
+                "replays": {f"{k[0]}x{k[1]}": g.replays for k, g in self.graphs.items()}}

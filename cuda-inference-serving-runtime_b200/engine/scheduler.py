@@ -100,7 +100,7 @@ class Engine:
         from ..sampling import DeviceSampler
         from .step import Stepper
 
-        stepper = Stepper(model, n_pages=pages, page_size=page_size, max_slots=max(max_active, 1))
+        stepper = Stepper(model, n_pages=pages, page_size=page_size, max_slots=max(max_active, 1), graph=graph)
         sampler = DeviceSampler(stepper)
         return cls(stepper, sampler, model.spec.vocab_size, model.spec.max_positions, max_active, token_budget,
                    prefill_chunk, policy, reserve)

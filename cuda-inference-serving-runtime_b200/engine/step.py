@@ -22,10 +22,7 @@ from .batch import HostBatch, PinnedRing, StepContext, StepEntry, build_context
 from .model import Model
 
 
-def prepare_step(cache: CacheManager, ring: PinnedRing, device, entries: Sequence[StepEntry], vocab_size: int,
-                 extra: Optional[Dict[str, np.ndarray]] = None):
-    """Validate a batch, reserve its pages (all or nothing), send its metadata and bring the device's block
-    tables up to date.  Returns (context, device views of `extra`).  Lengths advance in `commit_step`."""
+def validate_entries(cache: CacheManager, entries: Sequence[StepEntry], vocab_size: int) -> None:
     if not entries:
         raise ValueError("a step needs at least one entry")
     keys = [e.key for e in entries]
@@ -40,6 +37,24 @@ def prepare_step(cache: CacheManager, ring: PinnedRing, device, entries: Sequenc
             raise ValueError(f"token out of range in entry of {e.key!r}")
         if any(w < 0 or w >= len(e.tokens) for w in e.want):
             raise ValueError(f"wanted place outside the tokens of entry {e.key!r}")
+
+
+def run_page_copies(cache: CacheManager, device) -> None:
+    """Copy-on-write of shared, partly filled pages queued by `reserve`, for every entry of a group at once."""
+    for g in cache.page_groups:
+        copies = cache.drain_copies(g.index)
+        if copies:
+            pairs = torch.tensor(copies, dtype=torch.int32, device=device)
+            page_bytes = g.page_bytes()
+            kernels.page_copy(g.storage, pairs, g.storage.shape[0] * 2, g.pool.n_pages * page_bytes, page_bytes)
+
+
+def prepare_step(cache: CacheManager, ring: PinnedRing, device, entries: Sequence[StepEntry], vocab_size: int,
+                 extra: Optional[Dict[str, np.ndarray]] = None):
+    """Validate a batch, reserve its pages (all or nothing), send its metadata and bring the device's block
+    tables up to date.  Returns (context, device views of `extra`).  Lengths advance in `commit_step`."""
+    validate_entries(cache, entries, vocab_size)
+    keys = [e.key for e in entries]
     cache.reserve([(e.key, len(e.tokens)) for e in entries])   # raises before any change
 
     slots, q_start, q_len, ctx_len, logit_rows = [], [], [], [], []
@@ -62,11 +77,7 @@ def prepare_step(cache: CacheManager, ring: PinnedRing, device, entries: Sequenc
     for g, (idx, val) in zip(cache.page_groups, update_views):
         if idx.numel():
             kernels.table_update(g.device_table, idx, val)
-        copies = cache.drain_copies(g.index)
-        if copies:   # copy-on-write of shared, partly filled pages, for every entry of the group at once
-            pairs = torch.tensor(copies, dtype=torch.int32, device=device)
-            page_bytes = g.page_bytes()
-            kernels.page_copy(g.storage, pairs, g.storage.shape[0] * 2, g.pool.n_pages * page_bytes, page_bytes)
+    run_page_copies(cache, device)
     return ctx, extras
 
 
@@ -76,7 +87,10 @@ def commit_step(cache: CacheManager, entries: Sequence[StepEntry]) -> None:
 
 
 class Stepper:
-    def __init__(self, model: Model, n_pages: int, page_size: int = 16, max_slots: int = 64):
+    """`graph=True` replays steps made only of single new tokens from captured CUDA graphs (see engine/graph.py);
+    it is ignored when a mixer of the model reads the step through host values."""
+
+    def __init__(self, model: Model, n_pages: int, page_size: int = 16, max_slots: int = 64, graph: bool = False):
         if not model.loaded:
             raise RuntimeError("the model has no weights yet")
         self.model = model
@@ -84,6 +98,12 @@ class Stepper:
         self.ring = PinnedRing()
         self.last_context: Optional[StepContext] = None
         self.last_extras: Dict[str, torch.Tensor] = {}
+        self.last_tokens: Optional[torch.Tensor] = None     # tokens a graph step sampled itself
+        self.graphs = None
+        if graph and all(layer.mixer.graph_safe for layer in model.layers):
+            from .graph import DecodeGraphs
+            self.graphs = DecodeGraphs(self)
+        self._ahead = None
 
     # requests -------------------------------------------------------------
     def create(self, key) -> None:
@@ -98,8 +118,78 @@ class Stepper:
     # the step ---------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry], extra: Optional[Dict[str, np.ndarray]] = None) -> torch.Tensor:
         """Float logits [number of wanted places, vocab], in the order of the entries and of their `want`."""
+        self._ahead = None
+        if self.graphs is not None and entries and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return self._graph_step(entries, extra)
         ctx, extras = prepare_step(self.cache, self.ring, self.model.device, entries, self.model.spec.vocab_size, extra)
         logits = self.model.forward(ctx, self.cache)
         commit_step(self.cache, entries)
-        self.last_context, self.last_extras = ctx, extras
+        self.last_context, self.last_extras, self.last_tokens = ctx, extras, None
         return logits
+
+    def _flush_tables(self, limit: int):
+        """Pending block-table changes per group; those beyond `limit` entries are applied at once."""
+        device = self.model.device
+        out = []
+        for g in self.cache.page_groups:
+            idx, val = self.cache.drain_table_updates(g.index)
+            if idx.size > limit:
+                kernels.table_update(g.device_table, torch.from_numpy(idx).to(device), torch.from_numpy(val).to(device))
+                idx, val = idx[:0], val[:0]
+            out.append((idx, val))
+        run_page_copies(self.cache, device)
+        return out
+
+    def _graph_step(self, entries: Sequence[StepEntry], extra) -> torch.Tensor:
+        cache = self.cache
+        validate_entries(cache, entries, self.model.spec.vocab_size)
+        cache.reserve([(e.key, 1) for e in entries])
+        n = len(entries)
+        slots = [cache.slot(e.key) for e in entries]
+        positions = [cache.length(e.key) for e in entries]
+        graph, fresh = self.graphs.get(n, max(positions) + 1)
+        updates = self._flush_tables(graph.n_updates)
+        extra = extra or {}
+        graph.fill(slots, [int(e.tokens[0]) for e in entries], positions, extra.get("temperature", 0.0),
+                   extra.get("seed", 0), extra.get("counter", 0), updates)
+        graph.upload()
+        if fresh:
+            graph.capture()
+        graph.replay()
+        commit_step(cache, entries)
+        self.last_context, self.last_extras, self.last_tokens = None, {}, graph.tokens[:n]
+        self._ahead = (graph, [e.key for e in entries])
+        return graph.logits[:n]
+
+    def decode_ahead(self, steps: int) -> torch.Tensor:
+        """Run up to `steps` more decode steps of the batch of the last step without the host in between.
+
+        Each step feeds every request the token the step before sampled for it (on the device).  Valid only
+        right after a step that ran from a graph; stops early at the graph's context limit.  Pages for all
+        the steps are reserved first, all or nothing.  Returns the sampled tokens, int32 [steps run, requests].
+        """
+        if self._ahead is None:
+            raise RuntimeError("decode_ahead follows a step of single tokens that ran from a CUDA graph")
+        graph, keys = self._ahead
+        cache = self.cache
+        longest = max(cache.length(k) for k in keys)
+        steps = min(steps, graph.ctx_bucket - longest, self.model.spec.max_positions - longest)
+        if steps <= 0:
+            return torch.empty((0, len(keys)), dtype=torch.int32, device=self.model.device)
+        cache.reserve([(k, steps) for k in keys])
+        device = self.model.device
+        for g in cache.page_groups:
+            idx, val = cache.drain_table_updates(g.index)
+            if idx.size:
+                kernels.table_update(g.device_table, torch.from_numpy(idx).to(device), torch.from_numpy(val).to(device))
+        run_page_copies(cache, device)
+        for g in cache.page_groups:   # the tables are up to date: the graph's own update lists must do nothing
+            graph.d(f"upd_idx{g.index}").fill_(-1)
+        history = torch.empty((steps, graph.rows), dtype=torch.int32, device=device)
+        for i in range(steps):
+            graph.replay()
+            history[i].copy_(graph.tokens, non_blocking=True)
+        for k in keys:
+            cache.commit(k, steps)
+        self.last_tokens = graph.tokens[:len(keys)]
+        return history[:, :len(keys)]

@@ -38,7 +38,12 @@ def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(status: int, what: str) -> None:
+LAUNCHES = {"own": 0, "library": 0}   # kernels launched so far: this package's own, and vendor-library products
+
+
+def _check(status: int, what: str, own: int = 1, library: int = 0) -> None:
+    LAUNCHES["own"] += own
+    LAUNCHES["library"] += library
     if status != 0:
         detail = {-2: "invalid argument", -3: "shared memory need exceeds the device limit"}.get(status, "")
         raise KernelError(f"{what} failed with status {status} {detail}".rstrip())
@@ -222,7 +227,7 @@ def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec,
     lib = attention_library(dim, k_cache.dtype)
     _check(lib.cisr_attn_decode(_p(q), _p(out), _p(k_cache), _p(v_cache), _p(req_slot), _p(block_table), block_table.shape[1],
                                 _p(dec_req), n_dec, _p(q_start), _p(ctx_len), _p(partial), _p(stats), hq, hkv, page_size,
-                                ctypes.c_float(scale), int(window or 0), split_size, n_splits, _stream()), "attn_decode")
+                                ctypes.c_float(scale), int(window or 0), split_size, n_splits, _stream()), "attn_decode", own=2)
 
 
 # ------------------------------------------------------------------ sampling
@@ -287,7 +292,8 @@ def gemm_library(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.T
     n = w.shape[0]
     if w.shape[1] != k or out.shape != (m, n):
         raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
-    _check(_gemm_library().cisr_gemm_library(_p(a), _p(w), dtype_code(a.dtype), _p(out), m, n, k, _stream()), "gemm")
+    _check(_gemm_library().cisr_gemm_library(_p(a), _p(w), dtype_code(a.dtype), _p(out), m, n, k, _stream()), "gemm",
+           own=0, library=1)
     return out
 
 

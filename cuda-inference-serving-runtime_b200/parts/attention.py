@@ -21,6 +21,8 @@ from .linear import linear
 class GQAAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, position (PartSpec), window (None or int), scale."""
 
+    graph_safe = True
+
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         self.hidden = int(spec["hidden_size"])

@@ -71,6 +71,10 @@ class Rotation:
 
 
 class Mixer(Part):
+    # True when `forward` reads the step only through device tensors of the context (never `ctx.host`), so that
+    # a captured CUDA graph of it stays right when replayed with other requests, positions and lengths.
+    graph_safe = False
+
     def cache_use(self) -> CacheUse:
         return CacheUse("none")
 

@@ -35,7 +35,9 @@ class DeviceSampler:
 
     def __call__(self, logits: torch.Tensor, requests: Sequence) -> List[int]:
         extras = self.stepper.last_extras
-        if extras and "temperature" in extras:
+        if getattr(self.stepper, "last_tokens", None) is not None:
+            tokens = self.stepper.last_tokens        # the step ran from a graph that samples itself
+        elif extras and "temperature" in extras:
             tokens = sample_tokens(logits, extras["temperature"].view(torch.float32), extras["seed"].view(torch.int64),
                                    extras["counter"])
         else:
