@@ -175,15 +175,26 @@ def table_update(table: torch.Tensor, idx: torch.Tensor, val: torch.Tensor) -> N
 
 # ------------------------------------------------------------------ attention (one library per head size and storage)
 _attention_libs = {}
+TENSOR_CORE_MAX_HEAD_DIM = 128
 
 
-def attention_library(head_dim: int, dtype: torch.dtype):
+def _attention_source(head_dim: int, dtype: torch.dtype, kind: str):
+    """bfloat16 heads up to 128 wide run on the tensor cores; float, and wider heads, on the CUDA cores."""
+    if kind not in ("auto", "simt"):
+        raise KernelError(f"unknown attention kernel kind {kind!r}")
+    if kind == "auto" and dtype == torch.bfloat16 and head_dim <= TENSOR_CORE_MAX_HEAD_DIM:
+        return "attention_mma.cu", {"HEAD_DIM": head_dim}
+    return "attention.cu", {"HEAD_DIM": head_dim, "STORAGE_BF16": dtype_code(dtype)}
+
+
+def attention_library(head_dim: int, dtype: torch.dtype, kind: str = "auto"):
     if head_dim % 16 or not 16 <= head_dim <= 256:
         raise KernelError(f"attention kernels take head sizes that are multiples of 16 from 16 to 256, not {head_dim}")
-    key = (head_dim, dtype)
+    source, defines = _attention_source(head_dim, dtype, kind)
+    key = (source, head_dim, dtype)
     lib = _attention_libs.get(key)
     if lib is None:
-        lib = load_library("attention.cu", {"HEAD_DIM": head_dim, "STORAGE_BF16": dtype_code(dtype)})
+        lib = load_library(source, defines)
         for name in ("cisr_attn_prefill", "cisr_attn_decode", "cisr_attn_head_dim", "cisr_attn_prefill_tile"):
             getattr(lib, name).restype = ctypes.c_int
         assert lib.cisr_attn_head_dim() == head_dim
@@ -193,14 +204,15 @@ def attention_library(head_dim: int, dtype: torch.dtype):
 
 def attention_jobs(head_dim: int, dtype: torch.dtype):
     """The build job of the attention library for this head size and storage type."""
-    return ("attention.cu", {"HEAD_DIM": head_dim, "STORAGE_BF16": dtype_code(dtype)}, ())
+    source, defines = _attention_source(head_dim, dtype, "auto")
+    return (source, defines, ())
 
 
 PREFILL_TILE = 64
 
 
 def attn_prefill(q, out, k_cache, v_cache, req_slot, block_table, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv,
-                 page_size, scale, window) -> None:
+                 page_size, scale, window, kind: str = "auto") -> None:
     """Attention of portions: q, out [tokens, hq, D]; tiles list (request, first query of the tile)."""
     dim = k_cache.shape[-1]
     _need(q, k_cache.dtype, "q"); _need(out, k_cache.dtype, "out"); _need(k_cache, None, "k_cache", 4)
@@ -208,14 +220,14 @@ def attn_prefill(q, out, k_cache, v_cache, req_slot, block_table, tile_req, tile
     for name, t in (("req_slot", req_slot), ("block_table", block_table), ("tile_req", tile_req), ("tile_q0", tile_q0), ("q_start", q_start),
                     ("q_len", q_len), ("ctx_len", ctx_len)):
         _need(t, torch.int32, name)
-    lib = attention_library(dim, k_cache.dtype)
+    lib = attention_library(dim, k_cache.dtype, kind)
     _check(lib.cisr_attn_prefill(_p(q), _p(out), _p(k_cache), _p(v_cache), _p(req_slot), _p(block_table), block_table.shape[1],
                                  _p(tile_req), _p(tile_q0), tile_req.numel(), _p(q_start), _p(q_len), _p(ctx_len),
                                  hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), _stream()), "attn_prefill")
 
 
 def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, q_start, ctx_len, partial, stats, hq, hkv,
-                page_size, scale, window, split_size, n_splits) -> None:
+                page_size, scale, window, split_size, n_splits, kind: str = "auto") -> None:
     """Attention of single new tokens, split over key ranges of `split_size`, merged into out."""
     dim = k_cache.shape[-1]
     _need(q, k_cache.dtype, "q"); _need(out, k_cache.dtype, "out"); _need(k_cache, None, "k_cache", 4)
@@ -224,7 +236,7 @@ def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec,
         _need(t, torch.int32, name)
     if partial.numel() < n_dec * hq * n_splits * dim or stats.numel() < n_dec * hq * n_splits * 2:
         raise KernelError("attn_decode: scratch for partial sums is too small")
-    lib = attention_library(dim, k_cache.dtype)
+    lib = attention_library(dim, k_cache.dtype, kind)
     _check(lib.cisr_attn_decode(_p(q), _p(out), _p(k_cache), _p(v_cache), _p(req_slot), _p(block_table), block_table.shape[1],
                                 _p(dec_req), n_dec, _p(q_start), _p(ctx_len), _p(partial), _p(stats), hq, hkv, page_size,
                                 ctypes.c_float(scale), int(window or 0), split_size, n_splits, _stream()), "attn_decode", own=2)

@@ -112,7 +112,7 @@ def paged(k_dense, v_dense, page_size, n_pages, seed, dtype):
     return kc, vc, perm.astype(np.int32)
 
 
-def run_attention(q_all, k_all, v_all, q_lens, page_size, dtype, window=None, split_size=None, seed=0, width=64):
+def run_attention(q_all, k_all, v_all, q_lens, page_size, dtype, window=None, split_size=None, seed=0, width=64, kind="auto"):
     """Requests given as whole sequences; the last q_lens[r] positions of each are this step's queries."""
     k = kernels()
     R = len(q_all)
@@ -145,7 +145,7 @@ def run_attention(q_all, k_all, v_all, q_lens, page_size, dtype, window=None, sp
                 tile_req.append(r); tile_q0.append(q0)
     i32 = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32), device=dev())
     out = torch.full((total, hq, d), float("nan"), dtype=dtype, device=dev())
-    args = dict(hq=hq, hkv=hkv, page_size=page_size, scale=d ** -0.5, window=window)
+    args = dict(hq=hq, hkv=hkv, page_size=page_size, scale=d ** -0.5, window=window, kind=kind)
     kcd, vcd, qd = kc.to(dev()), vc.to(dev()), q.to(dev()).contiguous()
     req_slot = i32(np.arange(1, R + 1)); tab = i32(table)
     if tile_req:
@@ -173,13 +173,14 @@ def random_qkv(t, hq, hkv, d, seed, sharp=1.0):
 ATT_TOL = {torch.float32: (3e-6, 1e-5), torch.bfloat16: (2e-2, 2e-2)}
 
 
-@pytest.mark.parametrize("d,hq,hkv", [(64, 9, 3), (128, 4, 4), (48, 5, 1), (16, 2, 2)])
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_attention_mixed_portions_and_decode(d, hq, hkv, dtype):
-    """Whole prompts, portions with earlier context, and single tokens in one launch pair; pages of 8 in shuffled order."""
+@pytest.mark.parametrize("d,hq,hkv", [(64, 9, 3), (128, 4, 4), (48, 5, 1), (16, 2, 2), (32, 40, 2), (144, 2, 1)])
+@pytest.mark.parametrize("dtype,kind", [(torch.float32, "auto"), (torch.bfloat16, "auto"), (torch.bfloat16, "simt")])
+def test_attention_mixed_portions_and_decode(d, hq, hkv, dtype, kind):
+    """Whole prompts, portions with earlier context, and single tokens in one launch pair; pages of 8 in shuffled order.
+    bfloat16 runs on the tensor cores ("auto", heads up to 128 wide) and on the CUDA cores ("simt")."""
     lens, q_lens = [200, 77, 130, 1, 301, 65], [200, 13, 1, 1, 1, 2]
     data = [random_qkv(t, hq, hkv, d, 10 * d + i, sharp=2.0) for i, t in enumerate(lens)]
-    out, ref = run_attention([x[0] for x in data], [x[1] for x in data], [x[2] for x in data], q_lens, 8, dtype, seed=d)
+    out, ref = run_attention([x[0] for x in data], [x[1] for x in data], [x[2] for x in data], q_lens, 8, dtype, seed=d, kind=kind)
     assert torch.isfinite(out).all()
     close(out, ref, *ATT_TOL[dtype], "attention")
 
