@@ -35,6 +35,7 @@ constexpr int LDS = D + 8;      // shared-memory row stride in elements: ldmatri
 constexpr int CHUNKS = D / 8;   // 16-byte chunks per row
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
+bool g_pdl = false;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -246,6 +247,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
     bf16* pipe = Qs + 16 * LDS;                                      // [STAGES][K tile | V tile]
     float* merge = reinterpret_cast<float*>(pipe);                   // reused after the loop: [4][16][D + 2]
 
+    pdl_trigger();
+    pdl_wait();      // the keys and values of this step's token were written by the kernel before
     const int group = hq / hkv;
     const int rows = min(16, group - row0);                          // query heads of the group handled by this launch
     const int slot = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -396,6 +399,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
 __global__ void attn_merge_kernel(const float* __restrict__ partial, const float* __restrict__ stats,
                                   bf16* __restrict__ out, const int* __restrict__ dec_req,
                                   const int* __restrict__ q_start, int hq, int n_splits) {
+    pdl_trigger();
+    pdl_wait();
     const int slot = blockIdx.x, head = blockIdx.y;
     const size_t base = ((size_t)slot * hq + head) * n_splits;
     float m = -INFINITY;
@@ -418,6 +423,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ partial, const float
 }  // namespace
 
 CISR_EXPORT int cisr_attn_head_dim() { return D; }
+CISR_EXPORT void cisr_attn_set_pdl(int on) { g_pdl = on != 0; }
 CISR_EXPORT int cisr_attn_storage_bf16() { return 1; }
 CISR_EXPORT int cisr_attn_prefill_tile() { return BM; }
 
@@ -456,12 +462,12 @@ CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, 
     cudaStream_t s = (cudaStream_t)stream;
     const int group = hq / hkv;
     for (int row0 = 0; row0 < group; row0 += 16) {     // groups wider than one 16-row tile take several launches
-        attn_decode_mma_kernel<<<dim3(n_dec, hkv, n_splits), DEC_THREADS, DEC_SMEM, s>>>(
-            (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, req_slot, block_table, table_width, dec_req,
-            q_start, ctx_len, partial, stats, hq, hkv, page_size, scale, window, split_size, n_splits, row0);
-        int status = launch_status();
+        int status = launch_kernel(attn_decode_mma_kernel, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), DEC_SMEM, s, g_pdl,
+                                   (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, req_slot, block_table,
+                                   table_width, dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale,
+                                   window, split_size, n_splits, row0);
         if (status) return status;
     }
-    attn_merge_kernel<<<dim3(n_dec, hq), D < 128 ? 64 : 128, 0, s>>>(partial, stats, (bf16*)out, dec_req, q_start, hq, n_splits);
-    return launch_status();
+    return launch_kernel(attn_merge_kernel, dim3(n_dec, hq), dim3(D < 128 ? 64 : 128), 0, s, g_pdl, (const float*)partial,
+                         (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_splits);
 }

@@ -45,3 +45,28 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch.  A kernel launched with the attribute may start while the kernel before it
+// in the stream is still running; it must call pdl_wait() before it touches anything an earlier kernel wrote,
+// and may do work that depends on nothing earlier (fetching weights) before that.  pdl_trigger() lets the
+// kernel after this one start.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Whether launches carry the attribute: switched by the host (cisr_set_pdl in each library).
+template <typename... KernelArgs, typename... Args>
+static inline int launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                bool pdl, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
+    return e == cudaSuccess ? (int)cudaGetLastError() : (int)e;
+}

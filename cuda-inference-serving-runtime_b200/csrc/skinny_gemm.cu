@@ -1,0 +1,307 @@
+// Weight-streaming matrix products for steps with few tokens (decode): out[M, N] = a[M, K] * w[N, K]^T
+// with M <= 64, bfloat16 operands, float accumulation on the tensor cores, fused with what
+// surrounds the product so that a decode layer is five launches instead of ten:
+//
+//   prologue  ACT   : a is bfloat16 [M, K] in global memory
+//             NORM  : a = rmsnorm(x + delta) * norm_w, computed by every CTA in shared memory; CTA 0 also
+//                     writes the residual sum to x_out (a different buffer than x, so no CTA reads what
+//                     another has overwritten).  `rows`, when given, picks the rows of x (final norm).
+//   epilogue  PLAIN : out float [M, N]
+//             SWIGLU: w stacks gate rows [0, I) over up rows [I, 2I); out bfloat16 [M, I] = silu(g) * u
+//             ROPE  : w stacks q, k and v heads; each CTA owns one head, rotates it (q and k) and writes q to
+//                     q_out [M, Hq, D] and k, v into their cache pages (as elementwise.cu's rope_store does)
+//
+// The weight matrix is the A operand of mma.sync.m16n8k16 (16 output features by 16 k), the tokens are the
+// 8-wide N dimension, so every weight element is read from global memory exactly once, straight into
+// registers with 16-byte loads: lane (r = lane / 4, t = lane % 4) loads w[f0 + r][32c + 8t .. 8t + 7] and
+// w[f0 + r + 8][same]; the two mma of a 32-wide chunk take k = 8t + 4j + {0,1} and 8t + 4j + {2,3}
+// (j = 0, 1) as their "columns 2t + {0,1}" and "8 + 2t + {0,1}", and the token operand is read from shared
+// memory with the same k permutation, so the sum over k is unchanged.
+//
+// A CTA is RT row tiles (16 features each) by KS splits of K, one warp each.  A warp first issues the loads
+// of its first MAXC chunks of weights (they depend on no earlier kernel), then waits for the kernel before it
+// (programmatic dependent launch), stages the tokens, multiplies, and the KS partial sums of a row tile are
+// added in shared memory in a fixed order.
+//
+// Parity: these products are what runtime/blas.py:41-56 of the reference hands to cuBLAS with M = batch;
+// the fused neighbours are kernels/execution.cu:12-24 (residual + norm), :7-10 (SwiGLU), :28-40 (rotation
+// and cache write).  K must be a multiple of 8 (16-byte rows).
+#include "common.cuh"
+
+namespace {
+typedef __nv_bfloat16 bf16;
+enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ROPE = 2 };
+constexpr int MAXC = 6;     // chunks of 32 k whose weights a warp holds in registers at once
+bool g_pdl = false;
+
+struct SkinnyArgs {
+    const bf16* w; int n; int k;
+    const bf16* act;                               // ACT prologue
+    const float* x; const float* delta; const void* norm_w; int norm_w_bf16; float eps; float* x_out; const int* rows;
+    int m; int rt; int ks;
+    float* out_f32; bf16* out_bf16; int inter;      // PLAIN / SWIGLU
+    // ROPE
+    const float* cos_t; const float* sin_t; int rot_half; int interleaved; bf16* q_out; bf16* k_cache; bf16* v_cache;
+    const int* positions; const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size;
+    int hq; int hkv; int dim;
+};
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 load_weights(const bf16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// The token operand in shared memory: hs[MT * 8][ldh] bfloat16, rows >= m zero.  All warps take part.
+template <int MT>
+__device__ void stage_tokens(const SkinnyArgs& a, bf16* hs, int ldh) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    const int k = a.k, k8 = k / 8;
+    if (a.act) {
+        for (int e = tid; e < MT * 8 * k8; e += blockDim.x) {
+            const int r = e / k8, c = (e - r * k8) * 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < a.m) v = *reinterpret_cast<const uint4*>(a.act + (size_t)r * k + c);
+            *reinterpret_cast<uint4*>(hs + r * ldh + c) = v;
+        }
+        return;
+    }
+    const int k4 = k / 4;
+    for (int r = warp; r < MT * 8; r += nwarp) {
+        bf16* dst = hs + r * ldh;
+        if (r >= a.m) {
+            for (int c = lane; c < k8; c += 32) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        const size_t src = (size_t)(a.rows ? a.rows[r] : r) * k;
+        const float4* xr = reinterpret_cast<const float4*>(a.x + src);
+        const float4* dr = a.delta ? reinterpret_cast<const float4*>(a.delta + src) : nullptr;
+        float sq = 0.f;
+#pragma unroll 4
+        for (int c = lane; c < k4; c += 32) {
+            float4 v = xr[c];
+            if (dr) { const float4 d = dr[c]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+            sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        sq = warp_sum(sq);
+        const float scale = rsqrtf(sq / (float)k + a.eps);
+        const bool write_x = a.x_out && blockIdx.x == 0;
+#pragma unroll 4
+        for (int c = lane; c < k4; c += 32) {
+            float4 v = xr[c];
+            if (dr) { const float4 d = dr[c]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+            if (write_x) reinterpret_cast<float4*>(a.x_out + src)[c] = v;
+            float w0, w1, w2, w3;
+            if (a.norm_w_bf16) {
+                const bf16* wp = (const bf16*)a.norm_w + 4 * c;
+                w0 = __bfloat162float(wp[0]); w1 = __bfloat162float(wp[1]); w2 = __bfloat162float(wp[2]); w3 = __bfloat162float(wp[3]);
+            } else {
+                const float4 wv = reinterpret_cast<const float4*>(a.norm_w)[c];
+                w0 = wv.x; w1 = wv.y; w2 = wv.z; w3 = wv.w;
+            }
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * scale * w0, v.y * scale * w1);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * scale * w2, v.w * scale * w3);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&lo); packed.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(dst + 4 * c) = packed;
+        }
+    }
+}
+
+template <int MT, int EPI>
+__global__ void __launch_bounds__(512) skinny_kernel(const SkinnyArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int ldh = a.k + 8;
+    bf16* hs = reinterpret_cast<bf16*>(smem_raw);
+    float* red = reinterpret_cast<float*>(hs + MT * 8 * ldh);   // [KS][RT * 16][MT * 8]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, t = lane & 3;
+    const int RT = a.rt, KS = a.ks;
+    const int rt = warp % RT, ks = warp / RT;
+    const int k = a.k, chunks = (k + 31) / 32;
+
+    int f_lo, f_hi, n_lo;
+    if (EPI == EPI_SWIGLU) { f_lo = blockIdx.x * 8; f_hi = a.inter + blockIdx.x * 8; n_lo = a.inter; }   // rows 0-7 gate, 8-15 up
+    else if (EPI == EPI_ROPE) { f_lo = blockIdx.x * a.dim + rt * 16; f_hi = f_lo + 8; n_lo = a.n; }
+    else { f_lo = (blockIdx.x * RT + rt) * 16; f_hi = f_lo + 8; n_lo = a.n; }
+    const bool ok_lo = f_lo + r < n_lo, ok_hi = f_hi + r < a.n;
+    const bf16* row_lo = a.w + (size_t)(ok_lo ? f_lo + r : 0) * k + 8 * t;
+    const bf16* row_hi = a.w + (size_t)(ok_hi ? f_hi + r : 0) * k + 8 * t;
+
+    // weights of the first batch of chunks: nothing here depends on an earlier kernel
+    uint4 wl[MAXC], wh[MAXC];
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+        const int c = ks + i * KS;
+        const bool in_k = c < chunks && c * 32 + 8 * t < k;
+        wl[i] = make_uint4(0, 0, 0, 0); wh[i] = make_uint4(0, 0, 0, 0);
+        if (in_k && ok_lo) wl[i] = load_weights(row_lo + c * 32);
+        if (in_k && ok_hi) wh[i] = load_weights(row_hi + c * 32);
+    }
+    pdl_trigger();
+    pdl_wait();
+
+    stage_tokens<MT>(a, hs, ldh);
+    __syncthreads();
+
+    float acc[MT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    for (int base = 0; ks + base * KS < chunks; base += MAXC) {
+        if (base) {
+#pragma unroll
+            for (int i = 0; i < MAXC; ++i) {
+                const int c = ks + (base + i) * KS;
+                const bool in_k = c < chunks && c * 32 + 8 * t < k;
+                wl[i] = make_uint4(0, 0, 0, 0); wh[i] = make_uint4(0, 0, 0, 0);
+                if (in_k && ok_lo) wl[i] = load_weights(row_lo + c * 32);
+                if (in_k && ok_hi) wh[i] = load_weights(row_hi + c * 32);
+            }
+        }
+        // Every lane runs every mma (a warp-wide instruction must never sit under a lane-dependent condition);
+        // lanes whose 8 columns lie beyond K, and chunks beyond the last, feed zeros on both sides.
+#pragma unroll
+        for (int i = 0; i < MAXC; ++i) {
+            const int c = ks + (base + i) * KS;
+            const int kb = c * 32 + 8 * t;
+            const bool in_k = c < chunks && kb < k;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                uint4 b = make_uint4(0, 0, 0, 0);
+                if (in_k) b = *reinterpret_cast<const uint4*>(hs + (mt * 8 + r) * ldh + kb);   // k = kb .. kb + 7 of token mt*8 + r
+                mma_bf16(acc[mt], wl[i].x, wh[i].x, wl[i].y, wh[i].y, b.x, b.y);
+                mma_bf16(acc[mt], wl[i].z, wh[i].z, wl[i].w, wh[i].w, b.z, b.w);
+            }
+        }
+    }
+
+    // partial sums: red[ks][rt * 16 + row][token]
+    const int rows_cta = RT * 16, mw = MT * 8;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        float* dst = red + ((size_t)ks * rows_cta + rt * 16) * mw + mt * 8 + 2 * t;
+        dst[r * mw] = acc[mt][0]; dst[r * mw + 1] = acc[mt][1];
+        dst[(r + 8) * mw] = acc[mt][2]; dst[(r + 8) * mw + 1] = acc[mt][3];
+    }
+    __syncthreads();
+
+    if (EPI == EPI_PLAIN) {
+        for (int e = tid; e < rows_cta * a.m; e += blockDim.x) {
+            const int mrow = e / rows_cta, row = e - mrow * rows_cta;
+            const int f = blockIdx.x * rows_cta + row;
+            if (f >= a.n) continue;
+            float v = 0.f;
+            for (int q = 0; q < KS; ++q) v += red[((size_t)q * rows_cta + row) * mw + mrow];
+            a.out_f32[(size_t)mrow * a.n + f] = v;
+        }
+    } else if (EPI == EPI_SWIGLU) {
+        for (int e = tid; e < 8 * a.m; e += blockDim.x) {
+            const int mrow = e / 8, row = e - mrow * 8;
+            const int f = blockIdx.x * 8 + row;
+            if (f >= a.inter) continue;
+            float g = 0.f, u = 0.f;
+            for (int q = 0; q < KS; ++q) {
+                g += red[((size_t)q * 16 + row) * mw + mrow];
+                u += red[((size_t)q * 16 + row + 8) * mw + mrow];
+            }
+            a.out_bf16[(size_t)mrow * a.inter + f] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+        }
+    } else {
+        const int dim = a.dim, hh = blockIdx.x;
+        for (int e = tid; e < dim * a.m; e += blockDim.x) {     // first the sum over the K splits, in place in split 0
+            const int mrow = e / dim, row = e - mrow * dim;
+            float v = 0.f;
+            for (int q = 0; q < KS; ++q) v += red[((size_t)q * rows_cta + row) * mw + mrow];
+            red[(size_t)row * mw + mrow] = v;
+        }
+        __syncthreads();
+        const bool is_q = hh < a.hq, is_k = !is_q && hh < a.hq + a.hkv;
+        const int rot = 2 * a.rot_half;
+        for (int e = tid; e < a.m * dim; e += blockDim.x) {
+            const int mrow = e / dim, d = e - mrow * dim;
+            float v = red[(size_t)d * mw + mrow];
+            if ((is_q || is_k) && d < rot) {
+                int f, other; bool first;
+                if (a.interleaved) { f = d >> 1; first = !(d & 1); other = first ? d + 1 : d - 1; }
+                else { first = d < a.rot_half; f = first ? d : d - a.rot_half; other = first ? d + a.rot_half : d - a.rot_half; }
+                const float c = a.cos_t[(size_t)mrow * a.rot_half + f], s = a.sin_t[(size_t)mrow * a.rot_half + f];
+                const float o = red[(size_t)other * mw + mrow];
+                v = first ? v * c - o * s : v * c + o * s;
+            }
+            if (is_q) {
+                a.q_out[((size_t)mrow * a.hq + hh) * dim + d] = __float2bfloat16_rn(v);
+            } else {
+                const int pos = a.positions[mrow];
+                const int page = a.block_table[(size_t)a.req_slot[a.token_req[mrow]] * a.table_width + pos / a.page_size];
+                if (page < 0) continue;      // a padding row: its slot holds no pages
+                const int kvh = is_k ? hh - a.hq : hh - a.hq - a.hkv;
+                const size_t dst = (((size_t)page * a.hkv + kvh) * a.page_size + pos % a.page_size) * dim + d;
+                (is_k ? a.k_cache : a.v_cache)[dst] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+template <int MT, int EPI>
+int launch_epilogue(SkinnyArgs& a, cudaStream_t s) {
+    int grid;
+    if (EPI == EPI_ROPE) { a.rt = a.dim / 16; a.ks = max(1, min(4, 16 / a.rt)); grid = a.hq + 2 * a.hkv; }   // at most 512 threads
+    else if (EPI == EPI_SWIGLU) { a.rt = 1; a.ks = 8; grid = (a.inter + 7) / 8; }
+    else if (MT <= 2) { a.rt = 1; a.ks = 8; grid = (a.n + 15) / 16; }
+    else { a.rt = 4; a.ks = 2; grid = (a.n + 63) / 64; }       // more tokens: stage them once per 64 features
+    size_t smem = sizeof(bf16) * (size_t)(MT * 8) * (a.k + 8) + sizeof(float) * (size_t)a.ks * a.rt * 16 * MT * 8;
+    if (smem > 220 * 1024 && a.ks > 1 && EPI == EPI_PLAIN) {   // long rows and many tokens: give up the K split for room
+        a.ks = 1;
+        smem = sizeof(bf16) * (size_t)(MT * 8) * (a.k + 8) + sizeof(float) * (size_t)a.rt * 16 * MT * 8;
+    }
+    if (smem > 220 * 1024) return -3;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    return launch_kernel(skinny_kernel<MT, EPI>, dim3(grid), dim3(32 * a.rt * a.ks), smem, s, g_pdl, a);
+}
+
+template <int MT>
+int launch(SkinnyArgs& a, int epilogue, cudaStream_t s) {
+    if (epilogue == EPI_ROPE) return launch_epilogue<MT, EPI_ROPE>(a, s);
+    if (epilogue == EPI_SWIGLU) return launch_epilogue<MT, EPI_SWIGLU>(a, s);
+    return launch_epilogue<MT, EPI_PLAIN>(a, s);
+}
+}  // namespace
+
+CISR_EXPORT int cisr_skinny_max_tokens() { return 64; }
+CISR_EXPORT void cisr_skinny_set_pdl(int on) { g_pdl = on != 0; }
+
+// One entry point; unused pointer groups are null.  Returns -2 for shapes it does not take (the caller then
+// uses the library product and the separate kernels).
+CISR_EXPORT int cisr_skinny_gemm(const void* w, int n, int k, const void* act, const float* x, const float* delta,
+                                 const void* norm_w, int norm_w_dtype, float eps, float* x_out, const int* rows, int m,
+                                 int epilogue, float* out_f32, void* out_bf16, int inter, const float* cos_t,
+                                 const float* sin_t, int rot_half, int interleaved, void* q_out, void* k_cache,
+                                 void* v_cache, const int* positions, const int* token_req, const int* req_slot,
+                                 const int* block_table, int table_width, int page_size, int hq, int hkv, int dim,
+                                 void* stream) {
+    if (m <= 0) return 0;
+    if (m > 64 || k % 8 || k <= 0 || n <= 0) return -2;
+    if (epilogue == EPI_ROPE && (dim % 16 || dim > 256 || dim < 16 || n != (hq + 2 * hkv) * dim || 2 * rot_half > dim)) return -2;
+    if (epilogue == EPI_SWIGLU && n != 2 * inter) return -2;
+    SkinnyArgs a;
+    a.w = (const bf16*)w; a.n = n; a.k = k; a.act = (const bf16*)act; a.x = x; a.delta = delta; a.norm_w = norm_w;
+    a.norm_w_bf16 = norm_w_dtype == CISR_BF16; a.eps = eps; a.x_out = x_out; a.rows = rows; a.m = m; a.rt = 1; a.ks = 1;
+    a.out_f32 = out_f32; a.out_bf16 = (bf16*)out_bf16; a.inter = inter; a.cos_t = cos_t; a.sin_t = sin_t;
+    a.rot_half = rot_half; a.interleaved = interleaved; a.q_out = (bf16*)q_out; a.k_cache = (bf16*)k_cache;
+    a.v_cache = (bf16*)v_cache; a.positions = positions; a.token_req = token_req; a.req_slot = req_slot;
+    a.block_table = block_table; a.table_width = table_width; a.page_size = page_size; a.hq = hq; a.hkv = hkv; a.dim = dim;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (m <= 8) return launch<1>(a, epilogue, s);
+    if (m <= 16) return launch<2>(a, epilogue, s);
+    if (m <= 32) return launch<4>(a, epilogue, s);
+    return launch<8>(a, epilogue, s);
+}

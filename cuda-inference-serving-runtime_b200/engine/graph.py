@@ -16,6 +16,7 @@ steps can run back to back without the host (`run_ahead`).
 """
 from __future__ import annotations
 
+import os
 from collections import OrderedDict
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -135,8 +136,13 @@ class DecodeGraph:
         torch.cuda.synchronize()
         before = dict(kernels.LAUNCHES)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self._run(advance=True)
+        pdl = os.environ.get("CISR_PDL", "1") != "0"
+        kernels.set_pdl(pdl)        # inside the graph a kernel may fetch its weights while the one before it still runs
+        try:
+            with torch.cuda.graph(self.graph):
+                self._run(advance=True)
+        finally:
+            kernels.set_pdl(False)
         self.launches = {k: kernels.LAUNCHES[k] - before[k] for k in before}   # kernels one replay launches
 
     def replay(self) -> None:

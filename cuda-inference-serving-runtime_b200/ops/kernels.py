@@ -198,6 +198,8 @@ def attention_library(head_dim: int, dtype: torch.dtype, kind: str = "auto"):
         for name in ("cisr_attn_prefill", "cisr_attn_decode", "cisr_attn_head_dim", "cisr_attn_prefill_tile"):
             getattr(lib, name).restype = ctypes.c_int
         assert lib.cisr_attn_head_dim() == head_dim
+        if source == "attention_mma.cu":
+            lib.cisr_attn_set_pdl(int(_pdl_state["on"]))
         _attention_libs[key] = lib
     return lib
 
@@ -317,3 +319,100 @@ def gemm_jobs(dtype: torch.dtype):
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[M, N] (float) = a[M, K] @ w[N, K]^T; picks the kernel for the shape and dtype."""
     return gemm_library(a, w, out)
+
+
+# ------------------------------------------------------------------ weight-streaming products for few tokens
+SKINNY_MAX_TOKENS = 16           # above this the library product is faster than streaming the weights per 16 features
+SKINNY_NORM_MAX_TOKENS = 16      # beyond this the norm runs once as its own kernel instead of in every CTA
+EPI_PLAIN, EPI_SWIGLU, EPI_ROPE = 0, 1, 2
+
+
+def _skinny():
+    lib = load_library("skinny_gemm.cu")
+    if not getattr(lib, "_typed", False):
+        lib.cisr_skinny_gemm.restype = ctypes.c_int
+        lib._typed = True
+    return lib
+
+
+def set_pdl(on: bool) -> None:
+    """Launch the decode-path kernels with programmatic dependent launch (a kernel may fetch its weights while the
+    kernel before it is still running)."""
+    _skinny().cisr_skinny_set_pdl(int(on))
+    for (source, _, _), lib in list(_attention_libs.items()):
+        if source == "attention_mma.cu":
+            lib.cisr_attn_set_pdl(int(on))
+    _pdl_state["on"] = bool(on)
+
+
+_pdl_state = {"on": False}
+
+
+def skinny_jobs():
+    return [("skinny_gemm.cu", {}, ())]
+
+
+def skinny_ok(tokens: int, w: torch.Tensor) -> bool:
+    """Shapes the weight-streaming kernels take: bfloat16 weights, at most 64 tokens, K a multiple of 8."""
+    if w.dtype != torch.bfloat16 or not 0 < tokens <= SKINNY_MAX_TOKENS or w.shape[1] % 8:
+        return False
+    padded = -(-tokens // 8) * 8
+    return padded * (w.shape[1] + 8) * 2 + 64 * padded * 4 * 2 <= 200 * 1024     # the tokens and the partial sums fit in shared memory
+
+
+def skinny_gemm(w: torch.Tensor, tokens: int, *, act: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None,
+                delta: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
+                x_out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None, epilogue: int = EPI_PLAIN,
+                out: Optional[torch.Tensor] = None, rope: Optional[dict] = None) -> None:
+    """out = prologue(input) @ w^T with a fused epilogue; see csrc/skinny_gemm.cu.
+
+    Input is either `act` (bfloat16 [tokens, K]) or the norm prologue (`x`, optional `delta`, `norm_w`, `eps`,
+    optional `x_out` receiving x + delta, optional `rows` picking rows of x).  PLAIN writes float `out`
+    [tokens, N]; SWIGLU writes bfloat16 `out` [tokens, N / 2]; ROPE takes the `rope` dict (cos, sin, rot_half,
+    interleaved, q_out, k_cache, v_cache, positions, token_req, req_slot, block_table, page_size, hq, hkv, dim).
+    """
+    _need(w, torch.bfloat16, "w", 2)
+    n, k = w.shape
+    if act is not None:
+        _need(act, torch.bfloat16, "act", 2)
+        if act.shape[0] < tokens or act.shape[1] != k:
+            raise KernelError("skinny_gemm: act must be [tokens, K]")
+    else:
+        _need(x, torch.float32, "x", 2); _need(norm_w, None, "norm_w", 1)
+        if x.shape[1] != k or norm_w.numel() != k:
+            raise KernelError("skinny_gemm: x and norm_w must be K wide")
+        if delta is not None:
+            _need(delta, torch.float32, "delta", 2)
+        if x_out is not None:
+            _need(x_out, torch.float32, "x_out", 2)
+            if x_out.data_ptr() == x.data_ptr():
+                raise KernelError("skinny_gemm: x_out must be another buffer than x")
+        if rows is not None:
+            _need(rows, torch.int32, "rows", 1)
+    r = rope or {}
+    out_f32 = out if epilogue == EPI_PLAIN else None
+    out_b16 = out if epilogue == EPI_SWIGLU else None
+    if epilogue == EPI_PLAIN:
+        _need(out, torch.float32, "out", 2)
+        if out.shape[0] < tokens or out.shape[1] != n:
+            raise KernelError("skinny_gemm: out must be float [tokens, N]")
+    elif epilogue == EPI_SWIGLU:
+        _need(out, torch.bfloat16, "out", 2)
+        if out.shape[0] < tokens or out.shape[1] * 2 != n:
+            raise KernelError("skinny_gemm: out must be bfloat16 [tokens, N / 2]")
+    else:
+        for name in ("q_out", "k_cache", "v_cache"):
+            _need(r[name], torch.bfloat16, name)
+        for name in ("positions", "token_req", "req_slot", "block_table"):
+            _need(r[name], torch.int32, name)
+        if r["rot_half"]:
+            _need(r["cos"], torch.float32, "cos", 2); _need(r["sin"], torch.float32, "sin", 2)
+    status = _skinny().cisr_skinny_gemm(
+        _p(w), n, k, _p(act), _p(x), _p(delta), _p(norm_w), dtype_code(norm_w.dtype) if norm_w is not None else 0,
+        ctypes.c_float(eps), _p(x_out), _p(rows), tokens, epilogue, _p(out_f32), _p(out_b16),
+        n // 2 if epilogue == EPI_SWIGLU else 0, _p(r.get("cos")), _p(r.get("sin")), int(r.get("rot_half", 0)),
+        int(bool(r.get("interleaved", False))), _p(r.get("q_out")), _p(r.get("k_cache")), _p(r.get("v_cache")),
+        _p(r.get("positions")), _p(r.get("token_req")), _p(r.get("req_slot")), _p(r.get("block_table")),
+        r["block_table"].shape[1] if rope else 0, int(r.get("page_size", 0)), int(r.get("hq", 0)), int(r.get("hkv", 0)),
+        int(r.get("dim", 0)), _stream())
+    _check(status, "skinny_gemm")

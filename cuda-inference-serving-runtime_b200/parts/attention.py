@@ -14,7 +14,7 @@ import torch
 from ..config.spec import CacheUse
 from ..ops import kernels
 from .base import MIXERS, POSITIONS, Mixer, TensorNeed, build_part, register
-from .linear import linear
+from .linear import as_tensor, linear, norm_fusable
 
 
 @register(MIXERS, "gqa_attention")
@@ -22,6 +22,7 @@ class GQAAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, position (PartSpec), window (None or int), scale."""
 
     graph_safe = True
+    accepts_pending_norm = True
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
@@ -52,34 +53,51 @@ class GQAAttention(Mixer):
 
     def kernel_jobs(self):
         return ([("elementwise.cu", {}, ()), kernels.attention_jobs(self.dim, self.dtype)]
-                + kernels.gemm_jobs(self.dtype) + self.position.kernel_jobs())
+                + kernels.gemm_jobs(self.dtype) + self.position.kernel_jobs()
+                + (kernels.skinny_jobs() if self.dtype == torch.bfloat16 else []))
 
     def cache_use(self) -> CacheUse:
         return CacheUse("pages", kv_heads=self.hkv, head_dim=self.dim, window=self.window)
 
     def forward(self, h, ctx, cache):
-        tokens = h.shape[0]
+        tokens = ctx.n_tokens
         hq, hkv, dim = self.hq, self.hkv, self.dim
-        if cache.write:
-            proj = linear(h, self.qkv)
-            k_col, v_col = hq * dim, (hq + hkv) * dim
-        else:  # this run entry reads another entry's keys and values: queries only
-            proj = linear(h, self.qkv[: hq * dim])
-            k_col = v_col = -1
+        device = ctx.device
         rot = self.position.rotation(ctx)
-        q = torch.empty((tokens, hq, dim), dtype=self.dtype, device=h.device)
-        kernels.rope_store(proj, k_col, v_col, rot.cos if rot else None, rot.sin if rot else None,
-                           rot.rot_half if rot else 0, rot.interleaved if rot else False, q,
-                           cache.k if cache.write else None, cache.v if cache.write else None,
-                           ctx.token_req, ctx.positions, ctx.req_slot, cache.block_table, cache.page_size, hq, hkv, dim)
-        out = torch.empty((tokens, hq, dim), dtype=self.dtype, device=h.device)
+        q = torch.empty((tokens, hq, dim), dtype=self.dtype, device=device)
+        if cache.write and kernels.skinny_ok(tokens, self.qkv):
+            # few tokens: one launch computes (the norm,) the projection, the rotation and the cache write
+            rope = dict(cos=rot.cos if rot else None, sin=rot.sin if rot else None, rot_half=rot.rot_half if rot else 0,
+                        interleaved=rot.interleaved if rot else False, q_out=q, k_cache=cache.k, v_cache=cache.v,
+                        positions=ctx.positions, token_req=ctx.token_req, req_slot=ctx.req_slot,
+                        block_table=cache.block_table, page_size=cache.page_size, hq=hq, hkv=hkv, dim=dim)
+            if norm_fusable(h, tokens, self.qkv):
+                x_out = h.new_stream_buffer()
+                kernels.skinny_gemm(self.qkv, tokens, x=h.x, delta=h.delta, norm_w=h.weight, eps=h.eps, x_out=x_out,
+                                    epilogue=kernels.EPI_ROPE, rope=rope)
+                h.done(x_out)
+            else:
+                kernels.skinny_gemm(self.qkv, tokens, act=as_tensor(h), epilogue=kernels.EPI_ROPE, rope=rope)
+        else:
+            h = as_tensor(h)
+            if cache.write:
+                proj = linear(h, self.qkv)
+                k_col, v_col = hq * dim, (hq + hkv) * dim
+            else:  # this run entry reads another entry's keys and values: queries only
+                proj = linear(h, self.qkv[: hq * dim])
+                k_col = v_col = -1
+            kernels.rope_store(proj, k_col, v_col, rot.cos if rot else None, rot.sin if rot else None,
+                               rot.rot_half if rot else 0, rot.interleaved if rot else False, q,
+                               cache.k if cache.write else None, cache.v if cache.write else None,
+                               ctx.token_req, ctx.positions, ctx.req_slot, cache.block_table, cache.page_size, hq, hkv, dim)
+        out = torch.empty((tokens, hq, dim), dtype=self.dtype, device=device)
         if ctx.n_tiles:
             kernels.attn_prefill(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, ctx.tile_req, ctx.tile_q0, ctx.q_start,
                                  ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, self.scale, self.window)
         if ctx.n_decode:
             split_size, n_splits = ctx.decode_splits(hkv)
-            partial = torch.empty((ctx.n_decode, hq, n_splits, dim), dtype=torch.float32, device=h.device)
-            stats = torch.empty((ctx.n_decode, hq, n_splits, 2), dtype=torch.float32, device=h.device)
+            partial = torch.empty((ctx.n_decode, hq, n_splits, dim), dtype=torch.float32, device=device)
+            stats = torch.empty((ctx.n_decode, hq, n_splits, 2), dtype=torch.float32, device=device)
             kernels.attn_decode(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, ctx.dec_req, ctx.n_decode, ctx.q_start,
                                 ctx.ctx_len, partial, stats, hq, hkv, cache.page_size, self.scale, self.window,
                                 split_size, n_splits)

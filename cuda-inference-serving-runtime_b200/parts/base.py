@@ -49,6 +49,44 @@ class Part:
         return []
 
 
+class PendingNorm:
+    """The input of a mixer or feed-forward that has not been normed yet: norm(x + pending).
+
+    A part that can fuse the residual add and the norm into its first product (`accepts_pending_norm = True`)
+    asks `fusable(tokens)`; if so it reads `x`, `delta`, `weight`, `eps`, runs its fused kernel with a fresh
+    `x_out` buffer from `new_stream_buffer()`, and calls `done(x_out)`.  Otherwise it calls `materialize()`
+    and gets the normed tensor from the norm's own kernel.
+    """
+
+    def __init__(self, stream, norm: "Norm", dtype: torch.dtype):
+        self.stream, self.norm, self.dtype = stream, norm, dtype
+        self.x = stream.x
+        self.delta = stream.pending
+
+    def fusable(self) -> bool:
+        return getattr(self.norm, "fusable_into_product", False)
+
+    @property
+    def weight(self) -> torch.Tensor:
+        return self.norm.weight
+
+    @property
+    def eps(self) -> float:
+        return self.norm.eps
+
+    def new_stream_buffer(self) -> Optional[torch.Tensor]:
+        """Where x + delta goes; None when nothing is pending (x stays as it is)."""
+        return None if self.delta is None else torch.empty_like(self.x)
+
+    def done(self, x_out: Optional[torch.Tensor]) -> None:
+        self.stream.take_pending()
+        if x_out is not None:
+            self.stream.x = x_out
+
+    def materialize(self) -> torch.Tensor:
+        return self.norm.forward(self.stream.x, self.stream.take_pending(), self.dtype)
+
+
 class Norm(Part):
     def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None, write_back: bool = True) -> torch.Tensor:
@@ -71,6 +109,8 @@ class Rotation:
 
 
 class Mixer(Part):
+    # True when `forward` takes a `PendingNorm` in place of the normed tensor (and may fuse the norm into its product).
+    accepts_pending_norm = False
     # True when `forward` reads the step only through device tensors of the context (never `ctx.host`), so that
     # a captured CUDA graph of it stays right when replayed with other requests, positions and lengths.
     graph_safe = False
@@ -84,6 +124,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_pending_norm = False
+
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
 

@@ -11,7 +11,7 @@ from typing import Optional
 import torch
 
 from ..config.spec import LayerSpec
-from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, build_part, register
+from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, PendingNorm, build_part, register
 
 
 class ResidualStream:
@@ -42,7 +42,8 @@ class PreNormBlock:
         return {slot: getattr(self, slot) for slot in self.slots}
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
-        h = self.mixer_norm.forward(stream.x, stream.take_pending(), self.dtype)
-        mixed = self.mixer.forward(h, ctx, cache)
-        h = self.feed_forward_norm.forward(stream.x, mixed, self.dtype)
-        stream.pending = self.feed_forward.forward(h, ctx)
+        h = PendingNorm(stream, self.mixer_norm, self.dtype)
+        mixed = self.mixer.forward(h if self.mixer.accepts_pending_norm else h.materialize(), ctx, cache)
+        stream.pending = mixed
+        h = PendingNorm(stream, self.feed_forward_norm, self.dtype)
+        stream.pending = self.feed_forward.forward(h if self.feed_forward.accepts_pending_norm else h.materialize(), ctx)

@@ -57,7 +57,7 @@ class LinearHead(Head):
         self.weight = tensors["weight"]
 
     def kernel_jobs(self):
-        return kernels.gemm_jobs(self.dtype)
+        return kernels.gemm_jobs(self.dtype) + (kernels.skinny_jobs() if self.dtype == torch.bfloat16 else [])
 
     def forward(self, h):
         return linear(h, self.weight)

@@ -11,12 +11,14 @@ import torch
 
 from ..ops import kernels
 from .base import FEED_FORWARDS, FeedForward, TensorNeed, register
-from .linear import linear
+from .linear import as_tensor, linear, norm_fusable
 
 
 @register(FEED_FORWARDS, "swiglu")
 class SwiGLU(FeedForward):
     """params: hidden_size, intermediate_size."""
+
+    accepts_pending_norm = True
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
@@ -35,10 +37,22 @@ class SwiGLU(FeedForward):
         self.down = tensors["down_proj.weight"].contiguous()
 
     def kernel_jobs(self):
-        return [("elementwise.cu", {}, ())] + kernels.gemm_jobs(self.dtype)
+        return ([("elementwise.cu", {}, ())] + kernels.gemm_jobs(self.dtype)
+                + (kernels.skinny_jobs() if self.dtype == torch.bfloat16 else []))
 
     def forward(self, h, ctx):
-        gate_up = linear(h, self.gate_up)
-        act = torch.empty((h.shape[0], self.inter), dtype=self.dtype, device=h.device)
-        kernels.swiglu(gate_up, act)
+        tokens = h.x.shape[0] if not isinstance(h, torch.Tensor) else h.shape[0]
+        device = h.x.device if not isinstance(h, torch.Tensor) else h.device
+        act = torch.empty((tokens, self.inter), dtype=self.dtype, device=device)
+        if kernels.skinny_ok(tokens, self.gate_up):
+            # few tokens: (norm,) gate and up products and the activation in one launch
+            if norm_fusable(h, tokens, self.gate_up):
+                x_out = h.new_stream_buffer()
+                kernels.skinny_gemm(self.gate_up, tokens, x=h.x, delta=h.delta, norm_w=h.weight, eps=h.eps, x_out=x_out,
+                                    epilogue=kernels.EPI_SWIGLU, out=act)
+                h.done(x_out)
+            else:
+                kernels.skinny_gemm(self.gate_up, tokens, act=as_tensor(h), epilogue=kernels.EPI_SWIGLU, out=act)
+        else:
+            kernels.swiglu(linear(as_tensor(h), self.gate_up), act)
         return linear(act, self.down)

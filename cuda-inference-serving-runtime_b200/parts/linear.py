@@ -12,7 +12,23 @@ from ..ops import kernels
 
 
 def linear(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """Few tokens (a decode step): the weight-streaming kernel; otherwise the library product."""
     out = torch.empty((a.shape[0], w.shape[0]), dtype=torch.float32, device=a.device)
     if a.shape[0] == 0:
         return out
+    if kernels.skinny_ok(a.shape[0], w) and a.dtype == torch.bfloat16:
+        kernels.skinny_gemm(w, a.shape[0], act=a, epilogue=kernels.EPI_PLAIN, out=out)
+        return out
     return kernels.gemm(a, w, out)
+
+
+def norm_fusable(h, tokens: int, w: torch.Tensor) -> bool:
+    """Whether `h` is a pending norm that this product can compute in its own prologue."""
+    from .base import PendingNorm
+    return (isinstance(h, PendingNorm) and h.fusable() and tokens <= kernels.SKINNY_NORM_MAX_TOKENS
+            and kernels.skinny_ok(tokens, w))
+
+
+def as_tensor(h) -> torch.Tensor:
+    from .base import PendingNorm
+    return h.materialize() if isinstance(h, PendingNorm) else h

@@ -17,6 +17,8 @@ from .base import NORMS, Norm, TensorNeed, register
 class RMSNorm(Norm):
     """params: size (width), eps."""
 
+    fusable_into_product = True     # y = x * rsqrt(mean(x^2) + eps) * w is what the products' norm prologue computes
+
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         self.size = int(spec["size"])

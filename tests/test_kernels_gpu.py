@@ -348,3 +348,89 @@ def test_unsupported_head_size_is_refused_clearly():
         k.attention_library(40, torch.float32)
     with pytest.raises(k.KernelError, match="multiples of 16"):
         k.attention_library(272, torch.bfloat16)
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("n,kk", [(100, 64), (576, 576), (49, 1536), (960, 240), (3000, 72)])
+def test_skinny_gemm_plain(m, n, kk):
+    """The weight-streaming product against a float64 product, from activations and from the fused norm."""
+    k = kernels()
+    g = torch.Generator().manual_seed(m * n + kk)
+    w = (0.1 * torch.randn(n, kk, generator=g)).to(torch.bfloat16)
+    a = torch.randn(m, kk, generator=g).to(torch.bfloat16)
+    out = torch.full((m, n), float("nan"), device=dev())
+    k.skinny_gemm(w.to(dev()), m, act=a.to(dev()), epilogue=k.EPI_PLAIN, out=out)
+    close(out, a.double() @ w.double().T, 2e-5 * math.sqrt(kk), 1e-5, "skinny plain")
+    if m <= k.SKINNY_NORM_MAX_TOKENS:
+        x = torch.randn(m + 3, kk, generator=g) * 2
+        delta = torch.randn(m + 3, kk, generator=g)
+        nw = 1 + 0.1 * torch.randn(kk, generator=g)
+        rows = torch.randperm(m + 3, generator=g)[:m].to(torch.int32)
+        out2 = torch.full((m, n), float("nan"), device=dev())
+        k.skinny_gemm(w.to(dev()), m, x=x.to(dev()), delta=delta.to(dev()), norm_w=nw.to(dev()), eps=1e-5, rows=rows.to(dev()),
+                      epilogue=k.EPI_PLAIN, out=out2)
+        h = pl.rms_norm((x + delta).double()[rows.long()], nw.double(), 1e-5).to(torch.bfloat16).double()
+        close(out2, h @ w.double().T, 2e-2, 2e-2, "skinny plain with norm prologue")
+
+
+@pytest.mark.parametrize("m", [1, 7, 16, 40])
+@pytest.mark.parametrize("inter,kk", [(176, 64), (1536, 576), (250, 96), (13, 40)])
+def test_skinny_gemm_swiglu_and_residual_output(m, inter, kk):
+    k = kernels()
+    g = torch.Generator().manual_seed(m + inter)
+    w = (0.2 * torch.randn(2 * inter, kk, generator=g)).to(torch.bfloat16)
+    x = torch.randn(m, kk, generator=g)
+    delta = torch.randn(m, kk, generator=g)
+    nw = (1 + 0.1 * torch.randn(kk, generator=g)).to(torch.bfloat16)
+    act = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=dev())
+    h = pl.rms_norm((x + delta).double(), nw.double(), 2e-6).to(torch.bfloat16)
+    if m <= k.SKINNY_NORM_MAX_TOKENS:
+        x_out = torch.full_like(x, float("nan")).to(dev())
+        xd = x.to(dev())
+        k.skinny_gemm(w.to(dev()), m, x=xd, delta=delta.to(dev()), norm_w=nw.to(dev()), eps=2e-6, x_out=x_out,
+                      epilogue=k.EPI_SWIGLU, out=act)
+        close(x_out, x.double() + delta.double(), 1e-6, 1e-6, "residual sum written by CTA 0")
+        assert torch.equal(xd.cpu(), x)                                   # the input stream is not touched
+    else:
+        k.skinny_gemm(w.to(dev()), m, act=h.to(dev()), epilogue=k.EPI_SWIGLU, out=act)
+    gu = h.double() @ w.double().T
+    ref = gu[:, :inter] / (1 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
+    close(act, ref, 2e-2, 2e-2, "skinny swiglu")
+
+
+@pytest.mark.parametrize("m", [1, 8, 11, 30])
+@pytest.mark.parametrize("dim,hq,hkv,rot,interleaved", [(64, 9, 3, 64, False), (16, 2, 2, 16, False), (48, 5, 1, 32, True), (128, 2, 1, 128, False)])
+def test_skinny_gemm_rope_matches_the_separate_kernels(m, dim, hq, hkv, rot, interleaved):
+    """Fused norm + q/k/v product + rotation + cache write against product -> rope_store on the same inputs."""
+    k = kernels()
+    hidden, page, theta = 96, 4, 10000.0
+    g = torch.Generator().manual_seed(m * dim)
+    w = (0.2 * torch.randn((hq + 2 * hkv) * dim, hidden, generator=g)).to(torch.bfloat16).to(dev())
+    hbf = torch.randn(m, hidden, generator=g).to(torch.bfloat16).to(dev())
+    positions = torch.randperm(40, generator=g)[:m].to(torch.int32).to(dev())
+    token_req = (torch.arange(m) % 3).to(torch.int32).to(dev())
+    req_slot = torch.tensor([2, 0, 1], dtype=torch.int32, device=dev())
+    table = torch.arange(36, dtype=torch.int32).reshape(3, 12).to(dev())          # every (slot, logical page) its own page
+    half = rot // 2
+    inv = (theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / rot)).to(dev())
+    cos = torch.empty(m, half, device=dev()); sin = torch.empty(m, half, device=dev())
+    k.rotary_tables(positions, inv, cos, sin)
+    results = []
+    for fused in (False, True):
+        q = torch.zeros(m, hq, dim, dtype=torch.bfloat16, device=dev())
+        kc = torch.zeros(36, hkv, page, dim, dtype=torch.bfloat16, device=dev()); vc = torch.zeros_like(kc)
+        if fused:
+            k.skinny_gemm(w, m, act=hbf, epilogue=k.EPI_ROPE,
+                          rope=dict(cos=cos, sin=sin, rot_half=half, interleaved=interleaved, q_out=q, k_cache=kc, v_cache=vc,
+                                    positions=positions, token_req=token_req, req_slot=req_slot, block_table=table, page_size=page,
+                                    hq=hq, hkv=hkv, dim=dim))
+        else:
+            proj = torch.empty(m, w.shape[0], device=dev())
+            k.gemm_library(hbf, w, proj)
+            k.rope_store(proj, hq * dim, (hq + hkv) * dim, cos, sin, half, interleaved, q, kc, vc, token_req, positions, req_slot,
+                         table, page, hq, hkv, dim)
+        results.append((q.float().cpu(), kc.float().cpu(), vc.float().cpu()))
+    for a, b, what in zip(results[0], results[1], ("q", "k cache", "v cache")):
+        assert float(b.abs().sum()) > 0
+        torch.testing.assert_close(b, a, atol=2e-2, rtol=2e-2, msg=lambda s: f"{what}: {s}")
+        assert torch.equal(b == 0, a == 0) or what == "q"                          # the same cache places were written
