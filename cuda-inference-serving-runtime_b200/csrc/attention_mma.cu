@@ -65,15 +65,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Gather `rows` key (or value) rows starting at position k0 into a [BN][LDS] tile; rows at or beyond `limit`
-// and rows whose page entry is -1 (a page the window has passed) are zero-filled.
+// and rows whose page entry is -1 (a page the window has passed) are zero-filled.  `pages` holds the block
+// table entries of the CTA's key range in shared memory, entry 0 being logical page `first_page`: looking a
+// page up there costs nothing, while a lookup in global memory would sit in front of every copy.
 template <int THREADS>
 __device__ __forceinline__ void load_kv_tile(bf16* Kt, bf16* Vt, const bf16* __restrict__ k_cache,
-                                             const bf16* __restrict__ v_cache, const int* __restrict__ table, int k0,
+                                             const bf16* __restrict__ v_cache, const int* pages, int first_page, int k0,
                                              int limit, int hkv, int kvh, int page_size, int tid) {
     for (int c = tid; c < BN * CHUNKS; c += THREADS) {
         const int r = c / CHUNKS, ch = c - r * CHUNKS;
         const int kpos = k0 + r;
-        const int page = kpos < limit ? table[kpos / page_size] : -1;
+        const int page = kpos < limit ? pages[kpos / page_size - first_page] : -1;
         const bool ok = page >= 0;
         const size_t base = ok ? (((size_t)page * hkv + kvh) * page_size + kpos % page_size) * D + ch * 8 : 0;
         cp_async16(Kt + r * LDS + ch * 8, k_cache + base, ok);
@@ -96,6 +98,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][LDS]
     bf16* Ks = Qs + BM * LDS;                       // [2][BN][LDS]
     bf16* Vs = Ks + 2 * BN * LDS;                   // [2][BN][LDS]
+    int* pages = reinterpret_cast<int*>(Vs + 2 * BN * LDS);   // block table entries of this tile's key range
 
     const int tile = blockIdx.x, head = blockIdx.y;
     const int req = tile_req[tile], q0 = tile_q0[tile];
@@ -117,7 +120,10 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
     if (window > 0) k_first = max(0, qpos0 - window + 1);
     const int k_begin = (k_first / BN) * BN;
     const int n_tiles = (k_end - k_begin + BN - 1) / BN;
-    load_kv_tile<PREFILL_THREADS>(Ks, Vs, k_cache, v_cache, table, k_begin, ctx, hkv, kvh, page_size, tid);
+    const int first_page = k_begin / page_size;
+    for (int i = tid; i <= (k_end - 1) / page_size - first_page; i += PREFILL_THREADS) pages[i] = table[first_page + i];
+    __syncthreads();
+    load_kv_tile<PREFILL_THREADS>(Ks, Vs, k_cache, v_cache, pages, first_page, k_begin, k_end, hkv, kvh, page_size, tid);
     cp_async_commit();
 
     uint32_t qf[KD][4];
@@ -133,8 +139,8 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
         cp_async_wait<0>();
         __syncthreads();                      // tile t has landed; everyone is done with tile t-1's buffer
         if (t + 1 < n_tiles) {
-            load_kv_tile<PREFILL_THREADS>(Ks + (buf ^ 1) * BN * LDS, Vs + (buf ^ 1) * BN * LDS, k_cache, v_cache, table,
-                                          k0 + BN, ctx, hkv, kvh, page_size, tid);
+            load_kv_tile<PREFILL_THREADS>(Ks + (buf ^ 1) * BN * LDS, Vs + (buf ^ 1) * BN * LDS, k_cache, v_cache, pages,
+                                          first_page, k0 + BN, k_end, hkv, kvh, page_size, tid);   // keys from k_end on are masked for every row
         }
         cp_async_commit();
         if (t == 0) {
@@ -230,11 +236,14 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
 
 // ------------------------------------------------------------------ decode
 constexpr int DEC_THREADS = 128;
-constexpr int STAGES = 3;
+#ifndef DEC_STAGES
+#define DEC_STAGES 3
+#endif
+constexpr int STAGES = DEC_STAGES;   // key/value tiles in flight per CTA: enough bytes on the way to keep HBM busy
 constexpr size_t DEC_TILE_BYTES = sizeof(bf16) * (size_t)(2 * BN * LDS);
 constexpr size_t DEC_MERGE_BYTES = sizeof(float) * (size_t)(4 * 16 * (D + 2));
 constexpr size_t DEC_PIPE_BYTES = STAGES * DEC_TILE_BYTES > DEC_MERGE_BYTES ? STAGES * DEC_TILE_BYTES : DEC_MERGE_BYTES;
-constexpr size_t DEC_SMEM = sizeof(bf16) * (size_t)(16 * LDS) + DEC_PIPE_BYTES;
+constexpr size_t DEC_SMEM = ((sizeof(bf16) * (size_t)(16 * LDS) + DEC_PIPE_BYTES + 15) / 16) * 16;
 
 __global__ void __launch_bounds__(DEC_THREADS)
 attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
@@ -246,6 +255,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                    // [16][LDS]
     bf16* pipe = Qs + 16 * LDS;                                      // [STAGES][K tile | V tile]
     float* merge = reinterpret_cast<float*>(pipe);                   // reused after the loop: [4][16][D + 2]
+    int* pages = reinterpret_cast<int*>(smem_raw + DEC_SMEM);        // block table entries of this CTA's key range
 
     pdl_trigger();
     pdl_wait();      // the keys and values of this step's token were written by the kernel before
@@ -262,7 +272,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
     const int hi = min(lo + split_size, ctx);
     if (window > 0) lo = max(lo, ctx - window);
     const size_t part_base = ((size_t)slot * hq + (size_t)kvh * group + row0) * n_splits;
-    if (lo >= hi) {
+    if (lo >= hi) {      // nothing in this range (the same for every thread): the merge skips a zero denominator
         for (int g = tid; g < rows; g += DEC_THREADS) {
             const size_t p = part_base + (size_t)g * n_splits + split;
             stats[2 * p] = -INFINITY; stats[2 * p + 1] = 0.f;
@@ -275,11 +285,14 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
         cp_async16(Qs + r * LDS + ch * 8, q + ((size_t)tok * hq + kvh * group + row0 + (ok ? r : 0)) * D + ch * 8, ok);
     }
     const int n_tiles = (hi - lo + BN - 1) / BN;
+    const int first_page = lo / page_size;
+    for (int i = tid; i <= (hi - 1) / page_size - first_page; i += DEC_THREADS) pages[i] = table[first_page + i];
+    __syncthreads();
 #pragma unroll
     for (int st = 0; st < STAGES - 1; ++st) {
         if (st < n_tiles) {
             bf16* Kt = pipe + st * 2 * BN * LDS;
-            load_kv_tile<DEC_THREADS>(Kt, Kt + BN * LDS, k_cache, v_cache, table, lo + st * BN, hi, hkv, kvh, page_size, tid);
+            load_kv_tile<DEC_THREADS>(Kt, Kt + BN * LDS, k_cache, v_cache, pages, first_page, lo + st * BN, hi, hkv, kvh, page_size, tid);
         }
         cp_async_commit();
     }
@@ -298,7 +311,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
             const int nt = t + STAGES - 1;
             if (nt < n_tiles) {
                 bf16* Kt = pipe + (nt % STAGES) * 2 * BN * LDS;
-                load_kv_tile<DEC_THREADS>(Kt, Kt + BN * LDS, k_cache, v_cache, table, lo + nt * BN, hi, hkv, kvh, page_size, tid);
+                load_kv_tile<DEC_THREADS>(Kt, Kt + BN * LDS, k_cache, v_cache, pages, first_page, lo + nt * BN, hi, hkv, kvh, page_size, tid);
             }
             cp_async_commit();
         }
@@ -434,13 +447,15 @@ CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache,
                                   void* stream) {
     if (n_tiles <= 0) return 0;
     if (hq % hkv) return -2;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM);
+    const size_t smem = PREFILL_SMEM + sizeof(int) * ((size_t)table_width + 4);    // a tile's key range spans at most the table
+    if (smem > 220 * 1024) return -3;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured = smem;
     }
-    attn_prefill_mma_kernel<<<dim3(n_tiles, hq), PREFILL_THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(
+    attn_prefill_mma_kernel<<<dim3(n_tiles, hq), PREFILL_THREADS, smem, (cudaStream_t)stream>>>(
         (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, req_slot, block_table, table_width,
         tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window);
     return launch_status();
@@ -453,16 +468,18 @@ CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, 
                                  void* stream) {
     if (n_dec <= 0) return 0;
     if (hq % hkv || split_size <= 0 || n_splits <= 0) return -2;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM);
+    const size_t smem = DEC_SMEM + sizeof(int) * ((size_t)split_size / page_size + 4);   // + the range's block table entries
+    if (smem > 220 * 1024) return -3;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured = smem;
     }
     cudaStream_t s = (cudaStream_t)stream;
     const int group = hq / hkv;
     for (int row0 = 0; row0 < group; row0 += 16) {     // groups wider than one 16-row tile take several launches
-        int status = launch_kernel(attn_decode_mma_kernel, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), DEC_SMEM, s, g_pdl,
+        int status = launch_kernel(attn_decode_mma_kernel, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), smem, s, g_pdl,
                                    (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, req_slot, block_table,
                                    table_width, dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale,
                                    window, split_size, n_splits, row0);

@@ -198,7 +198,8 @@ def attention_library(head_dim: int, dtype: torch.dtype, kind: str = "auto"):
         for name in ("cisr_attn_prefill", "cisr_attn_decode", "cisr_attn_head_dim", "cisr_attn_prefill_tile"):
             getattr(lib, name).restype = ctypes.c_int
         assert lib.cisr_attn_head_dim() == head_dim
-        if source == "attention_mma.cu":
+        lib._tensor_core = source == "attention_mma.cu"
+        if lib._tensor_core:
             lib.cisr_attn_set_pdl(int(_pdl_state["on"]))
         _attention_libs[key] = lib
     return lib
@@ -239,9 +240,10 @@ def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec,
     if partial.numel() < n_dec * hq * n_splits * dim or stats.numel() < n_dec * hq * n_splits * 2:
         raise KernelError("attn_decode: scratch for partial sums is too small")
     lib = attention_library(dim, k_cache.dtype, kind)
-    _check(lib.cisr_attn_decode(_p(q), _p(out), _p(k_cache), _p(v_cache), _p(req_slot), _p(block_table), block_table.shape[1],
-                                _p(dec_req), n_dec, _p(q_start), _p(ctx_len), _p(partial), _p(stats), hq, hkv, page_size,
-                                ctypes.c_float(scale), int(window or 0), split_size, n_splits, _stream()), "attn_decode", own=2)
+    args = [_p(q), _p(out), _p(k_cache), _p(v_cache), _p(req_slot), _p(block_table), block_table.shape[1], _p(dec_req), n_dec,
+            _p(q_start), _p(ctx_len), _p(partial), _p(stats), hq, hkv, page_size, ctypes.c_float(scale), int(window or 0),
+            split_size, n_splits, _stream()]
+    _check(lib.cisr_attn_decode(*args), "attn_decode", own=2)
 
 
 # ------------------------------------------------------------------ sampling
