@@ -1,0 +1,243 @@
+// Matrix product on the 5th-generation tensor cores: out[M, N] (float) = a[M, K] * w[N, K]^T, bfloat16
+// operands, float accumulation in tensor memory.  Used for steps with many tokens (prompt portions).
+//
+//   * one CTA per 128 x BN output tile (BN = 128, or 64 for narrow outputs)
+//   * warp 0: one thread issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the A tile
+//     [128 rows x 64 k] and the B tile [BN rows x 64 k] into a STAGES-deep ring of shared memory, each
+//     load completing on the stage's "full" mbarrier
+//   * warp 1: allocates BN columns of tensor memory; one thread issues tcgen05.mma (kind::f16, M = 128,
+//     N = BN, K = 16, four per 64-wide k block) on shared-memory descriptors and commits each stage to its
+//     "empty" mbarrier, and the whole tile to the "accumulator ready" mbarrier
+//   * warps 2..5: read the accumulator with tcgen05.ld (32 lanes x 32 columns per warp and step) and
+//     write float rows of `out`
+//
+// Rows and columns beyond M, N or K are zero-filled by TMA on the way in and skipped on the way out, so any
+// M and N work; K must be a multiple of 8 (16-byte rows for the tensor map).  Every wait on an mbarrier
+// gives up after a bounded number of polls: the kernel then sets `*error`, skips the rest of its work,
+// frees its tensor memory and returns, and the host reports the failure.
+//
+// Parity: this is the product runtime/blas.py:41-56 of the reference hands to cuBLAS (C^T = W * X^T).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr unsigned MAX_POLLS = 1u << 20;   // a stage is ready within microseconds; this is seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Polls until the barrier's phase with the given parity has completed; false when it gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (unsigned i = 0; i < MAX_POLLS; ++i) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16) in the 128-byte
+// swizzle: 8-row groups 1024 bytes apart (stride byte offset), leading byte offset unused, descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);       // start address, 16-byte units
+    desc |= (uint64_t)1 << 16;                                  // leading byte offset (ignored for swizzled K-major)
+    desc |= (uint64_t)(1024 >> 4) << 32;                        // stride byte offset: 8 rows x 128 bytes
+    desc |= (uint64_t)1 << 46;                                  // descriptor version of this architecture
+    desc |= (uint64_t)2 << 61;                                  // 128-byte swizzle
+    return desc;
+}
+// Instruction descriptor of kind::f16: float accumulator, bfloat16 A and B, both K-major, M = 128, N = bn.
+__host__ __device__ constexpr uint32_t umma_idesc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, int STAGES>
+struct Smem {
+    static constexpr size_t A_BYTES = (size_t)BM * BK * sizeof(bf16);
+    static constexpr size_t B_BYTES = (size_t)BN * BK * sizeof(bf16);
+    static constexpr size_t TILES = STAGES * (A_BYTES + B_BYTES);
+    static constexpr size_t TOTAL = TILES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    float* __restrict__ out, int m, int n, int k, int* __restrict__ error) {
+    extern __shared__ unsigned char smem_raw[];
+    typedef Smem<BN, STAGES> S;
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024-byte aligned
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + S::TILES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const int k_blocks = (k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {    // one warp allocates the accumulator's columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_acc = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(empty_bar + s, ((kb / STAGES) & 1) ^ 1);      // the MMAs that read this stage are done
+                if (!ok) break;
+                mbar_expect_tx(full_bar + s, (uint32_t)(S::A_BYTES + S::B_BYTES));
+                tma_load_2d(tiles + s * (S::A_BYTES + S::B_BYTES), &map_a, kb * BK, m0, full_bar + s);
+                tma_load_2d(tiles + s * (S::A_BYTES + S::B_BYTES) + S::A_BYTES, &map_w, kb * BK, n0, full_bar + s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BN);
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(full_bar + s, (kb / STAGES) & 1);              // both tiles of this stage have landed
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint64_t desc_a = umma_desc(tiles + s * (S::A_BYTES + S::B_BYTES));
+                const uint64_t desc_b = umma_desc(tiles + s * (S::A_BYTES + S::B_BYTES) + S::A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk)                        // 32 bytes further along K per step
+                    umma_bf16(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kb | kk) != 0);
+                umma_commit(empty_bar + s);                                    // frees the stage when these MMAs finish
+            }
+            if (ok) umma_commit(acc_bar);                                      // the whole tile is accumulated
+        }
+    } else {
+        ok = mbar_wait(acc_bar, 0);
+        tcgen05_fence_after();
+        if (ok) {
+            const int quarter = warp & 3;                                      // the 32 lanes this warp may read
+            const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                               "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                               "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                               "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                             : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < m) {
+                    float* dst = out + (size_t)row * n + n0 + c;
+                    if (n0 + c + 32 <= n && (n & 3) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                              __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + c + j < n) dst[j] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+        }
+    }
+    if (!ok && lane == 0) atomicExch(error, 1);
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(BN) : "memory");
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled g_encode = nullptr;
+int* g_error = nullptr;          // device flag, owned by the caller (see cisr_gemm_tcgen05_init)
+
+int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(bf16)};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -20 - (int)r;
+}
+
+template <int BN, int STAGES>
+int launch(const void* a, const void* w, float* out, int m, int n, int k, cudaStream_t s) {
+    CUtensorMap map_a, map_w;
+    int status = make_map(&map_a, a, m, k, BM);
+    if (status) return status;
+    if ((status = make_map(&map_w, w, n, k, BN))) return status;
+    typedef Smem<BN, STAGES> S;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    gemm_tcgen05_kernel<BN, STAGES><<<dim3((n + BN - 1) / BN, (m + BM - 1) / BM), 192, S::TOTAL, s>>>(map_a, map_w, out, m, n, k, g_error);
+    return launch_status();
+}
+}  // namespace
+
+// `error_flag`: one zeroed int in device memory that a kernel sets when one of its waits ran out.
+CISR_EXPORT int cisr_gemm_tcgen05_init(int* error_flag) {
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query);
+        if (e != cudaSuccess || query != cudaDriverEntryPointSuccess || !fn) return -15;
+        g_encode = (EncodeTiled)fn;
+    }
+    g_error = error_flag;
+    return 0;
+}
+
+CISR_EXPORT int cisr_gemm_tcgen05(const void* a, const void* w, float* out, int m, int n, int k, void* stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (!g_encode || !g_error) return -13;
+    if (k <= 0 || k % 8) return -2;                                   // tensor-map rows must be multiples of 16 bytes
+    if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) & 15) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (n <= 64) return launch<64, 6>(a, w, out, m, n, k, s);
+    return launch<128, 5>(a, w, out, m, n, k, s);
+}

@@ -238,6 +238,9 @@ class Engine:
                     raise
                 self._preempt(self.active[-1])
         chosen = self.choose(logits, choosing) if choosing else []
+        check = getattr(self.stepper, "check_kernels", None)
+        if check is not None:
+            check()        # after the read of the chosen tokens synchronised the device
         completed = time.perf_counter()
         prefilled = decoded = 0
         for (r, n), e in zip(plan, entries):

@@ -115,6 +115,11 @@ class Stepper:
     def fork(self, source, target) -> None:
         self.cache.fork(source, target)
 
+    @staticmethod
+    def check_kernels() -> None:
+        """Raise if a kernel reported that it gave up on a bounded wait (reads a device flag: synchronises)."""
+        kernels.raise_if_kernel_gave_up()
+
     # the step ---------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry], extra: Optional[Dict[str, np.ndarray]] = None) -> torch.Tensor:
         """Float logits [number of wanted places, vocab], in the order of the entries and of their `want`."""

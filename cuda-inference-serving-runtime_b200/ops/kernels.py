@@ -315,11 +315,19 @@ def gemm_library(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.T
 
 def gemm_jobs(dtype: torch.dtype):
     """Build jobs of the libraries `gemm` may launch for operands of this dtype."""
-    return [("gemm_library.cu", {}, ("-lcublas",))]
+    jobs = [("gemm_library.cu", {}, ("-lcublas",))]
+    if dtype == torch.bfloat16:
+        jobs.append(("gemm_tcgen05.cu", {}, ()))
+    return jobs
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[M, N] (float) = a[M, K] @ w[N, K]^T; picks the kernel for the shape and dtype."""
+    """out[M, N] (float) = a[M, K] @ w[N, K]^T; picks the kernel for the shape and dtype.
+
+    bfloat16 with at least one 128-row tile of tokens: this package's tcgen05 + TMA kernel; float (true 32-bit),
+    and shapes that kernel does not take: the vendor library."""
+    if tcgen05_ok(a, w):
+        return gemm_tcgen05(a, w, out)
     return gemm_library(a, w, out)
 
 
@@ -418,3 +426,48 @@ def skinny_gemm(w: torch.Tensor, tokens: int, *, act: Optional[torch.Tensor] = N
         r["block_table"].shape[1] if rope else 0, int(r.get("page_size", 0)), int(r.get("hq", 0)), int(r.get("hkv", 0)),
         int(r.get("dim", 0)), _stream())
     _check(status, "skinny_gemm")
+
+
+# ------------------------------------------------------------------ tcgen05 + TMA matrix product
+_tcgen05_state = {}
+TCGEN05_MIN_TOKENS = 128         # below one 128-row tile the weight-streaming kernels or the library serve better
+
+
+def _tcgen05():
+    lib = _tcgen05_state.get("lib")
+    if lib is None:
+        lib = load_library("gemm_tcgen05.cu")
+        lib.cisr_gemm_tcgen05_init.restype = ctypes.c_int
+        lib.cisr_gemm_tcgen05.restype = ctypes.c_int
+        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        _check(lib.cisr_gemm_tcgen05_init(_p(flag)), "tcgen05 gemm init", own=0)
+        _tcgen05_state["lib"], _tcgen05_state["flag"] = lib, flag
+    return lib
+
+
+def tcgen05_jobs():
+    return [("gemm_tcgen05.cu", {}, ())]
+
+
+def tcgen05_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] >= TCGEN05_MIN_TOKENS
+            and a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] (float) = a[M, K] @ w[N, K]^T on tcgen05 tensor cores fed by TMA (bfloat16 operands)."""
+    _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 2); _need(out, torch.float32, "out", 2)
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n):
+        raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
+    _check(_tcgen05().cisr_gemm_tcgen05(_p(a), _p(w), _p(out), m, n, k, _stream()), "gemm_tcgen05")
+    return out
+
+
+def raise_if_kernel_gave_up() -> None:
+    """Reads the flag a kernel sets when one of its bounded waits ran out (synchronises the device)."""
+    flag = _tcgen05_state.get("flag")
+    if flag is not None and int(flag.item()) != 0:
+        flag.zero_()
+        raise KernelError("a tcgen05 matrix product gave up waiting on a barrier; its output is not valid")
