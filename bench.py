@@ -216,7 +216,7 @@ def prefill_run(model, tokens: int, seed: int, reps: int = 5, profile: bool = Fa
 
     rng = np.random.default_rng(seed + 2)
     ids = rng.integers(0, model.spec.vocab_size, size=tokens).tolist()
-    stepper = Stepper(model, n_pages=-(-tokens // 16) + 1, page_size=16, max_slots=1)
+    stepper = Stepper(model, n_pages=-(-tokens // 16) + 1, page_size=16, max_slots=1, graph=True)
     times = []
     for rep in range(reps + 3):
         stepper.create("p")

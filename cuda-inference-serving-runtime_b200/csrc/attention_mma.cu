@@ -84,9 +84,22 @@ __device__ __forceinline__ void load_kv_tile(bf16* Kt, bf16* Vt, const bf16* __r
 }
 
 // ------------------------------------------------------------------ prefill
+// NG warp groups of 4 warps share one 64-query tile: group g takes key tiles g, g + NG, ... with its own running
+// softmax and its own double buffer, and the groups are merged by log-sum-exp at the end.  A causal prompt's last
+// query tile has the longest key loop of the whole launch; splitting it over groups shortens that tail and puts
+// more warps on each SM.
 constexpr int BM = 64;
-constexpr int PREFILL_THREADS = 128;
-constexpr size_t PREFILL_SMEM = sizeof(bf16) * (size_t)(BM * LDS + 4 * BN * LDS);
+#ifndef PREFILL_GROUPS
+#define PREFILL_GROUPS (HEAD_DIM <= 64 ? 4 : 2)
+#endif
+constexpr int NG = PREFILL_GROUPS;
+constexpr int PREFILL_THREADS = 128 * NG;
+constexpr size_t PREFILL_MERGE_BYTES = sizeof(float) * (size_t)(NG - 1) * BM * (D + 2);
+constexpr size_t PREFILL_PIPE_BYTES = sizeof(bf16) * (size_t)(NG * 4 * BN * LDS);
+constexpr size_t PREFILL_SMEM = ((sizeof(bf16) * (size_t)(BM * LDS) +
+                                  (PREFILL_PIPE_BYTES > PREFILL_MERGE_BYTES ? PREFILL_PIPE_BYTES : PREFILL_MERGE_BYTES) + 15) / 16) * 16;
+
+__device__ __forceinline__ void group_sync(int group) { asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory"); }
 
 __global__ void __launch_bounds__(PREFILL_THREADS)
 attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_cache,
@@ -96,9 +109,9 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
                         const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][LDS]
-    bf16* Ks = Qs + BM * LDS;                       // [2][BN][LDS]
-    bf16* Vs = Ks + 2 * BN * LDS;                   // [2][BN][LDS]
-    int* pages = reinterpret_cast<int*>(Vs + 2 * BN * LDS);   // block table entries of this tile's key range
+    bf16* pipe = Qs + BM * LDS;                     // [NG][2][K tile | V tile]
+    float* merge = reinterpret_cast<float*>(pipe);  // reused after the loops: [NG - 1][BM][D + 2]
+    int* pages = reinterpret_cast<int*>(smem_raw + PREFILL_SMEM);   // block table entries of this tile's key range
 
     const int tile = blockIdx.x, head = blockIdx.y;
     const int req = tile_req[tile], q0 = tile_q0[tile];
@@ -108,13 +121,15 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
     const int qpos0 = ctx - q_len[req] + q0;
     const int kvh = head / (hq / hkv);
     const int* table = block_table + (size_t)req_slot[req] * table_width;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int group = tid >> 7, gtid = tid & 127, warp = gtid >> 5;     // warp: which 16 query rows, within the group
 
     for (int c = tid; c < BM * CHUNKS; c += PREFILL_THREADS) {
         const int r = c / CHUNKS, ch = c - r * CHUNKS;
         const bool ok = r < rows;
         cp_async16(Qs + r * LDS + ch * 8, q + ((size_t)(tok0 + (ok ? r : 0)) * hq + head) * D + ch * 8, ok);
     }
+    cp_async_commit();
     const int k_end = qpos0 + rows;
     int k_first = 0;
     if (window > 0) k_first = max(0, qpos0 - window + 1);
@@ -122,34 +137,38 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
     const int n_tiles = (k_end - k_begin + BN - 1) / BN;
     const int first_page = k_begin / page_size;
     for (int i = tid; i <= (k_end - 1) / page_size - first_page; i += PREFILL_THREADS) pages[i] = table[first_page + i];
-    __syncthreads();
-    load_kv_tile<PREFILL_THREADS>(Ks, Vs, k_cache, v_cache, pages, first_page, k_begin, k_end, hkv, kvh, page_size, tid);
-    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();                              // Q and the page entries are in shared memory
 
     uint32_t qf[KD][4];
+#pragma unroll
+    for (int kk = 0; kk < KD; ++kk)
+        ldmatrix_x4(qf[kk], Qs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
     float o[ND][4];
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < ND; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     const float scale2 = scale * LOG2E;
 
-    for (int t = 0; t < n_tiles; ++t) {
+    bf16* gbuf = pipe + (size_t)group * 4 * BN * LDS;      // this group's two [K tile | V tile] buffers
+    if (group < n_tiles)
+        load_kv_tile<128>(gbuf, gbuf + BN * LDS, k_cache, v_cache, pages, first_page, k_begin + group * BN, k_end, hkv, kvh,
+                          page_size, gtid);
+    cp_async_commit();
+
+    for (int t = group, it = 0; t < n_tiles; t += NG, ++it) {
         const int k0 = k_begin + t * BN;
-        const int buf = t & 1;
+        const int buf = it & 1;
         cp_async_wait<0>();
-        __syncthreads();                      // tile t has landed; everyone is done with tile t-1's buffer
-        if (t + 1 < n_tiles) {
-            load_kv_tile<PREFILL_THREADS>(Ks + (buf ^ 1) * BN * LDS, Vs + (buf ^ 1) * BN * LDS, k_cache, v_cache, pages,
-                                          first_page, k0 + BN, k_end, hkv, kvh, page_size, tid);   // keys from k_end on are masked for every row
+        group_sync(group);                    // tile t has landed; the group is done with the other buffer
+        if (t + NG < n_tiles) {
+            bf16* nb = gbuf + (buf ^ 1) * 2 * BN * LDS;
+            load_kv_tile<128>(nb, nb + BN * LDS, k_cache, v_cache, pages, first_page, k0 + NG * BN, k_end, hkv, kvh, page_size,
+                              gtid);          // keys from k_end on are masked for every row
         }
         cp_async_commit();
-        if (t == 0) {
-#pragma unroll
-            for (int kk = 0; kk < KD; ++kk)
-                ldmatrix_x4(qf[kk], Qs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
-        }
-        const bf16* Kt = Ks + buf * BN * LDS;
-        const bf16* Vt = Vs + buf * BN * LDS;
+        const bf16* Kt = gbuf + buf * 2 * BN * LDS;
+        const bf16* Vt = Kt + BN * LDS;
 
         float s[8][4];
 #pragma unroll
@@ -217,13 +236,50 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
         }
     }
     cp_async_wait<0>();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {      // whole-row denominators
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    __syncthreads();                   // every group is done with its buffers: they become the merge area
 
+    // groups 1.. hand their (output, max, denominator) to group 0 through shared memory, thread to same-placed thread
+    if (NG > 1 && group > 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float* dst = merge + ((size_t)(group - 1) * BM + warp * 16 + (lane >> 2) + 8 * h) * (D + 2);
+#pragma unroll
+            for (int i = 0; i < ND; ++i) {
+                dst[i * 8 + 2 * (lane & 3)] = o[i][2 * h];
+                dst[i * 8 + 2 * (lane & 3) + 1] = o[i][2 * h + 1];
+            }
+            if ((lane & 3) == 0) { dst[D] = m_run[h]; dst[D + 1] = l_run[h]; }
+        }
+    }
+    if (NG > 1) __syncthreads();
+    if (group > 0) return;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        float l = l_run[h];
-        l += __shfl_xor_sync(0xffffffffu, l, 1);
-        l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int row = warp * 16 + (lane >> 2) + 8 * h;
+        float m = m_run[h], l = l_run[h];
+#pragma unroll
+        for (int g = 1; g < NG; ++g) m = fmaxf(m, merge[((size_t)(g - 1) * BM + row) * (D + 2) + D]);
+        const float m_use = (m == -INFINITY) ? 0.f : m;
+        const float w0 = exp2f(m_run[h] - m_use);
+        l *= w0;
+#pragma unroll
+        for (int i = 0; i < ND; ++i) { o[i][2 * h] *= w0; o[i][2 * h + 1] *= w0; }
+#pragma unroll
+        for (int g = 1; g < NG; ++g) {
+            const float* src = merge + ((size_t)(g - 1) * BM + row) * (D + 2);
+            const float wg = exp2f(src[D] - m_use);     // a group without tiles has max -inf: weight 0
+            l += wg * src[D + 1];
+#pragma unroll
+            for (int i = 0; i < ND; ++i) {
+                o[i][2 * h] += wg * src[i * 8 + 2 * (lane & 3)];
+                o[i][2 * h + 1] += wg * src[i * 8 + 2 * (lane & 3) + 1];
+            }
+        }
         if (row < rows) {
             const float inv = 1.f / l;
             bf16* dst = out + ((size_t)(tok0 + row) * hq + head) * D + 2 * (lane & 3);

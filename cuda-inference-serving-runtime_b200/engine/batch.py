@@ -106,10 +106,26 @@ def _align(n: int) -> int:
     return (n + 3) & ~3
 
 
+class StaticMeta:
+    """Fixed host and device buffers for the metadata of steps of one shape (the inputs of a captured graph).
+
+    Block-table updates are padded to `update_capacity` entries per group (index -1: no change), so a step of the
+    same shape always has the same layout; the caller applies what does not fit before packing.
+    """
+
+    def __init__(self, device, ints: int, update_capacity: int, max_decode_ctx: int):
+        self.pinned = torch.zeros(ints, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.zeros(ints, dtype=torch.int32, device=device)
+        self.update_capacity = update_capacity
+        self.max_decode_ctx = max_decode_ctx        # an upper bound (the bucket), so the decode split plan is fixed
+
+
 def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarray, positions: np.ndarray,
                   token_req: np.ndarray, table_updates: Sequence[Tuple[np.ndarray, np.ndarray]],
-                  extra: Optional[Dict[str, np.ndarray]] = None):
-    """Pack the step's metadata, send it in one copy, and return (context, update views, extra views)."""
+                  extra: Optional[Dict[str, np.ndarray]] = None, static: Optional[StaticMeta] = None):
+    """Pack the step's metadata, send it in one copy, and return (context, update views, extra views).
+
+    With `static`, the metadata goes into that shape's fixed buffers instead of fresh ones."""
     q_len = np.asarray(host.q_len, dtype=np.int32)
     tile = kernels.PREFILL_TILE
     tile_req: List[int] = []
@@ -121,7 +137,7 @@ def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarr
             dec_req.append(r)
             max_decode_ctx = max(max_decode_ctx, host.ctx_len[r])
         else:
-            for q0 in range(0, n, tile):
+            for q0 in reversed(range(0, n, tile)):     # a portion's last tile has the longest key loop: launch it first
                 tile_req.append(r)
                 tile_q0.append(q0)
     segments: List[Tuple[str, np.ndarray]] = [
@@ -132,6 +148,12 @@ def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarr
         ("dec_req", np.asarray(dec_req, dtype=np.int32)), ("logit_rows", np.asarray(host.logit_rows, dtype=np.int32)),
     ]
     for g, (idx, val) in enumerate(table_updates):
+        if static is not None:
+            padded_idx = np.full(static.update_capacity, -1, dtype=np.int32)
+            padded_val = np.zeros(static.update_capacity, dtype=np.int32)
+            padded_idx[:idx.size] = idx
+            padded_val[:val.size] = val
+            idx, val = padded_idx, padded_val
         segments.append((f"upd_idx{g}", idx))
         segments.append((f"upd_val{g}", val))
     for name, arr in (extra or {}).items():
@@ -142,14 +164,20 @@ def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarr
         offsets[name] = (total, arr.size)
         total += _align(arr.size)
     total = max(total, 4)
-    pinned, ring_index = ring.take(total)
+    if static is not None:
+        if total > static.pinned.numel():
+            raise ValueError("the step's metadata does not fit the buffers of its shape")
+        pinned, dev = static.pinned, static.dev
+    else:
+        pinned, ring_index = ring.take(total)
+        dev = torch.empty(total, dtype=torch.int32, device=device)
     flat = pinned.numpy()
     for name, arr in segments:
         start, size = offsets[name]
         flat[start:start + size] = arr
-    dev = torch.empty(total, dtype=torch.int32, device=device)
-    dev.copy_(pinned[:total], non_blocking=True)
-    ring.sent(ring_index)
+    dev[:total].copy_(pinned[:total], non_blocking=True)
+    if static is None:
+        ring.sent(ring_index)
 
     def view(name: str) -> torch.Tensor:
         start, size = offsets[name]
@@ -161,7 +189,7 @@ def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarr
     ctx.tile_req, ctx.tile_q0, ctx.dec_req = view("tile_req"), view("tile_q0"), view("dec_req")
     ctx.n_tiles, ctx.n_decode = len(tile_req), len(dec_req)
     ctx.logit_rows = view("logit_rows")
-    ctx.max_decode_ctx = max_decode_ctx
+    ctx.max_decode_ctx = max_decode_ctx if static is None else max(static.max_decode_ctx, max_decode_ctx)
     updates = [(view(f"upd_idx{g}"), view(f"upd_val{g}")) for g in range(len(table_updates))]
     extras = {name: view(name) for name in (extra or {})}
     return ctx, updates, extras

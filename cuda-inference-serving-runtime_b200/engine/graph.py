@@ -150,12 +150,57 @@ class DecodeGraph:
         self.replays += 1
 
 
+class ShapeGraph:
+    """One captured step of a fixed shape: the same portion lengths per request, in the same order, and the same number
+    of wanted logit rows.  Portions of prompts repeat their shape whenever prompts are cut by a fixed budget."""
+
+    def __init__(self, stepper, q_lens: Tuple[int, ...], n_rows: int, ctx_bucket: int):
+        from .batch import StaticMeta
+        cache = stepper.cache
+        tokens = sum(q_lens)
+        self.stepper = stepper
+        capacity = tokens // max(1, cache.page_size) + 2 * len(q_lens) + 8
+        ints = 4 * tokens + 8 * len(q_lens) + 2 * (tokens // 64 + len(q_lens)) + n_rows * 8 + 2 * capacity * max(1, len(cache.page_groups)) + 256
+        self.static = StaticMeta(stepper.model.device, ints, capacity, ctx_bucket)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.replays = 0
+        self.launches = {"own": 0, "library": 0}
+
+    def _run(self, ctx, update_views) -> None:
+        cache, model = self.stepper.cache, self.stepper.model
+        ctx.shared.clear()      # what parts share within a step (rotary tables) is computed inside every run, so also inside the graph
+        for g, (idx, val) in zip(cache.page_groups, update_views):
+            kernels.table_update(g.device_table, idx, val)
+        self.logits = model.forward(ctx, cache)
+
+    def run(self, ctx, update_views) -> torch.Tensor:
+        """`ctx` and `update_views` view this shape's static buffers, already filled and sent for this step."""
+        if self.graph is None:
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                self._run(ctx, update_views)        # warm-up outside the graph; writes the same cache entries the replay will
+            torch.cuda.current_stream().wait_stream(stream)
+            torch.cuda.synchronize()
+            before = dict(kernels.LAUNCHES)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self._run(ctx, update_views)
+            self.launches = {k: kernels.LAUNCHES[k] - before[k] for k in before}
+        self.graph.replay()
+        self.replays += 1
+        return self.logits
+
+
 class DecodeGraphs:
     """The graphs of one stepper, kept by (batch bucket, context bucket), least recently used evicted first."""
 
     def __init__(self, stepper, capacity: int = 8):
         self.stepper, self.capacity = stepper, capacity
         self.graphs: "OrderedDict[Tuple[int, int], DecodeGraph]" = OrderedDict()
+        self.shapes: "OrderedDict[tuple, ShapeGraph]" = OrderedDict()
+        self.seen: Dict[tuple, int] = {}
         self.hits = self.misses = self.evictions = 0
 
     def get(self, n_rows: int, max_ctx: int) -> Tuple[DecodeGraph, bool]:
@@ -173,6 +218,27 @@ class DecodeGraphs:
             self.evictions += 1
         return graph, True
 
+    def shape(self, q_lens: Tuple[int, ...], n_rows: int, max_decode_ctx: int) -> Optional[ShapeGraph]:
+        """The graph of a step shape, from the second time the shape is seen (a shape seen once is not worth a capture)."""
+        key = (q_lens, n_rows, bucket_of(max_decode_ctx, MIN_CONTEXT_BUCKET) if max_decode_ctx else 0)
+        graph = self.shapes.get(key)
+        if graph is not None:
+            self.shapes.move_to_end(key)
+            self.hits += 1
+            return graph
+        self.seen[key] = self.seen.get(key, 0) + 1
+        if self.seen[key] < 2:
+            return None
+        if len(self.seen) > 4096:
+            self.seen.clear()
+        self.misses += 1
+        graph = ShapeGraph(self.stepper, q_lens, n_rows, key[2])
+        self.shapes[key] = graph
+        while len(self.shapes) > self.capacity:
+            self.shapes.popitem(last=False)
+            self.evictions += 1
+        return graph
+
     def report(self) -> dict:
-        return {"entries": len(self.graphs), "hits": self.hits, "misses": self.misses, "evictions": self.evictions,
+        return {"entries": len(self.graphs), "shape_entries": len(self.shapes), "hits": self.hits, "misses": self.misses, "evictions": self.evictions,
                 "replays": {f"{k[0]}x{k[1]}": g.replays for k, g in self.graphs.items()}}

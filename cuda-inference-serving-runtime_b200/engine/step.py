@@ -50,9 +50,12 @@ def run_page_copies(cache: CacheManager, device) -> None:
 
 
 def prepare_step(cache: CacheManager, ring: PinnedRing, device, entries: Sequence[StepEntry], vocab_size: int,
-                 extra: Optional[Dict[str, np.ndarray]] = None):
+                 extra: Optional[Dict[str, np.ndarray]] = None, shape_graphs=None):
     """Validate a batch, reserve its pages (all or nothing), send its metadata and bring the device's block
-    tables up to date.  Returns (context, device views of `extra`).  Lengths advance in `commit_step`."""
+    tables up to date.  Returns (context, device views of `extra`, graph or None).  Lengths advance in `commit_step`.
+
+    With `shape_graphs`, a step whose shape has a captured graph gets its metadata into that graph's buffers and
+    leaves the table updates to the graph."""
     validate_entries(cache, entries, vocab_size)
     keys = [e.key for e in entries]
     cache.reserve([(e.key, len(e.tokens)) for e in entries])   # raises before any change
@@ -70,15 +73,27 @@ def prepare_step(cache: CacheManager, ring: PinnedRing, device, entries: Sequenc
         logit_rows.extend(total + int(w) for w in e.want)
         total += n
     host = HostBatch(keys, slots, q_start, q_len, ctx_len, total, logit_rows)
-    updates = [cache.drain_table_updates(g.index) for g in cache.page_groups]
+    graph = None
+    if shape_graphs is not None:
+        decode_ctx = max((c for n, c in zip(q_len, ctx_len) if n == 1), default=0)
+        graph = shape_graphs.shape(tuple(q_len), len(logit_rows), decode_ctx)
+    updates = []
+    for g in cache.page_groups:
+        idx, val = cache.drain_table_updates(g.index)
+        if graph is not None and idx.size > graph.static.update_capacity:      # more than the graph's list holds: apply now
+            kernels.table_update(g.device_table, torch.from_numpy(idx).to(device), torch.from_numpy(val).to(device))
+            idx, val = idx[:0], val[:0]
+        updates.append((idx, val))
     ctx, update_views, extras = build_context(
         device, ring, host, np.asarray(token_ids, dtype=np.int32), np.asarray(positions, dtype=np.int32),
-        np.asarray(token_req, dtype=np.int32), updates, extra)
-    for g, (idx, val) in zip(cache.page_groups, update_views):
-        if idx.numel():
-            kernels.table_update(g.device_table, idx, val)
+        np.asarray(token_req, dtype=np.int32), updates, extra, static=graph.static if graph is not None else None)
+    if graph is None:
+        for g, (idx, val) in zip(cache.page_groups, update_views):
+            if idx.numel():
+                kernels.table_update(g.device_table, idx, val)
     run_page_copies(cache, device)
-    return ctx, extras
+    ctx.update_views = update_views
+    return ctx, extras, graph
 
 
 def commit_step(cache: CacheManager, entries: Sequence[StepEntry]) -> None:
@@ -126,8 +141,12 @@ class Stepper:
         self._ahead = None
         if self.graphs is not None and entries and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return self._graph_step(entries, extra)
-        ctx, extras = prepare_step(self.cache, self.ring, self.model.device, entries, self.model.spec.vocab_size, extra)
-        logits = self.model.forward(ctx, self.cache)
+        ctx, extras, graph = prepare_step(self.cache, self.ring, self.model.device, entries, self.model.spec.vocab_size,
+                                          extra, shape_graphs=self.graphs)
+        if graph is not None:
+            logits = graph.run(ctx, ctx.update_views)
+        else:
+            logits = self.model.forward(ctx, self.cache)
         commit_step(self.cache, entries)
         self.last_context, self.last_extras, self.last_tokens = ctx, extras, None
         return logits

@@ -116,3 +116,35 @@ def test_a_mixer_that_reads_host_values_turns_graphs_off(model_dir):
         assert Stepper(model, n_pages=4, page_size=8, max_slots=2, graph=True).graphs is None
     finally:
         del model.layers[0].mixer.graph_safe
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_step_shapes_replay_from_a_graph_with_new_contents(model_dir, dtype):
+    """Portions of the same lengths recur (prompts cut by a fixed budget): from the second time on the step is a graph
+    replay whose tokens, positions, requests, pages and wanted rows are rebound."""
+    from cisr_b200 import Model, StepEntry, Stepper
+
+    cfg, weights, path = model_dir
+    model = Model.from_pretrained(path, dtype=dtype)
+    stepper = Stepper(model, n_pages=40, page_size=8, max_slots=4, graph=True)
+    tokens = {k: tm.random_tokens(cfg, 75, 10 + i) for i, k in enumerate("abcd")}
+    reference = {k: replay.plain_logits(cfg, weights, t) for k, t in tokens.items()}
+    got = {}
+    for k in "abcd":
+        stepper.create(k)
+    # shape (30,) five times (a, b, c, d at position 0, then a at 30), shape (15, 1) three times with changing partners
+    plan = [[("a", 0, 30)], [("b", 0, 30)], [("c", 0, 30)], [("d", 0, 30)], [("a", 30, 30)],
+            [("b", 30, 15), ("a", 60, 1)], [("c", 30, 15), ("a", 61, 1)], [("d", 30, 15), ("b", 45, 1)]]
+    for step in plan:
+        entries = [StepEntry(k, tokens[k][at:at + n], [n - 1, 0] if n > 1 else [0]) for k, at, n in step]
+        logits = stepper.step(entries).cpu().numpy()
+        row = 0
+        for k, at, n in step:
+            for w in ([n - 1, 0] if n > 1 else [0]):
+                got[(k, at + w)] = logits[row].copy()
+                row += 1
+        stepper.cache.check()
+    replay.compare(got, tokens, reference, dtype)
+    report = stepper.graphs.report()
+    assert report["shape_entries"] == 2 and report["hits"] >= 4
+    assert sorted(g.replays for g in stepper.graphs.shapes.values()) == [2, 4]

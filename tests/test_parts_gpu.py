@@ -83,7 +83,7 @@ class MiniStep:
         from cisr_b200 import StepEntry
         from cisr_b200.engine.step import commit_step, prepare_step
         entries = [StepEntry(k, [0] * n) for k, n in entries]
-        ctx, _ = prepare_step(self.cache, self.ring, torch.device(DEV), entries, 1)
+        ctx, _, _ = prepare_step(self.cache, self.ring, torch.device(DEV), entries, 1)
         out = fn(ctx, self.cache.binding(0))
         commit_step(self.cache, entries)
         return out
