@@ -8,8 +8,10 @@
 //   * warp 1: allocates BN columns of tensor memory; one thread issues tcgen05.mma (kind::f16, M = 128,
 //     N = BN, K = 16, four per 64-wide k block) on shared-memory descriptors and commits each stage to its
 //     "empty" mbarrier, and the whole tile to the "accumulator ready" mbarrier
-//   * warps 2..5: read the accumulator with tcgen05.ld (32 lanes x 32 columns per warp and step) and
-//     write float rows of `out`
+//   * warps 2..5: read the accumulator with tcgen05.ld (32 lanes x 32 columns per warp and step) and run the
+//     epilogue: PLAIN writes float rows of `out`; SWIGLU (the B tile is 64 gate rows and the 64 up rows of the
+//     same features) writes silu(gate) * up as bfloat16; ROPE (the tile is whole heads of the stacked q/k/v
+//     projection) rotates q and k heads and writes q rows and the k, v cache pages as bfloat16
 //
 // Rows and columns beyond M, N or K are zero-filled by TMA on the way in and skipped on the way out, so any
 // M and N work; K must be a multiple of 8 (16-byte rows for the tensor map).  Every wait on an mbarrier
@@ -21,9 +23,18 @@
 
 #include "common.cuh"
 
+#include <unordered_map>
+
 namespace {
 typedef __nv_bfloat16 bf16;
+enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ROPE = 2 };
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
+
+struct Epilogue {                       // what the epilogue variants need beyond the accumulator
+    float* out_f32; bf16* out_bf16; int inter;
+    const float* cos_t; const float* sin_t; bf16* q_out; bf16* k_cache; bf16* v_cache; const int* positions;
+    const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size; int hq; int hkv; int dim;
+};
 constexpr unsigned MAX_POLLS = 1u << 20;   // a stage is ready within microseconds; this is seconds
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -75,6 +86,38 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// 32 consecutive accumulator columns of this thread's lane (its output row)
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 32 floats -> 32 bfloat16 (64 bytes) at dst; `count` of them are valid
+__device__ __forceinline__ void store_bf16x32(bf16* dst, const float (&v)[32], int count) {
+    if (count >= 32 && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            uint4 p;
+            __nv_bfloat162 a = __floats2bfloat162_rn(v[j], v[j + 1]), b = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+            __nv_bfloat162 c = __floats2bfloat162_rn(v[j + 4], v[j + 5]), d = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+            p.x = *reinterpret_cast<uint32_t*>(&a); p.y = *reinterpret_cast<uint32_t*>(&b);
+            p.z = *reinterpret_cast<uint32_t*>(&c); p.w = *reinterpret_cast<uint32_t*>(&d);
+            *reinterpret_cast<uint4*>(dst + j) = p;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < count) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+}
+
 template <int BN, int STAGES>
 struct Smem {
     static constexpr size_t A_BYTES = (size_t)BM * BK * sizeof(bf16);
@@ -83,10 +126,10 @@ struct Smem {
     static constexpr size_t TOTAL = TILES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    float* __restrict__ out, int m, int n, int k, int* __restrict__ error) {
+                    const Epilogue ep, int m, int n, int k, int* __restrict__ error) {
     extern __shared__ unsigned char smem_raw[];
     typedef Smem<BN, STAGES> S;
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024-byte aligned
@@ -96,7 +139,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    // SWIGLU: the tile's 128 accumulator columns are 64 gate features and the 64 up features of the same indices
+    const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? BN / 2 : BN), m0 = blockIdx.y * BM;
     const int k_blocks = (k + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -122,7 +166,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!ok) break;
                 mbar_expect_tx(full_bar + s, (uint32_t)(S::A_BYTES + S::B_BYTES));
                 tma_load_2d(tiles + s * (S::A_BYTES + S::B_BYTES), &map_a, kb * BK, m0, full_bar + s);
-                tma_load_2d(tiles + s * (S::A_BYTES + S::B_BYTES) + S::A_BYTES, &map_w, kb * BK, n0, full_bar + s);
+                unsigned char* b_tile = tiles + s * (S::A_BYTES + S::B_BYTES) + S::A_BYTES;
+                if (EPI == EPI_SWIGLU) {      // two boxes of 64 rows: gate rows n0.., up rows inter + n0..
+                    tma_load_2d(b_tile, &map_w, kb * BK, n0, full_bar + s);
+                    tma_load_2d(b_tile + S::B_BYTES / 2, &map_w, kb * BK, ep.inter + n0, full_bar + s);
+                } else {
+                    tma_load_2d(b_tile, &map_w, kb * BK, n0, full_bar + s);
+                }
             }
         }
     } else if (warp == 1) {
@@ -148,30 +198,86 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (ok) {
             const int quarter = warp & 3;                                      // the 32 lanes this warp may read
             const int row = m0 + quarter * 32 + lane;
+            const uint32_t lane_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+            if (EPI == EPI_PLAIN) {
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t v[32];
-                const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                               "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                               "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                               "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                             : "r"(taddr) : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t v[32];
+                    tmem_load32(lane_base + (uint32_t)c, v);
+                    if (row < m) {
+                        float* dst = ep.out_f32 + (size_t)row * n + n0 + c;
+                        if (n0 + c + 32 <= n && (n & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                                  __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n0 + c + j < n) dst[j] = __uint_as_float(v[j]);
+                        }
+                    }
+                }
+            } else if (EPI == EPI_SWIGLU) {
+#pragma unroll 1
+                for (int c = 0; c < BN / 2; c += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_load32(lane_base + (uint32_t)c, g);
+                    tmem_load32(lane_base + (uint32_t)(BN / 2 + c), u);
+                    float act[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float gv = __uint_as_float(g[j]);
+                        act[j] = gv / (1.f + expf(-gv)) * __uint_as_float(u[j]);
+                    }
+                    if (row < m && n0 + c < ep.inter)
+                        store_bf16x32(ep.out_bf16 + (size_t)row * ep.inter + n0 + c, act, ep.inter - (n0 + c));
+                }
+            } else {
+                // whole heads of the stacked q, k, v projection: BN / dim heads per tile, rotation pairs (i, i + dim / 2)
+                const int dim = ep.dim, half = dim / 2;
+                int pos = 0, page = -1;
                 if (row < m) {
-                    float* dst = out + (size_t)row * n + n0 + c;
-                    if (n0 + c + 32 <= n && (n & 3) == 0) {
+                    pos = ep.positions[row];
+                    page = ep.block_table[(size_t)ep.req_slot[ep.token_req[row]] * ep.table_width + pos / ep.page_size];
+                }
+#pragma unroll 1
+                for (int h0 = 0; h0 < BN; h0 += dim) {
+                    const int hh = (n0 + h0) / dim;                        // head index in the stacked projection
+                    if (hh >= ep.hq + 2 * ep.hkv) break;
+                    const bool is_q = hh < ep.hq, is_k = !is_q && hh < ep.hq + ep.hkv;
+                    bf16* dst = nullptr;
+                    if (row < m) {
+                        if (is_q) dst = ep.q_out + ((size_t)row * ep.hq + hh) * dim;
+                        else if (page >= 0) {                               // a missing page entry: a padding row, nothing to write
+                            const int kvh = is_k ? hh - ep.hq : hh - ep.hq - ep.hkv;
+                            dst = (is_k ? ep.k_cache : ep.v_cache) +
+                                  (((size_t)page * ep.hkv + kvh) * ep.page_size + pos % ep.page_size) * dim;
+                        }
+                    }
+#pragma unroll 1
+                    for (int c = 0; c < half; c += 32) {
+                        uint32_t lo[32], hi[32];
+                        tmem_load32(lane_base + (uint32_t)(h0 + c), lo);
+                        tmem_load32(lane_base + (uint32_t)(h0 + half + c), hi);
+                        float first[32], second[32];
+                        if ((is_q || is_k) && row < m) {
+                            const float* cs = ep.cos_t + (size_t)row * half + c;
+                            const float* sn = ep.sin_t + (size_t)row * half + c;
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                                              __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                    } else {
+                            for (int j = 0; j < 32; ++j) {
+                                const float a = __uint_as_float(lo[j]), b = __uint_as_float(hi[j]), cv = cs[j], sv = sn[j];
+                                first[j] = a * cv - b * sv;
+                                second[j] = b * cv + a * sv;
+                            }
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (n0 + c + j < n) dst[j] = __uint_as_float(v[j]);
+                            for (int j = 0; j < 32; ++j) { first[j] = __uint_as_float(lo[j]); second[j] = __uint_as_float(hi[j]); }
+                        }
+                        if (dst) {
+                            store_bf16x32(dst + c, first, 32);
+                            store_bf16x32(dst + half + c, second, 32);
+                        }
                     }
                 }
             }
@@ -201,21 +307,50 @@ int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_row
     return r == CUDA_SUCCESS ? 0 : -20 - (int)r;
 }
 
-template <int BN, int STAGES>
-int launch(const void* a, const void* w, float* out, int m, int n, int k, cudaStream_t s) {
-    CUtensorMap map_a, map_w;
-    int status = make_map(&map_a, a, m, k, BM);
+struct MapKey {
+    const void* base; int rows, cols, box_rows;
+    bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.base) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^ (size_t)k.box_rows;
+    }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;     // a map describes geometry only, so it stays right while the address does
+
+int cached_map(const CUtensorMap** out, const void* base, int rows, int cols, int box_rows) {
+    const MapKey key{base, rows, cols, box_rows};
+    auto it = g_maps.find(key);
+    if (it == g_maps.end()) {
+        if (g_maps.size() > 4096) g_maps.clear();
+        CUtensorMap map;
+        const int status = make_map(&map, base, rows, cols, box_rows);
+        if (status) return status;
+        it = g_maps.emplace(key, map).first;
+    }
+    *out = &it->second;
+    return 0;
+}
+
+template <int BN, int STAGES, int EPI>
+int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k, int grid_x, cudaStream_t s) {
+    const CUtensorMap *map_a, *map_w;
+    int status = cached_map(&map_a, a, m, k, BM);
     if (status) return status;
-    if ((status = make_map(&map_w, w, n, k, BN))) return status;
+    if ((status = cached_map(&map_w, w, n, k, EPI == EPI_SWIGLU ? BN / 2 : BN))) return status;
     typedef Smem<BN, STAGES> S;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::TOTAL);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_tcgen05_kernel<BN, STAGES><<<dim3((n + BN - 1) / BN, (m + BM - 1) / BM), 192, S::TOTAL, s>>>(map_a, map_w, out, m, n, k, g_error);
+    gemm_tcgen05_kernel<BN, STAGES, EPI><<<dim3(grid_x, (m + BM - 1) / BM), 192, S::TOTAL, s>>>(*map_a, *map_w, ep, m, n, k, g_error);
     return launch_status();
+}
+
+bool operands_ok(const void* a, const void* w, int k) {
+    return g_encode && g_error && k > 0 && k % 8 == 0 && !(((uintptr_t)a | (uintptr_t)w) & 15);
 }
 }  // namespace
 
@@ -232,12 +367,43 @@ CISR_EXPORT int cisr_gemm_tcgen05_init(int* error_flag) {
     return 0;
 }
 
+// Three pipeline stages keep a CTA near 100 KB of shared memory, so two CTAs share an SM and one's epilogue overlaps
+// the other's main loop.
 CISR_EXPORT int cisr_gemm_tcgen05(const void* a, const void* w, float* out, int m, int n, int k, void* stream) {
     if (m <= 0 || n <= 0) return 0;
     if (!g_encode || !g_error) return -13;
-    if (k <= 0 || k % 8) return -2;                                   // tensor-map rows must be multiples of 16 bytes
-    if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) & 15) return -2;
+    if (!operands_ok(a, w, k) || ((uintptr_t)out & 15)) return -2;
+    Epilogue ep = {};
+    ep.out_f32 = out;
     cudaStream_t s = (cudaStream_t)stream;
-    if (n <= 64) return launch<64, 6>(a, w, out, m, n, k, s);
-    return launch<128, 5>(a, w, out, m, n, k, s);
+    if (n <= 64) return launch<64, 4, EPI_PLAIN>(a, w, ep, m, n, k, (n + 63) / 64, s);
+    return launch<128, 3, EPI_PLAIN>(a, w, ep, m, n, k, (n + 127) / 128, s);
+}
+
+// w stacks gate rows [0, inter) over up rows [inter, 2 * inter); out (bfloat16 [m, inter]) = silu(a gate^T) * (a up^T).
+CISR_EXPORT int cisr_gemm_tcgen05_swiglu(const void* a, const void* w, void* out, int m, int inter, int k, void* stream) {
+    if (m <= 0 || inter <= 0) return 0;
+    if (!g_encode || !g_error) return -13;
+    if (!operands_ok(a, w, k)) return -2;
+    Epilogue ep = {};
+    ep.out_bf16 = (bf16*)out; ep.inter = inter;
+    return launch<128, 3, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 63) / 64, (cudaStream_t)stream);
+}
+
+// w stacks the q, k and v heads; q and k heads are rotated (pairs (i, i + dim / 2), cos/sin [m, dim / 2]); q goes to
+// q_out [m, hq, dim], k and v to their cache pages.  Takes dim 64 or 128 (whole heads per 128-column tile and 32-column
+// halves of the rotation); other head sizes use the plain product and the separate rotation kernel.
+CISR_EXPORT int cisr_gemm_tcgen05_rope(const void* a, const void* w, int m, int k, const float* cos_t, const float* sin_t,
+                                       void* q_out, void* k_cache, void* v_cache, const int* positions,
+                                       const int* token_req, const int* req_slot, const int* block_table,
+                                       int table_width, int page_size, int hq, int hkv, int dim, void* stream) {
+    if (m <= 0) return 0;
+    if (!g_encode || !g_error) return -13;
+    if (!operands_ok(a, w, k) || (dim != 64 && dim != 128)) return -2;
+    Epilogue ep = {};
+    ep.cos_t = cos_t; ep.sin_t = sin_t; ep.q_out = (bf16*)q_out; ep.k_cache = (bf16*)k_cache; ep.v_cache = (bf16*)v_cache;
+    ep.positions = positions; ep.token_req = token_req; ep.req_slot = req_slot; ep.block_table = block_table;
+    ep.table_width = table_width; ep.page_size = page_size; ep.hq = hq; ep.hkv = hkv; ep.dim = dim;
+    const int n = (hq + 2 * hkv) * dim;
+    return launch<128, 3, EPI_ROPE>(a, w, ep, m, n, k, (n + 127) / 128, (cudaStream_t)stream);
 }

@@ -439,6 +439,8 @@ def _tcgen05():
         lib = load_library("gemm_tcgen05.cu")
         lib.cisr_gemm_tcgen05_init.restype = ctypes.c_int
         lib.cisr_gemm_tcgen05.restype = ctypes.c_int
+        lib.cisr_gemm_tcgen05_swiglu.restype = ctypes.c_int
+        lib.cisr_gemm_tcgen05_rope.restype = ctypes.c_int
         flag = torch.zeros(1, dtype=torch.int32, device="cuda")
         _check(lib.cisr_gemm_tcgen05_init(_p(flag)), "tcgen05 gemm init", own=0)
         _tcgen05_state["lib"], _tcgen05_state["flag"] = lib, flag
@@ -463,6 +465,42 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.T
         raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
     _check(_tcgen05().cisr_gemm_tcgen05(_p(a), _p(w), _p(out), m, n, k, _stream()), "gemm_tcgen05")
     return out
+
+
+def gemm_tcgen05_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out (bfloat16 [M, I]) = silu(a @ w[:I]^T) * (a @ w[I:]^T): the product with SwiGLU as its epilogue."""
+    _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 2); _need(out, torch.bfloat16, "out", 2)
+    m, k = a.shape
+    inter = out.shape[1]
+    if w.shape != (2 * inter, k) or out.shape[0] != m:
+        raise KernelError(f"gemm swiglu: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
+    _check(_tcgen05().cisr_gemm_tcgen05_swiglu(_p(a), _p(w), _p(out), m, inter, k, _stream()), "gemm_tcgen05_swiglu")
+    return out
+
+
+def tcgen05_rope_ok(dim: int, rot_half: int, interleaved: bool) -> bool:
+    """The rotation epilogue takes heads of 64 or 128 rotated over their whole width in split-half pairs."""
+    return dim in (64, 128) and 2 * rot_half == dim and not interleaved
+
+
+def gemm_tcgen05_rope(a: torch.Tensor, w: torch.Tensor, rope: dict) -> None:
+    """The stacked q/k/v product with rotation and cache write as its epilogue (`rope` as for skinny_gemm)."""
+    _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 2)
+    m, k = a.shape
+    hq, hkv, dim = rope["hq"], rope["hkv"], rope["dim"]
+    if w.shape != ((hq + 2 * hkv) * dim, k):
+        raise KernelError("gemm rope: w must stack the q, k and v heads")
+    for name in ("q_out", "k_cache", "v_cache"):
+        _need(rope[name], torch.bfloat16, name)
+    for name in ("positions", "token_req", "req_slot", "block_table"):
+        _need(rope[name], torch.int32, name)
+    _need(rope["cos"], torch.float32, "cos", 2); _need(rope["sin"], torch.float32, "sin", 2)
+    if rope["cos"].shape != (m, dim // 2):
+        raise KernelError("gemm rope: rotary tables must be [tokens, head_dim / 2]")
+    _check(_tcgen05().cisr_gemm_tcgen05_rope(
+        _p(a), _p(w), m, k, _p(rope["cos"]), _p(rope["sin"]), _p(rope["q_out"]), _p(rope["k_cache"]), _p(rope["v_cache"]),
+        _p(rope["positions"]), _p(rope["token_req"]), _p(rope["req_slot"]), _p(rope["block_table"]),
+        rope["block_table"].shape[1], rope["page_size"], hq, hkv, dim, _stream()), "gemm_tcgen05_rope")
 
 
 def raise_if_kernel_gave_up() -> None:

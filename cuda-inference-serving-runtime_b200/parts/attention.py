@@ -78,8 +78,15 @@ class GQAAttention(Mixer):
                 h.done(x_out)
             else:
                 kernels.skinny_gemm(self.qkv, tokens, act=as_tensor(h), epilogue=kernels.EPI_ROPE, rope=rope)
+        elif (cache.write and rot is not None and kernels.tcgen05_rope_ok(dim, rot.rot_half, rot.interleaved)
+              and kernels.tcgen05_ok(as_tensor(h) if isinstance(h, torch.Tensor) else h.materialize_once(), self.qkv)):
+            # many tokens: rotation and cache write are the epilogue of the tcgen05 product
+            kernels.gemm_tcgen05_rope(h if isinstance(h, torch.Tensor) else h.materialize_once(), self.qkv, dict(
+                cos=rot.cos, sin=rot.sin, q_out=q, k_cache=cache.k, v_cache=cache.v, positions=ctx.positions,
+                token_req=ctx.token_req, req_slot=ctx.req_slot, block_table=cache.block_table, page_size=cache.page_size,
+                hq=hq, hkv=hkv, dim=dim))
         else:
-            h = as_tensor(h)
+            h = h if isinstance(h, torch.Tensor) else h.materialize_once()
             if cache.write:
                 proj = linear(h, self.qkv)
                 k_col, v_col = hq * dim, (hq + hkv) * dim

@@ -86,6 +86,12 @@ class PendingNorm:
     def materialize(self) -> torch.Tensor:
         return self.norm.forward(self.stream.x, self.stream.take_pending(), self.dtype)
 
+    def materialize_once(self) -> torch.Tensor:
+        """`materialize`, remembered: a part may ask for the normed tensor more than once while choosing its kernels."""
+        if getattr(self, "_tensor", None) is None:
+            self._tensor = self.materialize()
+        return self._tensor
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,

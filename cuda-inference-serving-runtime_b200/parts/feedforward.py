@@ -54,5 +54,9 @@ class SwiGLU(FeedForward):
             else:
                 kernels.skinny_gemm(self.gate_up, tokens, act=as_tensor(h), epilogue=kernels.EPI_SWIGLU, out=act)
         else:
-            kernels.swiglu(linear(as_tensor(h), self.gate_up), act)
+            hn = as_tensor(h)
+            if kernels.tcgen05_ok(hn, self.gate_up):
+                kernels.gemm_tcgen05_swiglu(hn, self.gate_up, act)      # many tokens: SwiGLU is the product's epilogue
+            else:
+                kernels.swiglu(linear(hn, self.gate_up), act)
         return linear(act, self.down)

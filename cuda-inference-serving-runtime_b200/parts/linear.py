@@ -31,4 +31,4 @@ def norm_fusable(h, tokens: int, w: torch.Tensor) -> bool:
 
 def as_tensor(h) -> torch.Tensor:
     from .base import PendingNorm
-    return h.materialize() if isinstance(h, PendingNorm) else h
+    return h.materialize_once() if isinstance(h, PendingNorm) else h

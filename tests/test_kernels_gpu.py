@@ -452,3 +452,53 @@ def test_gemm_tcgen05(m, n, kk):
     k.raise_if_kernel_gave_up()
     ref = a.double() @ w.double().T
     close(out, ref, 2e-6 * kk ** 0.5 * 4, 1e-5, f"tcgen05 gemm {m}x{n}x{kk}")
+
+
+@pytest.mark.parametrize("m,inter,kk", [(128, 64, 64), (300, 176, 64), (2048, 1536, 576), (130, 250, 96), (129, 13, 40)])
+def test_gemm_tcgen05_swiglu_epilogue(m, inter, kk):
+    k = kernels()
+    g = torch.Generator().manual_seed(m + inter)
+    a = torch.randn(m, kk, generator=g).to(torch.bfloat16)
+    w = (0.2 * torch.randn(2 * inter, kk, generator=g)).to(torch.bfloat16)
+    out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=dev())
+    k.gemm_tcgen05_swiglu(a.to(dev()), w.to(dev()), out)
+    k.raise_if_kernel_gave_up()
+    gu = a.double() @ w.double().T
+    ref = gu[:, :inter] / (1 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
+    close(out, ref, 1e-3, 2 ** -7, "tcgen05 swiglu epilogue")
+
+
+@pytest.mark.parametrize("m", [128, 333])
+@pytest.mark.parametrize("dim,hq,hkv", [(64, 9, 3), (128, 2, 1), (64, 2, 2)])
+def test_gemm_tcgen05_rope_epilogue_matches_the_separate_kernels(m, dim, hq, hkv):
+    k = kernels()
+    hidden, page, theta = 96, 16, 10000.0
+    g = torch.Generator().manual_seed(m + dim)
+    w = (0.2 * torch.randn((hq + 2 * hkv) * dim, hidden, generator=g)).to(torch.bfloat16).to(dev())
+    hbf = torch.randn(m, hidden, generator=g).to(torch.bfloat16).to(dev())
+    positions = torch.arange(m, dtype=torch.int32).to(dev()) % 200
+    token_req = (torch.arange(m) // 200).to(torch.int32).to(dev())               # two requests
+    req_slot = torch.tensor([1, 0], dtype=torch.int32, device=dev())
+    table = torch.arange(32, dtype=torch.int32).reshape(2, 16).to(dev())
+    half = dim // 2
+    inv = (theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / dim)).to(dev())
+    cos = torch.empty(m, half, device=dev()); sin = torch.empty(m, half, device=dev())
+    k.rotary_tables(positions, inv, cos, sin)
+    results = []
+    for fused in (False, True):
+        q = torch.zeros(m, hq, dim, dtype=torch.bfloat16, device=dev())
+        kc = torch.zeros(32, hkv, page, dim, dtype=torch.bfloat16, device=dev()); vc = torch.zeros_like(kc)
+        if fused:
+            k.gemm_tcgen05_rope(hbf, w, dict(cos=cos, sin=sin, q_out=q, k_cache=kc, v_cache=vc, positions=positions, token_req=token_req,
+                                             req_slot=req_slot, block_table=table, page_size=page, hq=hq, hkv=hkv, dim=dim))
+            k.raise_if_kernel_gave_up()
+        else:
+            proj = torch.empty(m, w.shape[0], device=dev())
+            k.gemm_library(hbf, w, proj)
+            k.rope_store(proj, hq * dim, (hq + hkv) * dim, cos, sin, half, False, q, kc, vc, token_req, positions, req_slot, table,
+                         page, hq, hkv, dim)
+        results.append((q.float().cpu(), kc.float().cpu(), vc.float().cpu()))
+    for a, b, what in zip(results[0], results[1], ("q", "k cache", "v cache")):
+        assert float(b.abs().sum()) > 0
+        torch.testing.assert_close(b, a, atol=2e-2, rtol=2e-2, msg=lambda s: f"{what}: {s}")
+        assert torch.equal(b == 0, a == 0) or what == "q"
