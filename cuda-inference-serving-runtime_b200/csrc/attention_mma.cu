@@ -59,6 +59,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x in one instruction (ex2.approx: 2 ulp, -inf -> 0); the probabilities are rounded to bfloat16 right after
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -184,34 +190,48 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
             }
         }
 
+        // Mask only where a tile can be cut by the causal edge, the window's edge or the tile's row count; most
+        // tiles of a long prompt lie wholly inside and skip the per-element test.
+        const int warp_row0 = warp * 16;
+        const bool inside = (k0 + BN - 1 <= qpos0 + warp_row0) && (warp_row0 + 15 < rows) &&
+                            (window <= 0 || k0 + window > qpos0 + warp_row0 + 15);
         float tile_max[2] = {-INFINITY, -INFINITY};
+        if (inside) {
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+            for (int nt = 0; nt < 8; ++nt) {
+                tile_max[0] = fmaxf(tile_max[0], fmaxf(s[nt][0], s[nt][1]));
+                tile_max[1] = fmaxf(tile_max[1], fmaxf(s[nt][2], s[nt][3]));
+            }
+        } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int row = warp * 16 + (lane >> 2) + 8 * (e >> 1);
-                const int kpos = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
-                const int qpos = qpos0 + row;
-                const bool ok = (row < rows) && (kpos <= qpos) && (window <= 0 || kpos + window > qpos);
-                const float v = ok ? s[nt][e] * scale2 : -INFINITY;
-                s[nt][e] = v;
-                tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+            for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int row = warp_row0 + (lane >> 2) + 8 * (e >> 1);
+                    const int kpos = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                    const int qpos = qpos0 + row;
+                    const bool ok = (row < rows) && (kpos <= qpos) && (window <= 0 || kpos + window > qpos);
+                    const float v = ok ? s[nt][e] : -INFINITY;
+                    s[nt][e] = v;
+                    tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+                }
             }
         }
+        // the running max is kept in scaled units (score * scale * log2 e); p = 2^(s * scale2 - m) is one fma and one ex2
         float alpha[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             float mx = tile_max[h];
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m_run[h], mx);
+            const float m_new = fmaxf(m_run[h], mx * scale2);      // scale2 > 0, so the max commutes with the scaling
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            alpha[h] = exp2f(m_run[h] - m_use);
+            alpha[h] = fast_exp2(m_run[h] - m_use);
             m_run[h] = m_new;
             float sum = 0.f;
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-                const float p0 = exp2f(s[nt][2 * h] - m_use), p1 = exp2f(s[nt][2 * h + 1] - m_use);
+                const float p0 = fast_exp2(fmaf(s[nt][2 * h], scale2, -m_use)), p1 = fast_exp2(fmaf(s[nt][2 * h + 1], scale2, -m_use));
                 s[nt][2 * h] = p0; s[nt][2 * h + 1] = p1;
                 sum += p0 + p1;
             }

@@ -60,6 +60,43 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
         o[d] = from_float<OT>(row_cache[d] * scale * to_float(weight[d]));
 }
 
+// The same with 16-byte accesses, for widths that are multiples of 4.
+template <typename WT, typename OT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                       const WT* __restrict__ weight, OT* __restrict__ out,
+                                       const int* __restrict__ rows, int hidden, float eps, int write_back) {
+    __shared__ float scratch[32];
+    extern __shared__ __align__(16) float row_cache[];
+    const int r = blockIdx.x, h4 = hidden >> 2;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    float4* xr = reinterpret_cast<float4*>(x + src);
+    const float4* dr = delta ? reinterpret_cast<const float4*>(delta + src) : nullptr;
+    float4* cache4 = reinterpret_cast<float4*>(row_cache);
+    float sq = 0.f;
+    for (int d = threadIdx.x; d < h4; d += blockDim.x) {
+        float4 v = xr[d];
+        if (dr) {
+            const float4 dv = dr[d];
+            v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+            if (write_back) xr[d] = v;
+        }
+        cache4[d] = v;
+        sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float total = block_sum(sq, scratch);
+    const float scale = rsqrtf(total / (float)hidden + eps);
+    OT* o = out + (size_t)r * hidden;
+    for (int d = threadIdx.x; d < h4; d += blockDim.x) {
+        const float4 v = cache4[d];
+        const float w0 = to_float(weight[4 * d]), w1 = to_float(weight[4 * d + 1]);
+        const float w2 = to_float(weight[4 * d + 2]), w3 = to_float(weight[4 * d + 3]);
+        o[4 * d] = from_float<OT>(v.x * scale * w0);
+        o[4 * d + 1] = from_float<OT>(v.y * scale * w1);
+        o[4 * d + 2] = from_float<OT>(v.z * scale * w2);
+        o[4 * d + 3] = from_float<OT>(v.w * scale * w3);
+    }
+}
+
 template <typename WT, typename OT>
 static int add_rmsnorm_launch(float* x, const float* delta, const void* w, void* out, const int* rows, int n_rows,
                               int hidden, float eps, int write_back, cudaStream_t s) {
@@ -69,8 +106,18 @@ static int add_rmsnorm_launch(float* x, const float* delta, const void* w, void*
         cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<WT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-    add_rmsnorm_kernel<WT, OT><<<n_rows, threads, smem, s>>>(x, delta, (const WT*)w, (OT*)out, rows, hidden, eps, write_back);
+    const bool vec = (hidden & 3) == 0 && !(((uintptr_t)x | (uintptr_t)delta) & 15);
+    if (smem > 48 * 1024 && vec) {
+        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_vec_kernel<WT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (vec) {
+        const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+        add_rmsnorm_vec_kernel<WT, OT><<<n_rows, threads, smem, s>>>(x, delta, (const WT*)w, (OT*)out, rows, hidden, eps, write_back);
+    } else {
+        const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+        add_rmsnorm_kernel<WT, OT><<<n_rows, threads, smem, s>>>(x, delta, (const WT*)w, (OT*)out, rows, hidden, eps, write_back);
+    }
     return launch_status();
 }
 

@@ -262,13 +262,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         tmem_load32(lane_base + (uint32_t)(h0 + half + c), hi);
                         float first[32], second[32];
                         if ((is_q || is_k) && row < m) {
-                            const float* cs = ep.cos_t + (size_t)row * half + c;
-                            const float* sn = ep.sin_t + (size_t)row * half + c;
+                            const float4* cs = reinterpret_cast<const float4*>(ep.cos_t + (size_t)row * half + c);   // half is a multiple of 32
+                            const float4* sn = reinterpret_cast<const float4*>(ep.sin_t + (size_t)row * half + c);
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const float a = __uint_as_float(lo[j]), b = __uint_as_float(hi[j]), cv = cs[j], sv = sn[j];
-                                first[j] = a * cv - b * sv;
-                                second[j] = b * cv + a * sv;
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 cv = cs[j >> 2], sv = sn[j >> 2];
+                                const float cc[4] = {cv.x, cv.y, cv.z, cv.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    const float a = __uint_as_float(lo[j + u]), b = __uint_as_float(hi[j + u]);
+                                    first[j + u] = a * cc[u] - b * ss[u];
+                                    second[j + u] = b * cc[u] + a * ss[u];
+                                }
                             }
                         } else {
 #pragma unroll
