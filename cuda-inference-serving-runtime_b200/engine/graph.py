@@ -73,6 +73,11 @@ class DecodeGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.tokens = torch.zeros(rows, dtype=torch.int32, device=device)
+        # the update lists are the tail of the buffer; two pinned copies of that tail, used in turn, let a step's lists be
+        # written while the copy of the step before may still be on its way
+        self.upd_start = min((self.offsets[f"upd_idx{g.index}"][0] for g in cache.page_groups), default=total)
+        self.upd_host = [torch.full((total - self.upd_start,), -1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.upd_turn = 0
         self.replays = 0
         self.launches = {"own": 0, "library": 0}
 
@@ -104,6 +109,21 @@ class DecodeGraph:
 
     def upload(self) -> None:
         self.dev.copy_(self.host, non_blocking=True)
+
+    def upload_updates(self, updates) -> None:
+        """Send only new block-table update lists (the rest of the buffer holds what the device fed back to itself)."""
+        if self.upd_start >= self.dev.numel():
+            return
+        self.upd_turn ^= 1
+        staging = self.upd_host[self.upd_turn]
+        flat = staging.numpy()
+        for g, (idx, val) in zip(self.stepper.cache.page_groups, updates):
+            a, size = self.offsets[f"upd_idx{g.index}"]
+            b, _ = self.offsets[f"upd_val{g.index}"]
+            flat[a - self.upd_start:a - self.upd_start + size] = -1
+            flat[a - self.upd_start:a - self.upd_start + idx.size] = idx
+            flat[b - self.upd_start:b - self.upd_start + idx.size] = val
+        self.dev[self.upd_start:].copy_(staging, non_blocking=True)
 
     def _run(self, advance: bool) -> None:
         stepper = self.stepper

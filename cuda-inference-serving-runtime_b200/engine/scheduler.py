@@ -75,7 +75,8 @@ class Engine:
     """
 
     def __init__(self, stepper, choose: Callable, vocab_size: int, max_positions: int, max_active: int = 8,
-                 token_budget: int = 32, prefill_chunk: int = 8, policy: str = "chunked", reserve: str = "full"):
+                 token_budget: int = 32, prefill_chunk: int = 8, policy: str = "chunked", reserve: str = "full",
+                 lookahead: bool = False):
         if min(max_active, token_budget, prefill_chunk) <= 0:
             raise ValueError("invalid scheduler limits")
         if policy not in POLICIES:
@@ -86,6 +87,7 @@ class Engine:
         self.vocab_size, self.max_positions = vocab_size, max_positions
         self.max_active = 1 if policy == "serial" else max_active
         self.token_budget, self.prefill_chunk, self.policy, self.reserve = token_budget, prefill_chunk, policy, reserve
+        self.lookahead = lookahead
         self.waiting: deque = deque()
         self.active: List[Request] = []
         self.requests = {}
@@ -93,6 +95,7 @@ class Engine:
         self.trace: List[dict] = []
         self.start = time.perf_counter()
         self.rotation = 0
+        self._deferred = None      # (requests, device tokens, began): a decode step whose chosen tokens are not read yet
 
     @classmethod
     def for_model(cls, model, pages: int = 128, page_size: int = 16, max_active: int = 8, token_budget: int = 32,
@@ -103,7 +106,7 @@ class Engine:
         stepper = Stepper(model, n_pages=pages, page_size=page_size, max_slots=max(max_active, 1), graph=graph)
         sampler = DeviceSampler(stepper)
         return cls(stepper, sampler, model.spec.vocab_size, model.spec.max_positions, max_active, token_budget,
-                   prefill_chunk, policy, reserve)
+                   prefill_chunk, policy, reserve, lookahead=graph)
 
     # ---------------------------------------------------------------- page arithmetic
     @property
@@ -217,7 +220,44 @@ class Engine:
             remaining -= n
         return plan
 
+    def _tick_deferred(self) -> bool:
+        """Finish a decode step whose tokens were left on the device, launching the step after it first when nothing
+        about the batch can change in between: the device feeds its own tokens back, so the host's read of step k
+        overlaps step k + 1.  A request that ends at step k (EOS) has then run one step too many, whose token is dropped."""
+        reqs, tokens_dev, began = self._deferred
+        self._deferred = None
+        ahead = None
+        stable = (not self.waiting and len(reqs) == len(self.active) and all(r in self.active for r in reqs)
+                  and all(len(r.generated) + 2 <= r.max_new_tokens for r in reqs))
+        if stable and self.stepper.can_run_ahead():
+            try:
+                ran = self.stepper.decode_ahead(1)
+                ahead = ran[0] if ran.shape[0] == 1 else None
+            except OutOfPages:
+                ahead = None
+        chosen = tokens_dev.to("cpu").tolist()        # waits for step k only; step k + 1 is already queued behind it
+        self.stepper.check_kernels()
+        completed = time.perf_counter()
+        decoded = 0
+        for r, token in zip(reqs, chosen):
+            if r not in self.active or r.status != "decode":
+                continue                               # ended or cancelled since the step was launched
+            r.cursor += 1
+            decoded += 1
+            r.generated.append(int(token))
+            r.token_times.append(completed)
+            if len(r.generated) >= r.max_new_tokens or int(token) in r.eos_ids():
+                self._finish(r)
+        self.trace.append({"elapsed_s": time.perf_counter() - self.start, "step_s": time.perf_counter() - began,
+                           "processed_tokens": decoded, "prefill_tokens": 0, "decode_tokens": decoded,
+                           "active": len(self.active), "resident_pages": self._resident_pages()})
+        if ahead is not None:
+            self._deferred = (reqs, ahead, completed)
+        return bool(self.active or self.waiting or self._deferred)
+
     def tick(self) -> bool:
+        if self._deferred is not None:
+            return self._tick_deferred()
         self._admit()
         if not self.active:
             return bool(self.waiting)
@@ -237,6 +277,12 @@ class Engine:
                 if self.reserve != "lazy" or len(self.active) <= 1:
                     raise
                 self._preempt(self.active[-1])
+        can_ahead = getattr(self.stepper, "can_run_ahead", None)
+        if (self.lookahead and can_ahead is not None and can_ahead() and len(choosing) == len(plan)
+                and all(r.status == "decode" for r in choosing)):
+            # a pure decode step from a graph: leave its tokens on the device until the next tick
+            self._deferred = (list(choosing), self.stepper.last_tokens, began)
+            return True
         chosen = self.choose(logits, choosing) if choosing else []
         check = getattr(self.stepper, "check_kernels", None)
         if check is not None:

@@ -181,7 +181,8 @@ class Stepper:
             graph.capture()
         graph.replay()
         commit_step(cache, entries)
-        self.last_context, self.last_extras, self.last_tokens = None, {}, graph.tokens[:n]
+        self.last_context, self.last_extras = None, {}
+        self.last_tokens = graph.tokens[:n].clone()       # a later replay overwrites the graph's own buffer
         self._ahead = (graph, [e.key for e in entries])
         return graph.logits[:n]
 
@@ -202,18 +203,17 @@ class Stepper:
             return torch.empty((0, len(keys)), dtype=torch.int32, device=self.model.device)
         cache.reserve([(k, steps) for k in keys])
         device = self.model.device
-        for g in cache.page_groups:
-            idx, val = cache.drain_table_updates(g.index)
-            if idx.size:
-                kernels.table_update(g.device_table, torch.from_numpy(idx).to(device), torch.from_numpy(val).to(device))
-        run_page_copies(cache, device)
-        for g in cache.page_groups:   # the tables are up to date: the graph's own update lists must do nothing
-            graph.d(f"upd_idx{g.index}").fill_(-1)
+        # new pages reach the device through the graph's own update lists (a pinned copy that does not wait for the step
+        # in flight); applying the same list again in the later replays of this call changes nothing
+        graph.upload_updates(self._flush_tables(graph.n_updates))
         history = torch.empty((steps, graph.rows), dtype=torch.int32, device=device)
         for i in range(steps):
             graph.replay()
             history[i].copy_(graph.tokens, non_blocking=True)
         for k in keys:
             cache.commit(k, steps)
-        self.last_tokens = graph.tokens[:len(keys)]
+        self.last_tokens = history[steps - 1, :len(keys)]
         return history[:, :len(keys)]
+
+    def can_run_ahead(self) -> bool:
+        return self._ahead is not None

@@ -175,3 +175,74 @@ def test_invalid_limits_are_refused():
     for kw in (dict(max_active=0), dict(token_budget=0), dict(prefill_chunk=0), dict(policy="fifo"), dict(reserve="none")):
         with pytest.raises(ValueError):
             engine(**kw)
+
+
+class AheadStepper(HostStepper):
+    """A stand-in whose decode steps can run one step ahead of the host, as the graph path does: the tokens a step chose
+    stay "on the device" (a tensor) and the next step feeds them back by itself."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self._batch = None
+        self.last_tokens = None
+        self.ahead_calls = 0
+
+    def _choose(self, key):
+        return hashlib.sha256(repr(self.history[key]).encode()).digest()[0] % VOCAB
+
+    def step(self, entries, extra=None):
+        import torch
+        logits = super().step(entries, extra)
+        self._batch = None
+        if all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            self._batch = [e.key for e in entries]
+            self.last_tokens = torch.tensor(np.argmax(logits, axis=-1))
+        return logits
+
+    def can_run_ahead(self):
+        return self._batch is not None
+
+    def check_kernels(self):
+        pass
+
+    def decode_ahead(self, steps):
+        import torch
+        assert steps == 1
+        self.ahead_calls += 1
+        self.cache.reserve([(k, 1) for k in self._batch])
+        out = []
+        for k in self._batch:
+            self.history[k].append(self._pending_token(k))
+            self.cache.commit(k, 1)
+            out.append(self._choose(k))
+        self.last_tokens = torch.tensor(out)
+        return torch.tensor([out])
+
+    def _pending_token(self, key):
+        # the token the step before chose for this request: the hash of its history as that step saw it
+        return hashlib.sha256(repr(self.history[key]).encode()).digest()[0] % VOCAB
+
+
+def test_lookahead_runs_the_next_decode_step_before_reading_the_last_and_drops_what_an_eos_made_useless():
+    prompts = {"a": [1, 2, 3], "b": [9], "c": list(range(5))}
+    plain, _ = engine(token_budget=16, prefill_chunk=16)
+    for k, p in prompts.items():
+        plain.submit(Request(k, p, 9))
+    want = {r.key: r.generated for r in plain.run()}
+    eos = want["b"][4]
+    cut = {k: (v[:v.index(eos) + 1] if eos in v else v) for k, v in want.items()}
+
+    stepper = AheadStepper()
+    e = Engine(stepper, choose, VOCAB, stepper.cache.max_positions, token_budget=16, prefill_chunk=16, lookahead=True)
+    for k, p in prompts.items():
+        e.submit(Request(k, p, 9))
+    assert {r.key: r.generated for r in e.run()} == want and stepper.ahead_calls >= 5
+
+    stepper = AheadStepper()
+    e = Engine(stepper, choose, VOCAB, stepper.cache.max_positions, token_budget=16, prefill_chunk=16, lookahead=True)
+    for k, p in prompts.items():
+        e.submit(Request(k, p, 9, eos_token_id=eos))
+    done = {r.key: r for r in e.run()}
+    assert {k: r.generated for k, r in done.items()} == cut
+    assert all(r.status == "finished" for r in done.values())
+    assert stepper.cache.page_groups[0].pool.n_free == 16 and not stepper.cache.requests
