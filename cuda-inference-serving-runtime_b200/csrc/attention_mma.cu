@@ -333,8 +333,10 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
     float* merge = reinterpret_cast<float*>(pipe);                   // reused after the loop: [4][16][D + 2]
     int* pages = reinterpret_cast<int*>(smem_raw + DEC_SMEM);        // block table entries of this CTA's key range
 
+    // Under programmatic dependent launch everything up to pdl_wait() overlaps the kernel before this one (the q/k/v
+    // projection of the same layer).  That kernel writes only this step's token: the query, and the key and value at
+    // position ctx - 1.  Request metadata, block tables and all older keys and values are safe to read before the wait.
     pdl_trigger();
-    pdl_wait();      // the keys and values of this step's token were written by the kernel before
     const int group = hq / hkv;
     const int rows = min(16, group - row0);                          // query heads of the group handled by this launch
     const int slot = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -349,28 +351,46 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
     if (window > 0) lo = max(lo, ctx - window);
     const size_t part_base = ((size_t)slot * hq + (size_t)kvh * group + row0) * n_splits;
     if (lo >= hi) {      // nothing in this range (the same for every thread): the merge skips a zero denominator
+        pdl_wait();
         for (int g = tid; g < rows; g += DEC_THREADS) {
             const size_t p = part_base + (size_t)g * n_splits + split;
             stats[2 * p] = -INFINITY; stats[2 * p + 1] = 0.f;
         }
         return;
     }
+    const int n_tiles = (hi - lo + BN - 1) / BN;
+    const int first_page = lo / page_size;
+    for (int i = tid; i <= (hi - 1) / page_size - first_page; i += DEC_THREADS) pages[i] = table[first_page + i];
+    __syncthreads();
+    // the first tiles can start early unless they hold the newest key
+    const bool early = !(hi == ctx && ctx - 1 < lo + (STAGES - 1) * BN);
+    if (early) {
+#pragma unroll
+        for (int st = 0; st < STAGES - 1; ++st) {
+            if (st < n_tiles) {
+                bf16* Kt = pipe + st * 2 * BN * LDS;
+                load_kv_tile<DEC_THREADS>(Kt, Kt + BN * LDS, k_cache, v_cache, pages, first_page, lo + st * BN, hi, hkv, kvh, page_size, tid);
+            }
+            cp_async_commit();
+        }
+    }
+    pdl_wait();
     for (int c = tid; c < 16 * CHUNKS; c += DEC_THREADS) {
         const int r = c / CHUNKS, ch = c - r * CHUNKS;
         const bool ok = r < rows;
         cp_async16(Qs + r * LDS + ch * 8, q + ((size_t)tok * hq + kvh * group + row0 + (ok ? r : 0)) * D + ch * 8, ok);
     }
-    const int n_tiles = (hi - lo + BN - 1) / BN;
-    const int first_page = lo / page_size;
-    for (int i = tid; i <= (hi - 1) / page_size - first_page; i += DEC_THREADS) pages[i] = table[first_page + i];
-    __syncthreads();
+    if (early) {
+        cp_async_commit();           // the query is a group of its own, behind the early tiles
+    } else {
 #pragma unroll
-    for (int st = 0; st < STAGES - 1; ++st) {
-        if (st < n_tiles) {
-            bf16* Kt = pipe + st * 2 * BN * LDS;
-            load_kv_tile<DEC_THREADS>(Kt, Kt + BN * LDS, k_cache, v_cache, pages, first_page, lo + st * BN, hi, hkv, kvh, page_size, tid);
+        for (int st = 0; st < STAGES - 1; ++st) {
+            if (st < n_tiles) {
+                bf16* Kt = pipe + st * 2 * BN * LDS;
+                load_kv_tile<DEC_THREADS>(Kt, Kt + BN * LDS, k_cache, v_cache, pages, first_page, lo + st * BN, hi, hkv, kvh, page_size, tid);
+            }
+            cp_async_commit();       // the query travels in the first tile's group
         }
-        cp_async_commit();
     }
 
     uint32_t qf[KD][4];
@@ -381,7 +401,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
     const float scale2 = scale * LOG2E;
 
     for (int t = 0; t < n_tiles; ++t) {
-        cp_async_wait<STAGES - 2>();
+        if (t == 0 && early) cp_async_wait<0>();       // the early tiles and the query, all issued long ago
+        else cp_async_wait<STAGES - 2>();
         __syncthreads();
         {
             const int nt = t + STAGES - 1;
@@ -489,13 +510,13 @@ __global__ void attn_merge_kernel(const float* __restrict__ partial, const float
                                   bf16* __restrict__ out, const int* __restrict__ dec_req,
                                   const int* __restrict__ q_start, int hq, int n_splits) {
     pdl_trigger();
-    pdl_wait();
     const int slot = blockIdx.x, head = blockIdx.y;
     const size_t base = ((size_t)slot * hq + head) * n_splits;
+    const int tok = q_start[dec_req[slot]];       // request metadata does not come from the kernel before
+    pdl_wait();
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s)
         if (stats[2 * (base + s) + 1] > 0.f) m = fmaxf(m, stats[2 * (base + s)]);
-    const int tok = q_start[dec_req[slot]];
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float num = 0.f, den = 0.f;
         for (int s = 0; s < n_splits; ++s) {

@@ -142,6 +142,14 @@ __global__ void __launch_bounds__(512) skinny_kernel(const SkinnyArgs a) {
         if (in_k && ok_lo) wl[i] = load_weights(row_lo + c * 32);
         if (in_k && ok_hi) wh[i] = load_weights(row_hi + c * 32);
     }
+    // ROPE: where each token's key and value go is known from the step's metadata and the block table, which the
+    // kernel before this one does not write: look it up now, three dependent loads off the path after the wait
+    __shared__ long long cache_row[MT * 8];
+    if (EPI == EPI_ROPE && tid < a.m) {
+        const int pos = a.positions[tid];
+        const int page = a.block_table[(size_t)a.req_slot[a.token_req[tid]] * a.table_width + pos / a.page_size];
+        cache_row[tid] = page < 0 ? -1 : (long long)page * a.hkv * a.page_size + pos % a.page_size;
+    }
     pdl_trigger();
     pdl_wait();
 
@@ -235,11 +243,10 @@ __global__ void __launch_bounds__(512) skinny_kernel(const SkinnyArgs a) {
             if (is_q) {
                 a.q_out[((size_t)mrow * a.hq + hh) * dim + d] = __float2bfloat16_rn(v);
             } else {
-                const int pos = a.positions[mrow];
-                const int page = a.block_table[(size_t)a.req_slot[a.token_req[mrow]] * a.table_width + pos / a.page_size];
-                if (page < 0) continue;      // a padding row: its slot holds no pages
+                const long long at = cache_row[mrow];     // page * hkv * page_size + offset in the page
+                if (at < 0) continue;                      // a padding row: its slot holds no pages
                 const int kvh = is_k ? hh - a.hq : hh - a.hq - a.hkv;
-                const size_t dst = (((size_t)page * a.hkv + kvh) * a.page_size + pos % a.page_size) * dim + d;
+                const size_t dst = ((size_t)at + (size_t)kvh * a.page_size) * dim + d;
                 (is_k ? a.k_cache : a.v_cache)[dst] = __float2bfloat16_rn(v);
             }
         }
