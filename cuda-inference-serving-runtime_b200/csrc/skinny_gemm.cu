@@ -31,7 +31,13 @@
 namespace {
 typedef __nv_bfloat16 bf16;
 enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ROPE = 2 };
-constexpr int MAXC = 6;     // chunks of 32 k whose weights a warp holds in registers at once
+#ifndef SKINNY_MAXC
+#define SKINNY_MAXC 6
+#endif
+#ifndef SKINNY_KS
+#define SKINNY_KS 8
+#endif
+constexpr int MAXC = SKINNY_MAXC;     // chunks of 32 k whose weights a warp holds in registers at once
 bool g_pdl = false;
 
 struct SkinnyArgs {
@@ -257,8 +263,8 @@ template <int MT, int EPI>
 int launch_epilogue(SkinnyArgs& a, cudaStream_t s) {
     int grid;
     if (EPI == EPI_ROPE) { a.rt = a.dim / 16; a.ks = max(1, min(4, 16 / a.rt)); grid = a.hq + 2 * a.hkv; }   // at most 512 threads
-    else if (EPI == EPI_SWIGLU) { a.rt = 1; a.ks = 8; grid = (a.inter + 7) / 8; }
-    else if (MT <= 2) { a.rt = 1; a.ks = 8; grid = (a.n + 15) / 16; }
+    else if (EPI == EPI_SWIGLU) { a.rt = 1; a.ks = SKINNY_KS; grid = (a.inter + 7) / 8; }
+    else if (MT <= 2) { a.rt = 1; a.ks = SKINNY_KS; grid = (a.n + 15) / 16; }
     else { a.rt = 4; a.ks = 2; grid = (a.n + 63) / 64; }       // more tokens: stage them once per 64 features
     size_t smem = sizeof(bf16) * (size_t)(MT * 8) * (a.k + 8) + sizeof(float) * (size_t)a.ks * a.rt * 16 * MT * 8;
     if (smem > 220 * 1024 && a.ks > 1 && EPI == EPI_PLAIN) {   // long rows and many tokens: give up the K split for room

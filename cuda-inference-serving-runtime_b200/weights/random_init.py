@@ -19,7 +19,7 @@ from ..parts.base import TensorNeed
 
 MATRIX_STD = 0.02
 VECTOR_STD = 0.1
-DEVICE_DRAW_THRESHOLD = 1 << 26   # tensors above this many elements are drawn on the device
+DEVICE_DRAW_THRESHOLD = 1 << 22   # tensors above this many elements are drawn on the device
 
 
 def _tensor_seed(seed: int, name: str) -> int:
