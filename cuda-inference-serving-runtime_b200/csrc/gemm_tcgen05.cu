@@ -126,172 +126,200 @@ struct Smem {
     static constexpr size_t TOTAL = TILES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
+// The epilogue of one output tile for one thread: `row` is the thread's output row, `lane_base` the tensor-memory
+// address of its lane in the tile's accumulator, n0 the tile's first column (feature).
+template <int BN, int EPI>
+__device__ __forceinline__ void epilogue_tile(const Epilogue& ep, uint32_t lane_base, int row, int m, int n, int n0) {
+    if (EPI == EPI_PLAIN) {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+            uint32_t v[32];
+            tmem_load32(lane_base + (uint32_t)c, v);
+            if (row < m) {
+                float* dst = ep.out_f32 + (size_t)row * n + n0 + c;
+                if (n0 + c + 32 <= n && (n & 3) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                          __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (n0 + c + j < n) dst[j] = __uint_as_float(v[j]);
+                }
+            }
+        }
+    } else if (EPI == EPI_SWIGLU) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+            uint32_t g[32], u[32];
+            tmem_load32(lane_base + (uint32_t)c, g);
+            tmem_load32(lane_base + (uint32_t)(BN / 2 + c), u);
+            float act[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float gv = __uint_as_float(g[j]);
+                act[j] = gv / (1.f + expf(-gv)) * __uint_as_float(u[j]);
+            }
+            if (row < m && n0 + c < ep.inter)
+                store_bf16x32(ep.out_bf16 + (size_t)row * ep.inter + n0 + c, act, ep.inter - (n0 + c));
+        }
+    } else {
+        // whole heads of the stacked q, k, v projection: BN / dim heads per tile, rotation pairs (i, i + dim / 2)
+        const int dim = ep.dim, half = dim / 2;
+        int pos = 0, page = -1;
+        if (row < m) {
+            pos = ep.positions[row];
+            page = ep.block_table[(size_t)ep.req_slot[ep.token_req[row]] * ep.table_width + pos / ep.page_size];
+        }
+#pragma unroll 1
+        for (int h0 = 0; h0 < BN; h0 += dim) {
+            const int hh = (n0 + h0) / dim;                        // head index in the stacked projection
+            if (hh >= ep.hq + 2 * ep.hkv) break;
+            const bool is_q = hh < ep.hq, is_k = !is_q && hh < ep.hq + ep.hkv;
+            bf16* dst = nullptr;
+            if (row < m) {
+                if (is_q) dst = ep.q_out + ((size_t)row * ep.hq + hh) * dim;
+                else if (page >= 0) {                               // a missing page entry: a padding row, nothing to write
+                    const int kvh = is_k ? hh - ep.hq : hh - ep.hq - ep.hkv;
+                    dst = (is_k ? ep.k_cache : ep.v_cache) +
+                          (((size_t)page * ep.hkv + kvh) * ep.page_size + pos % ep.page_size) * dim;
+                }
+            }
+#pragma unroll 1
+            for (int c = 0; c < half; c += 32) {
+                uint32_t lo[32], hi[32];
+                tmem_load32(lane_base + (uint32_t)(h0 + c), lo);
+                tmem_load32(lane_base + (uint32_t)(h0 + half + c), hi);
+                float first[32], second[32];
+                if ((is_q || is_k) && row < m) {
+                    const float4* cs = reinterpret_cast<const float4*>(ep.cos_t + (size_t)row * half + c);   // half is a multiple of 32
+                    const float4* sn = reinterpret_cast<const float4*>(ep.sin_t + (size_t)row * half + c);
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 cv = cs[j >> 2], sv = sn[j >> 2];
+                        const float cc[4] = {cv.x, cv.y, cv.z, cv.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const float a = __uint_as_float(lo[j + u]), b = __uint_as_float(hi[j + u]);
+                            first[j + u] = a * cc[u] - b * ss[u];
+                            second[j + u] = b * cc[u] + a * ss[u];
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) { first[j] = __uint_as_float(lo[j]); second[j] = __uint_as_float(hi[j]); }
+                }
+                if (dst) {
+                    store_bf16x32(dst + c, first, 32);
+                    store_bf16x32(dst + half + c, second, 32);
+                }
+            }
+        }
+    }
+}
+
+// Persistent: a CTA walks output tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the accumulator is double-buffered in
+// tensor memory, so the MMA thread fills one buffer while the epilogue warps drain the other.
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const Epilogue ep, int m, int n, int k, int* __restrict__ error) {
+                    const Epilogue ep, int m, int n, int k, int tiles_m, int tiles_n, int* __restrict__ error) {
     extern __shared__ unsigned char smem_raw[];
     typedef Smem<BN, STAGES> S;
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024-byte aligned
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + S::TILES);
     uint64_t* empty_bar = full_bar + STAGES;
-    uint64_t* acc_bar = empty_bar + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+    uint64_t* acc_full = empty_bar + STAGES;       // [2]: the MMAs of a tile are done
+    uint64_t* acc_empty = acc_full + 2;            // [2]: the epilogue has read the buffer
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // SWIGLU: the tile's 128 accumulator columns are 64 gate features and the 64 up features of the same indices
-    const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? BN / 2 : BN), m0 = blockIdx.y * BM;
     const int k_blocks = (k + BK - 1) / BK;
+    const int total_tiles = tiles_m * tiles_n;
+    constexpr int TILE_N = EPI == EPI_SWIGLU ? BN / 2 : BN;   // SWIGLU: 128 accumulator columns are 64 gate + 64 up features
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
-        mbar_init(acc_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {    // one warp allocates the accumulator's columns of tensor memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    if (warp == 1) {    // one warp allocates two accumulators' columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
-    const uint32_t tmem_acc = *tmem_slot;
+    const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(empty_bar + s, ((kb / STAGES) & 1) ^ 1);      // the MMAs that read this stage are done
-                if (!ok) break;
-                mbar_expect_tx(full_bar + s, (uint32_t)(S::A_BYTES + S::B_BYTES));
-                tma_load_2d(tiles + s * (S::A_BYTES + S::B_BYTES), &map_a, kb * BK, m0, full_bar + s);
-                unsigned char* b_tile = tiles + s * (S::A_BYTES + S::B_BYTES) + S::A_BYTES;
-                if (EPI == EPI_SWIGLU) {      // two boxes of 64 rows: gate rows n0.., up rows inter + n0..
-                    tma_load_2d(b_tile, &map_w, kb * BK, n0, full_bar + s);
-                    tma_load_2d(b_tile + S::B_BYTES / 2, &map_w, kb * BK, ep.inter + n0, full_bar + s);
-                } else {
-                    tma_load_2d(b_tile, &map_w, kb * BK, n0, full_bar + s);
+            int kbg = 0;                                                      // k blocks issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;   // neighbours share the weight tile
+                for (int kb = 0; kb < k_blocks; ++kb, ++kbg) {
+                    const int s = kbg % STAGES;
+                    ok = mbar_wait(empty_bar + s, ((kbg / STAGES) & 1) ^ 1);  // the MMAs that read this stage are done
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar + s, (uint32_t)(S::A_BYTES + S::B_BYTES));
+                    tma_load_2d(tiles + s * (S::A_BYTES + S::B_BYTES), &map_a, kb * BK, m0, full_bar + s);
+                    unsigned char* b_tile = tiles + s * (S::A_BYTES + S::B_BYTES) + S::A_BYTES;
+                    if (EPI == EPI_SWIGLU) {      // two boxes of BN/2 rows: gate rows n0.., up rows inter + n0..
+                        tma_load_2d(b_tile, &map_w, kb * BK, n0, full_bar + s);
+                        tma_load_2d(b_tile + S::B_BYTES / 2, &map_w, kb * BK, ep.inter + n0, full_bar + s);
+                    } else {
+                        tma_load_2d(b_tile, &map_w, kb * BK, n0, full_bar + s);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(BN);
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(full_bar + s, (kb / STAGES) & 1);              // both tiles of this stage have landed
+            int kbg = 0, it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+                const int acc = it & 1;
+                ok = mbar_wait(acc_empty + acc, ((it >> 1) & 1) ^ 1);          // the epilogue has drained this buffer
                 if (!ok) break;
                 tcgen05_fence_after();
-                const uint64_t desc_a = umma_desc(tiles + s * (S::A_BYTES + S::B_BYTES));
-                const uint64_t desc_b = umma_desc(tiles + s * (S::A_BYTES + S::B_BYTES) + S::A_BYTES);
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++kbg) {
+                    const int s = kbg % STAGES;
+                    ok = mbar_wait(full_bar + s, (kbg / STAGES) & 1);          // both tiles of this stage have landed
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint64_t desc_a = umma_desc(tiles + s * (S::A_BYTES + S::B_BYTES));
+                    const uint64_t desc_b = umma_desc(tiles + s * (S::A_BYTES + S::B_BYTES) + S::A_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < BK / UMMA_K; ++kk)                        // 32 bytes further along K per step
-                    umma_bf16(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kb | kk) != 0);
-                umma_commit(empty_bar + s);                                    // frees the stage when these MMAs finish
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk)                    // 32 bytes further along K per step
+                        umma_bf16(tmem_acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (kb | kk) != 0);
+                    umma_commit(empty_bar + s);                                // frees the stage when these MMAs finish
+                }
+                if (ok) umma_commit(acc_full + acc);                           // the whole tile is accumulated
             }
-            if (ok) umma_commit(acc_bar);                                      // the whole tile is accumulated
         }
     } else {
-        ok = mbar_wait(acc_bar, 0);
-        tcgen05_fence_after();
-        if (ok) {
-            const int quarter = warp & 3;                                      // the 32 lanes this warp may read
-            const int row = m0 + quarter * 32 + lane;
-            const uint32_t lane_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
-            if (EPI == EPI_PLAIN) {
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
-                    uint32_t v[32];
-                    tmem_load32(lane_base + (uint32_t)c, v);
-                    if (row < m) {
-                        float* dst = ep.out_f32 + (size_t)row * n + n0 + c;
-                        if (n0 + c + 32 <= n && (n & 3) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                                                  __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (n0 + c + j < n) dst[j] = __uint_as_float(v[j]);
-                        }
-                    }
-                }
-            } else if (EPI == EPI_SWIGLU) {
-#pragma unroll 1
-                for (int c = 0; c < BN / 2; c += 32) {
-                    uint32_t g[32], u[32];
-                    tmem_load32(lane_base + (uint32_t)c, g);
-                    tmem_load32(lane_base + (uint32_t)(BN / 2 + c), u);
-                    float act[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float gv = __uint_as_float(g[j]);
-                        act[j] = gv / (1.f + expf(-gv)) * __uint_as_float(u[j]);
-                    }
-                    if (row < m && n0 + c < ep.inter)
-                        store_bf16x32(ep.out_bf16 + (size_t)row * ep.inter + n0 + c, act, ep.inter - (n0 + c));
-                }
-            } else {
-                // whole heads of the stacked q, k, v projection: BN / dim heads per tile, rotation pairs (i, i + dim / 2)
-                const int dim = ep.dim, half = dim / 2;
-                int pos = 0, page = -1;
-                if (row < m) {
-                    pos = ep.positions[row];
-                    page = ep.block_table[(size_t)ep.req_slot[ep.token_req[row]] * ep.table_width + pos / ep.page_size];
-                }
-#pragma unroll 1
-                for (int h0 = 0; h0 < BN; h0 += dim) {
-                    const int hh = (n0 + h0) / dim;                        // head index in the stacked projection
-                    if (hh >= ep.hq + 2 * ep.hkv) break;
-                    const bool is_q = hh < ep.hq, is_k = !is_q && hh < ep.hq + ep.hkv;
-                    bf16* dst = nullptr;
-                    if (row < m) {
-                        if (is_q) dst = ep.q_out + ((size_t)row * ep.hq + hh) * dim;
-                        else if (page >= 0) {                               // a missing page entry: a padding row, nothing to write
-                            const int kvh = is_k ? hh - ep.hq : hh - ep.hq - ep.hkv;
-                            dst = (is_k ? ep.k_cache : ep.v_cache) +
-                                  (((size_t)page * ep.hkv + kvh) * ep.page_size + pos % ep.page_size) * dim;
-                        }
-                    }
-#pragma unroll 1
-                    for (int c = 0; c < half; c += 32) {
-                        uint32_t lo[32], hi[32];
-                        tmem_load32(lane_base + (uint32_t)(h0 + c), lo);
-                        tmem_load32(lane_base + (uint32_t)(h0 + half + c), hi);
-                        float first[32], second[32];
-                        if ((is_q || is_k) && row < m) {
-                            const float4* cs = reinterpret_cast<const float4*>(ep.cos_t + (size_t)row * half + c);   // half is a multiple of 32
-                            const float4* sn = reinterpret_cast<const float4*>(ep.sin_t + (size_t)row * half + c);
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                const float4 cv = cs[j >> 2], sv = sn[j >> 2];
-                                const float cc[4] = {cv.x, cv.y, cv.z, cv.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
-#pragma unroll
-                                for (int u = 0; u < 4; ++u) {
-                                    const float a = __uint_as_float(lo[j + u]), b = __uint_as_float(hi[j + u]);
-                                    first[j + u] = a * cc[u] - b * ss[u];
-                                    second[j + u] = b * cc[u] + a * ss[u];
-                                }
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) { first[j] = __uint_as_float(lo[j]); second[j] = __uint_as_float(hi[j]); }
-                        }
-                        if (dst) {
-                            store_bf16x32(dst + c, first, 32);
-                            store_bf16x32(dst + half + c, second, 32);
-                        }
-                    }
-                }
-            }
+        const int quarter = warp & 3;                                          // the 32 lanes this warp may read
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            const int acc = it & 1;
+            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
+            ok = mbar_wait(acc_full + acc, (it >> 1) & 1);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t lane_base = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
+            epilogue_tile<BN, EPI>(ep, lane_base, m0 + quarter * 32 + lane, m, n, n0);
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(acc_empty + acc)) : "memory");
         }
     }
     if (!ok && lane == 0) atomicExch(error, 1);
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(BN) : "memory");
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
 }
 
 // ---------------------------------------------------------------- host side
@@ -338,7 +366,7 @@ int cached_map(const CUtensorMap** out, const void* base, int rows, int cols, in
 }
 
 template <int BN, int STAGES, int EPI>
-int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k, int grid_x, cudaStream_t s) {
+int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k, int tiles_n, cudaStream_t s) {
     const CUtensorMap *map_a, *map_w;
     int status = cached_map(&map_a, a, m, k, BM);
     if (status) return status;
@@ -350,9 +378,25 @@ int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_tcgen05_kernel<BN, STAGES, EPI><<<dim3(grid_x, (m + BM - 1) / BM), 192, S::TOTAL, s>>>(*map_a, *map_w, ep, m, n, k, g_error);
+    static int slots = 0;                        // CTAs that fit on the device at once
+    if (!slots) {
+        int device = 0, sms = 0, per_sm = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tcgen05_kernel<BN, STAGES, EPI>, 192, S::TOTAL);
+        per_sm = per_sm < 1 ? 1 : per_sm;
+        if (per_sm * 2 * BN > 512) per_sm = 512 / (2 * BN);      // tensor memory: 512 columns per SM
+        slots = sms * per_sm;
+    }
+    const int tiles_m = (m + BM - 1) / BM, total = tiles_m * tiles_n;
+    gemm_tcgen05_kernel<BN, STAGES, EPI><<<total < slots ? total : slots, 192, S::TOTAL, s>>>(*map_a, *map_w, ep, m, n, k, tiles_m,
+                                                                                      tiles_n, g_error);
     return launch_status();
 }
+
+// 128 x 256 tiles read a third less from L2 per flop than 128 x 128; worth it once there are enough of them to
+// occupy most of the device (one CTA per SM at that size).
+bool wide_tiles(int m, int tiles_n256) { return (long long)((m + BM - 1) / BM) * tiles_n256 >= 120; }
 
 bool operands_ok(const void* a, const void* w, int k) {
     return g_encode && g_error && k > 0 && k % 8 == 0 && !(((uintptr_t)a | (uintptr_t)w) & 15);
@@ -382,6 +426,7 @@ CISR_EXPORT int cisr_gemm_tcgen05(const void* a, const void* w, float* out, int 
     ep.out_f32 = out;
     cudaStream_t s = (cudaStream_t)stream;
     if (n <= 64) return launch<64, 4, EPI_PLAIN>(a, w, ep, m, n, k, (n + 63) / 64, s);
+    if (wide_tiles(m, (n + 255) / 256)) return launch<256, 4, EPI_PLAIN>(a, w, ep, m, n, k, (n + 255) / 256, s);
     return launch<128, 3, EPI_PLAIN>(a, w, ep, m, n, k, (n + 127) / 128, s);
 }
 
@@ -392,6 +437,8 @@ CISR_EXPORT int cisr_gemm_tcgen05_swiglu(const void* a, const void* w, void* out
     if (!operands_ok(a, w, k)) return -2;
     Epilogue ep = {};
     ep.out_bf16 = (bf16*)out; ep.inter = inter;
+    if (wide_tiles(m, (inter + 127) / 128))
+        return launch<256, 4, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 127) / 128, (cudaStream_t)stream);
     return launch<128, 3, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 63) / 64, (cudaStream_t)stream);
 }
 
@@ -410,5 +457,6 @@ CISR_EXPORT int cisr_gemm_tcgen05_rope(const void* a, const void* w, int m, int 
     ep.positions = positions; ep.token_req = token_req; ep.req_slot = req_slot; ep.block_table = block_table;
     ep.table_width = table_width; ep.page_size = page_size; ep.hq = hq; ep.hkv = hkv; ep.dim = dim;
     const int n = (hq + 2 * hkv) * dim;
+    if (wide_tiles(m, (n + 255) / 256)) return launch<256, 4, EPI_ROPE>(a, w, ep, m, n, k, (n + 255) / 256, (cudaStream_t)stream);
     return launch<128, 3, EPI_ROPE>(a, w, ep, m, n, k, (n + 127) / 128, (cudaStream_t)stream);
 }
