@@ -101,7 +101,12 @@ constexpr int BM = 64;
 constexpr int NG = PREFILL_GROUPS;
 constexpr int PREFILL_THREADS = 128 * NG;
 constexpr size_t PREFILL_MERGE_BYTES = sizeof(float) * (size_t)(NG - 1) * BM * (D + 2);
-constexpr size_t PREFILL_PIPE_BYTES = sizeof(bf16) * (size_t)(NG * 4 * BN * LDS);
+#ifndef PREFILL_BUFS
+#define PREFILL_BUFS 2
+#endif
+constexpr int NB = PREFILL_BUFS;       // key/value buffers per group: 2 overlaps a group's own loads with its math; 1 halves
+                                       // the shared memory so two CTAs fit an SM and overlap each other instead
+constexpr size_t PREFILL_PIPE_BYTES = sizeof(bf16) * (size_t)(NG * NB * 2 * BN * LDS);
 constexpr size_t PREFILL_SMEM = ((sizeof(bf16) * (size_t)(BM * LDS) +
                                   (PREFILL_PIPE_BYTES > PREFILL_MERGE_BYTES ? PREFILL_PIPE_BYTES : PREFILL_MERGE_BYTES) + 15) / 16) * 16;
 
@@ -156,7 +161,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
     for (int i = 0; i < ND; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     const float scale2 = scale * LOG2E;
 
-    bf16* gbuf = pipe + (size_t)group * 4 * BN * LDS;      // this group's two [K tile | V tile] buffers
+    bf16* gbuf = pipe + (size_t)group * NB * 2 * BN * LDS;      // this group's [K tile | V tile] buffers
     if (group < n_tiles)
         load_kv_tile<128>(gbuf, gbuf + BN * LDS, k_cache, v_cache, pages, first_page, k_begin + group * BN, k_end, hkv, kvh,
                           page_size, gtid);
@@ -164,10 +169,10 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
 
     for (int t = group, it = 0; t < n_tiles; t += NG, ++it) {
         const int k0 = k_begin + t * BN;
-        const int buf = it & 1;
+        const int buf = NB == 2 ? (it & 1) : 0;
         cp_async_wait<0>();
         group_sync(group);                    // tile t has landed; the group is done with the other buffer
-        if (t + NG < n_tiles) {
+        if (NB == 2 && t + NG < n_tiles) {
             bf16* nb = gbuf + (buf ^ 1) * 2 * BN * LDS;
             load_kv_tile<128>(nb, nb + BN * LDS, k_cache, v_cache, pages, first_page, k0 + NG * BN, k_end, hkv, kvh, page_size,
                               gtid);          // keys from k_end on are masked for every row
@@ -253,6 +258,11 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
                 mma_bf16(o[2 * dp], pa, b[0], b[1]);
                 mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
             }
+        }
+        if (NB == 1 && t + NG < n_tiles) {
+            group_sync(group);                // every warp of the group is done with the only buffer
+            load_kv_tile<128>(gbuf, gbuf + BN * LDS, k_cache, v_cache, pages, first_page, k0 + NG * BN, k_end, hkv, kvh, page_size, gtid);
+            cp_async_commit();
         }
     }
     cp_async_wait<0>();
