@@ -67,6 +67,7 @@ attn_prefill_kernel(const st_t* __restrict__ q, st_t* __restrict__ out, const st
                     const int* __restrict__ block_table, int table_width, const int* __restrict__ tile_req, const int* __restrict__ tile_q0,
                     const int* __restrict__ q_start, const int* __restrict__ q_len,
                     const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window) {
+    CISR_TRACE_SCOPE(TRACE_ATTN_SIMT);
     extern __shared__ __align__(16) float smem[];
     float* Qs = smem;             // [D][QS]   transposed, pre-scaled
     float* Ks = Qs + D * QS;      // [D][KS]   transposed
@@ -226,6 +227,7 @@ attn_decode_kernel(const st_t* __restrict__ q, const st_t* __restrict__ k_cache,
                    const int* __restrict__ q_start, const int* __restrict__ ctx_len, float* __restrict__ partial,
                    float* __restrict__ stats, int hq, int hkv, int page_size, float scale, int window,
                    int split_size, int n_splits) {
+    CISR_TRACE_SCOPE(TRACE_ATTN_SIMT);
     extern __shared__ __align__(16) float smem[];
     const int group = hq / hkv;
     float* qs = smem;                 // [group][D]
@@ -353,6 +355,7 @@ attn_decode_kernel(const st_t* __restrict__ q, const st_t* __restrict__ k_cache,
 __global__ void attn_merge_kernel(const float* __restrict__ partial, const float* __restrict__ stats,
                                   st_t* __restrict__ out, const int* __restrict__ dec_req,
                                   const int* __restrict__ q_start, int hq, int n_splits) {
+    CISR_TRACE_SCOPE(TRACE_ATTN_MERGE);
     const int slot = blockIdx.x, head = blockIdx.y;
     const size_t base = ((size_t)slot * hq + head) * n_splits;
     float m = -INFINITY;

@@ -24,6 +24,9 @@
 #if (HEAD_DIM % 16) || (HEAD_DIM > 128) || (HEAD_DIM < 16)
 #error "the tensor-core attention takes HEAD_DIM in multiples of 16 from 16 to 128"
 #endif
+#if HEAD_DIM % 64 == 0
+#include "tma.cuh"
+#endif
 
 namespace {
 typedef __nv_bfloat16 bf16;
@@ -118,12 +121,14 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ tile_req,
                         const int* __restrict__ tile_q0, const int* __restrict__ q_start, const int* __restrict__ q_len,
                         const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window) {
+    CISR_TRACE_SCOPE(TRACE_ATTN_PREFILL);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][LDS]
     bf16* pipe = Qs + BM * LDS;                     // [NG][2][K tile | V tile]
     float* merge = reinterpret_cast<float*>(pipe);  // reused after the loops: [NG - 1][BM][D + 2]
     int* pages = reinterpret_cast<int*>(smem_raw + PREFILL_SMEM);   // block table entries of this tile's key range
 
+    pdl_trigger();
     const int tile = blockIdx.x, head = blockIdx.y;
     const int req = tile_req[tile], q0 = tile_q0[tile];
     const int rows = min(BM, q_len[req] - q0);
@@ -134,6 +139,14 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
     const int* table = block_table + (size_t)req_slot[req] * table_width;
     const int tid = threadIdx.x, lane = tid & 31;
     const int group = tid >> 7, gtid = tid & 127, warp = gtid >> 5;     // warp: which 16 query rows, within the group
+    {   // the step's metadata and block tables are older than the kernel before this one: stage the pages ahead of the wait
+        const int k_end_ = qpos0 + rows;
+        const int k_begin_ = ((window > 0 ? max(0, qpos0 - window + 1) : 0) / BN) * BN;
+        const int first_page_ = k_begin_ / page_size;
+        for (int i = tid; i <= (k_end_ - 1) / page_size - first_page_; i += PREFILL_THREADS) pages[i] = table[first_page_ + i];
+    }
+    pdl_wait();          // the queries, and this step's keys and values, come from the kernel before
+    CISR_TRACE_WAITED();
 
     for (int c = tid; c < BM * CHUNKS; c += PREFILL_THREADS) {
         const int r = c / CHUNKS, ch = c - r * CHUNKS;
@@ -147,7 +160,6 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
     const int k_begin = (k_first / BN) * BN;
     const int n_tiles = (k_end - k_begin + BN - 1) / BN;
     const int first_page = k_begin / page_size;
-    for (int i = tid; i <= (k_end - 1) / page_size - first_page; i += PREFILL_THREADS) pages[i] = table[first_page + i];
     cp_async_wait<0>();
     __syncthreads();                              // Q and the page entries are in shared memory
 
@@ -331,12 +343,125 @@ constexpr size_t DEC_MERGE_BYTES = sizeof(float) * (size_t)(4 * 16 * (D + 2));
 constexpr size_t DEC_PIPE_BYTES = STAGES * DEC_TILE_BYTES > DEC_MERGE_BYTES ? STAGES * DEC_TILE_BYTES : DEC_MERGE_BYTES;
 constexpr size_t DEC_SMEM = ((sizeof(bf16) * (size_t)(16 * LDS) + DEC_PIPE_BYTES + 15) / 16) * 16;
 
+// Where 16-byte chunk `chunk` of key row `row` of a tile gathered by cp.async lies: rows LDS elements apart.
+struct PaddedTile {
+    const bf16* k; const bf16* v;
+    __device__ __forceinline__ const void* k_at(int row, int chunk) const { return k + row * LDS + chunk * 8; }
+    __device__ __forceinline__ const void* v_at(int row, int chunk) const { return v + row * LDS + chunk * 8; }
+};
+// A warp's share of one 64-key tile: its 16-key slab against the group's query rows, with the running softmax.
+// k0 is the position of the slab's first key; keys outside [lo, hi) are masked.
+template <typename Tile>
+__device__ __forceinline__ void decode_slab(const Tile& tile, const uint32_t (&qf)[KD][4], float (&o)[ND][4], float (&m_run)[2],
+                                            float (&l_run)[2], int k0, int lo, int hi, float scale2, int warp, int lane) {
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < KD; ++kk) {
+        uint32_t b[4];
+        ldmatrix_x4(b, tile.k_at(warp * 16 + (lane & 7) + 8 * (lane >> 4), kk * 2 + ((lane >> 3) & 1)));
+        mma_bf16(s[0], qf[kk], b[0], b[1]);
+        mma_bf16(s[1], qf[kk], b[2], b[3]);
+    }
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int kpos = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+            const float v = (kpos < hi && kpos >= lo) ? s[nt][e] * scale2 : -INFINITY;
+            s[nt][e] = v;
+            tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+        }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float mx = tile_max[h];
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[h], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[h] = exp2f(m_run[h] - m_use);
+        m_run[h] = m_new;
+        const float p0 = exp2f(s[0][2 * h] - m_use), p1 = exp2f(s[0][2 * h + 1] - m_use);
+        const float p2 = exp2f(s[1][2 * h] - m_use), p3 = exp2f(s[1][2 * h + 1] - m_use);
+        s[0][2 * h] = p0; s[0][2 * h + 1] = p1; s[1][2 * h] = p2; s[1][2 * h + 1] = p3;
+        l_run[h] = l_run[h] * alpha[h] + (p0 + p1 + p2 + p3);
+    }
+#pragma unroll
+    for (int i = 0; i < ND; ++i) { o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1]; }
+    uint32_t pa[4];
+    pa[0] = pack_bf16(s[0][0], s[0][1]); pa[1] = pack_bf16(s[0][2], s[0][3]);
+    pa[2] = pack_bf16(s[1][0], s[1][1]); pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+    for (int dp = 0; dp < ND / 2; ++dp) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, tile.v_at(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), dp * 2 + (lane >> 4)));
+        mma_bf16(o[2 * dp], pa, b[0], b[1]);
+        mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
+    }
+}
+
+// Each warp's result into the merge area: merge[warp][row][0..D) = unnormalised output, [D] = running max (base 2),
+// [D+1] = denominator.  `merge` is [4][16][D + 2] floats of shared memory that no warp still reads as a tile.
+__device__ __forceinline__ void warps_to_merge_area(float* merge, const float (&o)[ND][4], const float (&m_run)[2],
+                                                    const float (&l_run)[2], int warp, int lane, int rows) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float l = l_run[h];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = (lane >> 2) + 8 * h;
+        if (row >= rows) continue;                // a padding row of the 16-row tile: nobody reads it
+        float* dst = merge + ((size_t)warp * 16 + row) * (D + 2);
+#pragma unroll
+        for (int i = 0; i < ND; ++i) {
+            dst[i * 8 + 2 * (lane & 3)] = o[i][2 * h];
+            dst[i * 8 + 2 * (lane & 3) + 1] = o[i][2 * h + 1];
+        }
+        if ((lane & 3) == 0) { dst[D] = m_run[h]; dst[D + 1] = l; }
+    }
+}
+// Element d of query row g of the CTA: the four warps' results merged by log-sum-exp, in a fixed order.
+// Returns the numerator; m (base 2) and den are the row's running max and denominator.
+__device__ __forceinline__ float merged_element(const float* merge, int g, int d, float& m, float& den) {
+    m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, merge[((size_t)w * 16 + g) * (D + 2) + D]);
+    float num = 0.f;
+    den = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const float* src = merge + ((size_t)w * 16 + g) * (D + 2);
+        const float wgt = src[D] == -INFINITY ? 0.f : exp2f(src[D] - m);
+        num = fmaf(wgt, src[d], num);
+        den = fmaf(wgt, src[D + 1], den);
+    }
+    return num;
+}
+// The CTA's result written as its key range's partial sum (the merge kernel works in natural logarithms).
+__device__ __forceinline__ void decode_finish(float* merge, const float (&o)[ND][4], const float (&m_run)[2], const float (&l_run)[2],
+                                              float* __restrict__ partial, float* __restrict__ stats, size_t part_base,
+                                              int rows, int n_splits, int split, int tid) {
+    warps_to_merge_area(merge, o, m_run, l_run, tid >> 5, tid & 31, rows);
+    __syncthreads();
+    for (int e = tid; e < rows * D; e += DEC_THREADS) {
+        const int g = e / D, d = e - g * D;
+        float m, den;
+        const float num = merged_element(merge, g, d, m, den);
+        const size_t p = part_base + (size_t)g * n_splits + split;
+        partial[p * D + d] = num;
+        if (d == 0) { stats[2 * p] = m * LN2; stats[2 * p + 1] = den; }
+    }
+}
+
 __global__ void __launch_bounds__(DEC_THREADS)
 attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                        const int* __restrict__ req_slot, const int* __restrict__ block_table, int table_width,
                        const int* __restrict__ dec_req, const int* __restrict__ q_start, const int* __restrict__ ctx_len,
                        float* __restrict__ partial, float* __restrict__ stats, int hq, int hkv, int page_size,
                        float scale, int window, int split_size, int n_splits, int row0) {
+    CISR_TRACE_SCOPE(TRACE_ATTN_DECODE_GATHER);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                    // [16][LDS]
     bf16* pipe = Qs + 16 * LDS;                                      // [STAGES][K tile | V tile]
@@ -385,6 +510,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
         }
     }
     pdl_wait();
+    CISR_TRACE_WAITED();
     for (int c = tid; c < 16 * CHUNKS; c += DEC_THREADS) {
         const int r = c / CHUNKS, ch = c - r * CHUNKS;
         const bool ok = r < rows;
@@ -428,24 +554,234 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
                 ldmatrix_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
         }
         const bf16* Kt = pipe + (t % STAGES) * 2 * BN * LDS;
-        const bf16* Vt = Kt + BN * LDS;
-        const int k0 = lo + t * BN + warp * 16;        // this warp's 16-key slab of the tile
+        decode_slab(PaddedTile{Kt, Kt + BN * LDS}, qf, o, m_run, l_run, lo + t * BN + warp * 16, lo, hi, scale2, warp, lane);
+    }
+    cp_async_wait<0>();
+    __syncthreads();          // every warp is done with the pipeline buffers: they become the merge area
+    decode_finish(merge, o, m_run, l_run, partial, stats, part_base, rows, n_splits, split, tid);
+}
 
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#if HEAD_DIM % 64 == 0
+// ------------------------------------------------------------------ decode, tiles staged by tensor-map copies
+// The same result with another division of the work.  Each of the four warps owns whole tiles of TK keys (tiles
+// w, w + 4, ... of the CTA's key range) with its own running softmax, its own 16 KB stage of shared memory and its
+// own mbarrier; it requests its next tile itself as soon as it is done with the current one, so the loop has no
+// CTA-wide barrier, and the tile's independent score columns give the tensor cores work to overlap.  A tile arrives
+// by cp.async.bulk.tensor: one copy per page (and per 64 columns), issued by the lanes of the owning warp, instead
+// of a 16-byte cp.async per thread with its own address arithmetic.  Every warp requests its first tile before the
+// wait on the previous kernel (older keys do not come from it).
+//
+// The cache is one 2-D tensor [pages * kv_heads * page_size, D] read in boxes of min(page_size, TK) rows by 64
+// columns with the 128-byte swizzle; the page size must be a multiple of 8 that divides TK or is a multiple of it.
+// A page the window has passed (table entry -1) is fetched from beyond the tensor, which TMA fills with zeros.
+constexpr int NSUB = D / 64;
+constexpr int TK = 4096 / D;                        // keys per tile: 64 or 32, so that a tile's keys are 8 KB
+constexpr int TKT = TK / 8;                         // score n-tiles per tile
+constexpr int SUB_BYTES = TK * 128;                 // one TK-key x 64-column sub-tile
+constexpr int TMA_TILE_BYTES = 2 * NSUB * SUB_BYTES;                 // keys then values: 16 KB
+static_assert(4 * (size_t)TMA_TILE_BYTES >= DEC_MERGE_BYTES, "the merge area reuses the warps' stages");
+constexpr size_t TMA_SMEM_FIXED = 1024 /* alignment slack */ + 4 * (size_t)TMA_TILE_BYTES + sizeof(bf16) * 16 * LDS + 64;
+
+__device__ __forceinline__ int swizzled(int row, int chunk) {      // byte offset of 16-byte chunk `chunk` of key row `row`
+    return (chunk >> 3) * SUB_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+// Thread-block clusters: the CTAs of one (request, kv head) that share a cluster exchange their partial sums through
+// distributed shared memory, each CTA finishing a slice of the output columns, so a step whose key ranges fit one
+// cluster (up to 16) needs no merge kernel and no round trip of the partial sums through global memory.  The
+// cluster barrier is the hardware's (all CTAs of a cluster are resident together); every CTA reaches it on every path.
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t shared_of_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void store_cluster(uint32_t addr, float v) { asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+#ifdef DEC_TRACE
+// Development aid (not built into the engine's libraries): clock stamps of thread 0 of every CTA of the last launch.
+__device__ unsigned long long g_trace[8192][10];
+__device__ __forceinline__ void stamp(int i) {
+    if (threadIdx.x == 0) {
+        const int b = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        if (b < 8192) {
+            g_trace[b][i] = clock64();
+            if (i == 0 || i == 7) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_trace[b][8 + (i ? 1 : 0)] = t; }
+        }
+    }
+}
+#define STAMP(i) stamp(i)
+#else
+#define STAMP(i)
+#endif
+
+// cluster: CTAs per cluster along the key ranges (1: none).  n_parts = n_splits / cluster partial sums per query head
+// remain; with one, the first CTA writes the finished rows to `out`, otherwise partial sums for the merge kernel.
+__global__ void __launch_bounds__(DEC_THREADS, 3)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_cache,
+                       const bf16* __restrict__ v_cache, int cache_rows, const int* __restrict__ req_slot,
+                       const int* __restrict__ block_table, int table_width, const int* __restrict__ dec_req,
+                       const int* __restrict__ q_start, const int* __restrict__ ctx_len, float* __restrict__ partial,
+                       float* __restrict__ stats, int hq, int hkv, int page_size, float scale, int window, int split_size,
+                       int cluster, int n_parts, int row0, int* __restrict__ error) {
+    CISR_TRACE_SCOPE(TRACE_ATTN_DECODE_TMA);
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024-byte aligned
+    float* merge = reinterpret_cast<float*>(ring);                   // reused after the loop: [4][16][D + 2]
+    bf16* Qs = reinterpret_cast<bf16*>(ring + 4 * (size_t)TMA_TILE_BYTES);         // [16][LDS]
+    uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * LDS);     // [4]: a warp's tile has landed
+    int* failed = reinterpret_cast<int*>(full + 4);
+    float* gathered = reinterpret_cast<float*>(failed + 4);          // [cluster][rows][D / cluster + 2]: this CTA's share of the cluster's results
+
+    STAMP(0);
+    pdl_trigger();
+    const int group = hq / hkv;
+    const int rows = min(16, group - row0);
+    int* pages = reinterpret_cast<int*>(gathered + (cluster > 1 ? (size_t)cluster * rows * ((D + cluster - 1) / cluster + 2) : 0));   // block table entries of the key range
+    const int slot = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int req = dec_req[slot];
+    const int tok = q_start[req];
+    const int ctx = ctx_len[req];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int* table = block_table + (size_t)req_slot[req] * table_width;
+
+    int lo = split * split_size;                                     // a multiple of TK (checked by the launcher)
+    const int hi = min(lo + split_size, ctx);
+    if (window > 0) lo = max(lo, ctx - window);
+    const size_t part_base = ((size_t)slot * hq + (size_t)kvh * group + row0) * n_parts;
+    const bool empty = lo >= hi;              // nothing in this range (the same for every thread)
+    if (empty && cluster == 1) {              // the merge skips a zero denominator
+        pdl_wait();
+        for (int g = tid; g < rows; g += DEC_THREADS) {
+            const size_t p = part_base + (size_t)g * n_parts + split;
+            stats[2 * p] = -INFINITY; stats[2 * p + 1] = 0.f;
+        }
+        return;
+    }
+    float o[ND][4];
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < ND; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    if (tid == 0) *failed = 0;
+
+    if (!empty) {
+    const int base = lo & ~(TK - 1);          // tiles start on multiples of TK keys, so a tile is whole pages (or part of one)
+    const int n_tiles = (hi - base + TK - 1) / TK;
+    const int first_page = base / page_size;
+    for (int i = tid; i <= (hi - 1) / page_size - first_page; i += DEC_THREADS) pages[i] = table[first_page + i];
+    if (tid == 0) {
+        for (int w = 0; w < 4; ++w) mbar_init(full + w, 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    STAMP(1);
+
+    // Tile t into this warp's stage: lane b fetches box b (K or V, 64-column half, run of box_rows keys).
+    unsigned char* stage = ring + (size_t)warp * TMA_TILE_BYTES;
+    uint64_t* bar = full + warp;
+    const int box_rows = min(page_size, TK), boxes = TK / box_rows;
+    auto fetch = [&](int t) {
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)TMA_TILE_BYTES);
+        __syncwarp();
+        for (int b = lane; b < 2 * NSUB * boxes; b += 32) {
+            const int i = b % boxes, sub = (b / boxes) % NSUB, is_v = b / (boxes * NSUB);
+            const int kpos = base + t * TK + i * box_rows;
+            const int page = kpos < hi ? pages[kpos / page_size - first_page] : -1;
+            const int row = page < 0 ? cache_rows : (page * hkv + kvh) * page_size + kpos % page_size;
+            tma_load_2d(stage + (is_v * NSUB + sub) * SUB_BYTES + i * box_rows * 128, is_v ? &map_v : &map_k, sub * 64, row, bar);
+        }
+    };
+    // Older keys do not come from the kernel before this one, only the newest (position ctx - 1) does.  Every warp's
+    // first tile is requested now; in the tile that holds the newest key that one row arrives stale and is fetched
+    // again, by ordinary loads, once the kernel before has finished.
+    const int newest = hi == ctx ? n_tiles - 1 : -1;
+    if (warp < n_tiles) fetch(warp);
+    STAMP(2);
+    pdl_wait();
+    CISR_TRACE_WAITED();
+    STAMP(3);
+    uint4 newest_k = make_uint4(0, 0, 0, 0), newest_v = newest_k;
+    if (warp == newest && lane < NSUB * 8) {
+        const int pos = ctx - 1, page = pages[pos / page_size - first_page];
+        if (page >= 0) {
+            const size_t at = (((size_t)page * hkv + kvh) * page_size + pos % page_size) * D + lane * 8;
+            newest_k = __ldcg(reinterpret_cast<const uint4*>(k_cache + at));     // from L2: no stale line of an earlier step
+            newest_v = __ldcg(reinterpret_cast<const uint4*>(v_cache + at));
+        }
+    }
+    for (int c = tid; c < 16 * CHUNKS; c += DEC_THREADS) {
+        const int r = c / CHUNKS, ch = c - r * CHUNKS;
+        const bool ok = r < rows;
+        cp_async16(Qs + r * LDS + ch * 8, q + ((size_t)tok * hq + kvh * group + row0 + (ok ? r : 0)) * D + ch * 8, ok);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();                                                 // the query rows are in shared memory
+    STAMP(4);
+
+    uint32_t qf[KD][4];
+#pragma unroll
+    for (int kk = 0; kk < KD; ++kk)
+        ldmatrix_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
+    const float scale2 = scale * LOG2E;
+    const unsigned char* Ks = stage;
+    unsigned char* Vs = stage + NSUB * SUB_BYTES;
+
+    for (int t = warp, it = 0; t < n_tiles; t += 4, ++it) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar, it & 1))) {      // the lanes agree on whether the wait ran out
+            if (lane == 0) { atomicExch(error, 3); *failed = 1; }
+            mbar_wait(bar, it & 1);      // one more bounded chance for the copy to land before the stage is given up
+            break;
+        }
+        if (it == 0) STAMP(5);
+        const int k0 = base + t * TK;
+        if (it == 0 && t == newest) {             // the newest key's row over the stale one the early copy brought
+            if (lane < NSUB * 8) {
+                const int r = ctx - 1 - k0;
+                *reinterpret_cast<uint4*>(stage + swizzled(r, lane)) = newest_k;
+                *reinterpret_cast<uint4*>(Vs + swizzled(r, lane)) = newest_v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+        }
+        if (k0 + TK > hi) {
+            // Value rows beyond the newest key were never written, or are left over from another request: whatever
+            // they hold must not meet the zero probabilities of those keys (0 * NaN).
+            for (int e = lane; e < TK * NSUB * 8; e += 32) {
+                const int r = e / (NSUB * 8), c = e - r * (NSUB * 8);
+                if (k0 + r >= hi) *reinterpret_cast<uint4*>(Vs + swizzled(r, c)) = make_uint4(0, 0, 0, 0);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // ordered before a tensor-map copy that refills the stage
+            __syncwarp();
+        }
+        float s[TKT][4];
+#pragma unroll
+        for (int nt = 0; nt < TKT; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
 #pragma unroll
         for (int kk = 0; kk < KD; ++kk) {
-            uint32_t b[4];
-            ldmatrix_x4(b, Kt + (warp * 16 + (lane & 7) + 8 * (lane >> 4)) * LDS + kk * 16 + 8 * ((lane >> 3) & 1));
-            mma_bf16(s[0], qf[kk], b[0], b[1]);
-            mma_bf16(s[1], qf[kk], b[2], b[3]);
+#pragma unroll
+            for (int np = 0; np < TKT / 2; ++np) {
+                uint32_t b[4];
+                ldmatrix_x4(b, Ks + swizzled(np * 16 + (lane & 7) + 8 * (lane >> 4), kk * 2 + ((lane >> 3) & 1)));
+                mma_bf16(s[2 * np], qf[kk], b[0], b[1]);
+                mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
+            }
         }
+        const bool edge = k0 < lo || k0 + TK > hi;                   // the same for the whole warp
         float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
+        for (int nt = 0; nt < TKT; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int kpos = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
-                const float v = kpos < hi ? s[nt][e] * scale2 : -INFINITY;
+                float v = s[nt][e] * scale2;
+                if (edge) {
+                    const int kpos = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                    if (kpos >= hi || kpos < lo) v = -INFINITY;
+                }
                 s[nt][e] = v;
                 tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
             }
@@ -458,87 +794,151 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float m_new = fmaxf(m_run[h], mx);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            alpha[h] = exp2f(m_run[h] - m_use);
+            alpha[h] = fast_exp2(m_run[h] - m_use);
             m_run[h] = m_new;
-            const float p0 = exp2f(s[0][2 * h] - m_use), p1 = exp2f(s[0][2 * h + 1] - m_use);
-            const float p2 = exp2f(s[1][2 * h] - m_use), p3 = exp2f(s[1][2 * h + 1] - m_use);
-            s[0][2 * h] = p0; s[0][2 * h + 1] = p1; s[1][2 * h] = p2; s[1][2 * h + 1] = p3;
-            l_run[h] = l_run[h] * alpha[h] + (p0 + p1 + p2 + p3);
+            float sum = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < TKT; ++nt) {
+                const float p0 = fast_exp2(s[nt][2 * h] - m_use), p1 = fast_exp2(s[nt][2 * h + 1] - m_use);
+                s[nt][2 * h] = p0; s[nt][2 * h + 1] = p1;
+                sum += p0 + p1;
+            }
+            l_run[h] = l_run[h] * alpha[h] + sum;
         }
 #pragma unroll
         for (int i = 0; i < ND; ++i) { o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1]; }
-        uint32_t pa[4];
-        pa[0] = pack_bf16(s[0][0], s[0][1]); pa[1] = pack_bf16(s[0][2], s[0][3]);
-        pa[2] = pack_bf16(s[1][0], s[1][1]); pa[3] = pack_bf16(s[1][2], s[1][3]);
 #pragma unroll
-        for (int dp = 0; dp < ND / 2; ++dp) {
-            uint32_t b[4];
-            ldmatrix_x4_trans(b, Vt + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
-            mma_bf16(o[2 * dp], pa, b[0], b[1]);
-            mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
+        for (int j = 0; j < TK / 16; ++j) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * j][0], s[2 * j][1]); pa[1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
+            pa[2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]); pa[3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < ND / 2; ++dp) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, Vs + swizzled(j * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), dp * 2 + (lane >> 4)));
+                mma_bf16(o[2 * dp], pa, b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
+            }
         }
+        __syncwarp();                                                // every lane has read the stage
+        if (t + 4 < n_tiles) fetch(t + 4);
     }
-    cp_async_wait<0>();
-    __syncthreads();          // every warp is done with the pipeline buffers: they become the merge area
+    } else {
+        pdl_wait();
+    }
+    __syncthreads();          // every warp is done with its stage: the stages become the merge area
+    STAMP(6);
+    if (cluster == 1) {
+        if (*failed) return;  // a copy never arrived; the host reads the error flag
+        decode_finish(merge, o, m_run, l_run, partial, stats, part_base, rows, n_parts, split, tid);
+        STAMP(7);
+        return;
+    }
 
-    // per-warp results: merge[warp][row][0..D) = unnormalised output, [D] = running max (base 2), [D+1] = denominator
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        float l = l_run[h];
-        l += __shfl_xor_sync(0xffffffffu, l, 1);
-        l += __shfl_xor_sync(0xffffffffu, l, 2);
-        const int row = (lane >> 2) + 8 * h;
-        float* dst = merge + ((size_t)warp * 16 + row) * (D + 2);
-#pragma unroll
-        for (int i = 0; i < ND; ++i) {
-            dst[i * 8 + 2 * (lane & 3)] = o[i][2 * h];
-            dst[i * 8 + 2 * (lane & 3) + 1] = o[i][2 * h + 1];
-        }
-        if ((lane & 3) == 0) { dst[D] = m_run[h]; dst[D + 1] = l; }
-    }
+    // All-to-all over the cluster: CTA r finishes output columns [r * cols, (r + 1) * cols) of every query row, so each
+    // CTA sends every other CTA that slice of its rows (and the rows' max and denominator).  A CTA without keys, or
+    // one that gave up, sends a zero weight.  Layout in the receiver: [sender][row][cols + 2].
+    const bool have = !empty && !*failed;
+    if (have) warps_to_merge_area(merge, o, m_run, l_run, warp, lane, rows);
     __syncthreads();
+    const uint32_t rank = cluster_rank();
+    const int cols = (D + cluster - 1) / cluster, stride = cols + 2;
+    const uint32_t mine = smem_u32(gathered) + (uint32_t)(rank * rows * stride * sizeof(float));   // this sender's block, in any receiver
     for (int e = tid; e < rows * D; e += DEC_THREADS) {
         const int g = e / D, d = e - g * D;
-        float m = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) m = fmaxf(m, merge[((size_t)w * 16 + g) * (D + 2) + D]);
-        float num = 0.f, den = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float* src = merge + ((size_t)w * 16 + g) * (D + 2);
-            const float wgt = src[D] == -INFINITY ? 0.f : exp2f(src[D] - m);
-            num = fmaf(wgt, src[d], num);
-            den = fmaf(wgt, src[D + 1], den);
+        float m = -INFINITY, den = 0.f, num = 0.f;
+        if (have) num = merged_element(merge, g, d, m, den);
+        const int dest = d / cols, c = d - dest * cols;
+        const uint32_t there = shared_of_rank(mine, (uint32_t)dest) + (uint32_t)((g * stride + c) * sizeof(float));
+        store_cluster(there, num);
+        if (c == 0) {
+            store_cluster(there + (uint32_t)(cols * sizeof(float)), m);
+            store_cluster(there + (uint32_t)((cols + 1) * sizeof(float)), den);
         }
-        const size_t p = part_base + (size_t)g * n_splits + split;
-        partial[p * D + d] = num;
-        if (d == 0) { stats[2 * p] = m * LN2; stats[2 * p + 1] = den; }   // the merge kernel works in natural logarithms
+    }
+    cluster_barrier();
+    const int part = split / cluster;
+    for (int e = tid; e < rows * cols; e += DEC_THREADS) {
+        const int g = e / cols, c = e - g * cols, d = (int)rank * cols + c;
+        if (d >= D) continue;
+        float m = -INFINITY;
+        for (int r = 0; r < cluster; ++r) m = fmaxf(m, gathered[((size_t)r * rows + g) * stride + cols]);
+        float num = 0.f, den = 0.f;
+        for (int r = 0; r < cluster; ++r) {              // in the order of the key ranges
+            const float* src = gathered + ((size_t)r * rows + g) * stride;
+            const float wgt = src[cols] == -INFINITY ? 0.f : exp2f(src[cols] - m);
+            num = fmaf(wgt, src[c], num);
+            den = fmaf(wgt, src[cols + 1], den);
+        }
+        if (n_parts == 1) {
+            out[((size_t)tok * hq + kvh * group + row0 + g) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        } else {
+            const size_t p = part_base + (size_t)g * n_parts + part;
+            partial[p * D + d] = num;
+            if (d == 0) { stats[2 * p] = m * LN2; stats[2 * p + 1] = den; }
+        }
     }
 }
+#endif
 
+// Log-sum-exp merge of the key ranges.  A thread owns one output dimension; it requests the first sixteen ranges'
+// partial sums at once, together with the ranges' statistics, so the kernel is one trip to memory deep; the weights
+// are computed once into shared memory and the sum runs over the ranges in their fixed order.
 __global__ void attn_merge_kernel(const float* __restrict__ partial, const float* __restrict__ stats,
                                   bf16* __restrict__ out, const int* __restrict__ dec_req,
                                   const int* __restrict__ q_start, int hq, int n_splits) {
+    CISR_TRACE_SCOPE(TRACE_ATTN_MERGE);
+    extern __shared__ float weights[];            // [n_splits] weights, then [n_splits] weighted denominators
+    __shared__ float scratch[32];
     pdl_trigger();
     const int slot = blockIdx.x, head = blockIdx.y;
     const size_t base = ((size_t)slot * hq + head) * n_splits;
     const int tok = q_start[dec_req[slot]];       // request metadata does not come from the kernel before
     pdl_wait();
+    CISR_TRACE_WAITED();
+    const int d = threadIdx.x;                    // blockDim.x >= D: threads beyond D only help with the statistics
+    float first[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) first[j] = (d < D && j < n_splits) ? partial[(base + j) * D + d] : 0.f;
     float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s)
-        if (stats[2 * (base + s) + 1] > 0.f) m = fmaxf(m, stats[2 * (base + s)]);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float l = stats[2 * (base + s) + 1];
-            if (l > 0.f) {
-                const float w = expf(stats[2 * (base + s)] - m);
-                num = fmaf(w, partial[(base + s) * D + d], num);
-                den = fmaf(w, l, den);
-            }
-        }
-        out[((size_t)tok * hq + head) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);   // no keys: a padding row
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
+        const float2 ml = reinterpret_cast<const float2*>(stats)[base + s];
+        weights[s] = ml.x; weights[n_splits + s] = ml.y;
+        if (ml.y > 0.f) m = fmaxf(m, ml.x);
     }
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
+    __syncthreads();
+    CISR_TRACE_MARK(0);
+    m = -INFINITY;
+    for (int w = 0; w < (int)(blockDim.x + 31) / 32; ++w) m = fmaxf(m, scratch[w]);
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {          // the thread that stored them
+        const float l = weights[n_splits + s];
+        const float w = l > 0.f ? expf(weights[s] - m) : 0.f;           // a range without keys weighs nothing
+        weights[s] = w;
+        weights[n_splits + s] = l > 0.f ? w * l : 0.f;
+    }
+    __syncthreads();
+    CISR_TRACE_MARK(1);
+    if (d >= D) return;
+    float den = 0.f, num = 0.f;                   // every thread sums in the same order: the same denominator in all
+    for (int s = 0; s < n_splits; ++s) den += weights[n_splits + s];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float w = j < n_splits ? weights[j] : 0.f;
+        num = fmaf(w, w > 0.f ? first[j] : 0.f, num);                   // what an empty range left there is not a number to use
+    }
+    for (int s0 = 16; s0 < n_splits; s0 += 16) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = s0 + j < n_splits ? partial[(base + s0 + j) * D + d] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float w = s0 + j < n_splits ? weights[s0 + j] : 0.f;
+            num = fmaf(w, w > 0.f ? v[j] : 0.f, num);
+        }
+    }
+    out[((size_t)tok * hq + head) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);   // no keys: a padding row
 }
 }  // namespace
 
@@ -562,10 +962,9 @@ CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache,
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    attn_prefill_mma_kernel<<<dim3(n_tiles, hq), PREFILL_THREADS, smem, (cudaStream_t)stream>>>(
-        (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, req_slot, block_table, table_width,
-        tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window);
-    return launch_status();
+    return launch_kernel(attn_prefill_mma_kernel, dim3(n_tiles, hq), dim3(PREFILL_THREADS), smem, (cudaStream_t)stream, g_pdl,
+                         (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, req_slot, block_table,
+                         table_width, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window);
 }
 
 CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
@@ -592,6 +991,104 @@ CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, 
                                    window, split_size, n_splits, row0);
         if (status) return status;
     }
-    return launch_kernel(attn_merge_kernel, dim3(n_dec, hq), dim3(D < 128 ? 64 : 128), 0, s, g_pdl, (const float*)partial,
-                         (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_splits);
+    return launch_kernel(attn_merge_kernel, dim3(n_dec, hq), dim3(D <= 64 ? 64 : 128), sizeof(float) * 2 * (size_t)n_splits, s, g_pdl,
+                         (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_splits);
 }
+
+// 1 when this library has the variant that stages tiles by tensor-map copies, and it takes this page and range size.
+CISR_EXPORT int cisr_attn_decode_tma_ok(int page_size, int split_size) {
+#if HEAD_DIM % 64 == 0
+    return page_size > 0 && page_size % 8 == 0 && (TK % page_size == 0 || page_size % TK == 0) && split_size > 0 &&
+           split_size % TK == 0;
+#else
+    return 0;
+#endif
+}
+
+#if HEAD_DIM % 64 == 0
+namespace { int* g_error = nullptr; bool g_clusters = false; }
+
+// `error_flag`: one zeroed int in device memory that a kernel sets when a wait on a copy ran out.
+CISR_EXPORT int cisr_attn_tma_init(int* error_flag) {
+    if (int status = tma_load_encoder()) return status;
+    g_error = error_flag;
+    return 0;
+}
+
+// As cisr_attn_decode, for caches of `n_pages` pages whose address is 16-byte aligned.  Key ranges are grouped into
+// thread-block clusters of up to 16 where the device can hold such clusters; when one cluster covers all ranges
+// the finished rows go straight to `out` and no merge kernel runs.
+CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cache, const void* v_cache, int n_pages,
+                                     const int* req_slot, const int* block_table, int table_width, const int* dec_req,
+                                     int n_dec, const int* q_start, const int* ctx_len, float* partial, float* stats,
+                                     int hq, int hkv, int page_size, float scale, int window, int split_size,
+                                     int n_splits, void* stream) {
+    if (n_dec <= 0) return 0;
+    if (!g_encode || !g_error) return -13;
+    if (hq % hkv || n_splits <= 0 || !cisr_attn_decode_tma_ok(page_size, split_size)) return -2;
+    const long long cache_rows = (long long)n_pages * hkv * page_size;
+    if (cache_rows <= 0 || cache_rows >= (1ll << 31) || (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15)) return -2;
+    const int box_rows = page_size < TK ? page_size : TK;
+    const CUtensorMap *map_k, *map_v;
+    int status = cached_map(&map_k, k_cache, cache_rows, D, box_rows, 64);
+    if (status) return status;
+    if ((status = cached_map(&map_v, v_cache, cache_rows, D, box_rows, 64))) return status;
+    const int group = hq / hkv, rows_max = group < 16 ? group : 16;
+    const size_t smem_plain = TMA_SMEM_FIXED + sizeof(int) * ((size_t)split_size / page_size + 8);
+    constexpr size_t SMEM_CAP = 110 * 1024;  // two CTAs per SM at the very least; the usual need is below 72 KB (three)
+    if (smem_plain > SMEM_CAP) return -3;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_CAP);
+        if (e != cudaSuccess) return (int)e;
+        cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);   // clusters of more than 8
+        cudaGetLastError();
+        configured = true;
+    }
+    // the largest cluster size that divides the number of ranges, fits shared memory and can be resident
+    int cluster = 1;
+    size_t smem = smem_plain;
+    static int resident[17] = {};            // per cluster size: 0 unknown, 1 yes, -1 no (asked with the largest shared memory)
+    for (int c = 16; c >= 2 && g_clusters; --c) {
+        if (n_splits % c) continue;
+        const size_t need = smem_plain + sizeof(float) * (size_t)c * rows_max * ((D + c - 1) / c + 2);
+        if (need > SMEM_CAP) continue;
+        if (!resident[c]) {
+            cudaLaunchConfig_t config = {};
+            config.gridDim = dim3(1, 1, c); config.blockDim = dim3(DEC_THREADS); config.dynamicSmemBytes = SMEM_CAP;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)c;
+            config.attrs = attr; config.numAttrs = 1;
+            int n = 0;
+            const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, attn_decode_tma_kernel, &config);
+            cudaGetLastError();
+            resident[c] = (e == cudaSuccess && n >= 1) ? 1 : -1;
+        }
+        if (resident[c] < 0) continue;
+        cluster = c;
+        smem = need;
+        break;
+    }
+    const int n_parts = n_splits / cluster;
+    cudaStream_t s = (cudaStream_t)stream;
+    for (int row0 = 0; row0 < group; row0 += 16) {
+        status = launch_kernel_cluster(attn_decode_tma_kernel, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), smem, s, g_pdl, cluster,
+                                       *map_k, *map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
+                                       (int)cache_rows, req_slot, block_table, table_width,
+                                       dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale, window, split_size,
+                                       cluster, n_parts, row0, g_error);
+        if (status) return status;
+    }
+    if (n_parts == 1 && cluster > 1) return 0;
+    return launch_kernel(attn_merge_kernel, dim3(n_dec, hq), dim3(D <= 64 ? 64 : 128), sizeof(float) * 2 * (size_t)n_parts, s, g_pdl,
+                         (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_parts);
+}
+
+#ifdef DEC_TRACE
+CISR_EXPORT int cisr_attn_trace_read(void* host, int bytes) { return (int)cudaMemcpyFromSymbol(host, g_trace, (size_t)bytes); }
+#endif
+
+// 0 turns the clusters off (every key range then writes its partial sum and the merge kernel runs).
+CISR_EXPORT void cisr_attn_set_clusters(int on) { g_clusters = on != 0; }
+#endif

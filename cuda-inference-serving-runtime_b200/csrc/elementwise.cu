@@ -9,10 +9,14 @@
 // reduction stay in float here whatever the storage type.
 #include "common.cuh"
 
+static bool g_pdl = false;
+CISR_EXPORT void cisr_elementwise_set_pdl(int on) { g_pdl = on != 0; }
+
 // ---------------------------------------------------------------- embedding
 template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab) {
+    CISR_TRACE_SCOPE(TRACE_EMBEDDING);
     const int row = blockIdx.x;
     int id = ids[row];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // host validates; clamp keeps a bad id from reading outside
@@ -39,6 +43,7 @@ template <typename WT, typename OT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                    const WT* __restrict__ weight, OT* __restrict__ out,
                                    const int* __restrict__ rows, int hidden, float eps, int write_back) {
+    CISR_TRACE_SCOPE(TRACE_ADD_RMSNORM);
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
@@ -65,8 +70,12 @@ template <typename WT, typename OT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                        const WT* __restrict__ weight, OT* __restrict__ out,
                                        const int* __restrict__ rows, int hidden, float eps, int write_back) {
+    CISR_TRACE_SCOPE(TRACE_ADD_RMSNORM);
     __shared__ float scratch[32];
     extern __shared__ __align__(16) float row_cache[];
+    pdl_trigger();
+    pdl_wait();          // x and delta come from the kernels before
+    CISR_TRACE_WAITED();
     const int r = blockIdx.x, h4 = hidden >> 2;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     float4* xr = reinterpret_cast<float4*>(x + src);
@@ -113,7 +122,8 @@ static int add_rmsnorm_launch(float* x, const float* delta, const void* w, void*
     }
     if (vec) {
         const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
-        add_rmsnorm_vec_kernel<WT, OT><<<n_rows, threads, smem, s>>>(x, delta, (const WT*)w, (OT*)out, rows, hidden, eps, write_back);
+        return launch_kernel(add_rmsnorm_vec_kernel<WT, OT>, dim3(n_rows), dim3(threads), smem, s, g_pdl, x, delta, (const WT*)w,
+                             (OT*)out, rows, hidden, eps, write_back);
     } else {
         const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
         add_rmsnorm_kernel<WT, OT><<<n_rows, threads, smem, s>>>(x, delta, (const WT*)w, (OT*)out, rows, hidden, eps, write_back);
@@ -139,6 +149,7 @@ CISR_EXPORT int cisr_add_rmsnorm(float* x, const float* delta, const void* weigh
 // gate_up [T, 2I] float: gate in columns [0, I), up in [I, 2I).  out = gate/(1+exp(-gate)) * up.
 template <typename OT>
 __global__ void swiglu_kernel(const float* __restrict__ gate_up, OT* __restrict__ out, int inter, size_t total) {
+    CISR_TRACE_SCOPE(TRACE_SWIGLU);
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t t = i / inter;
@@ -163,6 +174,7 @@ CISR_EXPORT int cisr_swiglu(const float* gate_up, void* out, int out_dtype, int 
 // and shared by every layer that rotates with the same theta and width.
 __global__ void rotary_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                     float* __restrict__ cos_out, float* __restrict__ sin_out, int half, int total) {
+    CISR_TRACE_SCOPE(TRACE_ROTARY_TABLE);
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const int t = i / half, f = i - t * half;
@@ -194,6 +206,7 @@ __global__ void rope_store_kernel(const float* __restrict__ proj, int row_stride
                                   const int* __restrict__ positions, const int* __restrict__ req_slot,
                                   const int* __restrict__ block_table, int table_width, int page_size, int hq,
                                   int hkv, int dim) {
+    CISR_TRACE_SCOPE(TRACE_ROPE_STORE);
     const int t = blockIdx.x;
     const float* row = proj + (size_t)t * row_stride;
     const float* cs = cos_t ? cos_t + (size_t)t * rot_half : nullptr;
@@ -259,6 +272,7 @@ CISR_EXPORT int cisr_rope_store(const float* proj, int row_stride, int k_col, in
 // Copies whole pages inside one pool: pool viewed as [n_planes, pages, page_elems]; pairs (src, dst) in `pairs`.
 __global__ void page_copy_kernel(uint4* __restrict__ pool, const int* __restrict__ pairs, size_t plane_vec,
                                  size_t page_vec) {
+    CISR_TRACE_SCOPE(TRACE_PAGE_COPY);
     const int pair = blockIdx.x, plane = blockIdx.y;
     const uint4* src = pool + plane * plane_vec + (size_t)pairs[2 * pair] * page_vec;
     uint4* dst = pool + plane * plane_vec + (size_t)pairs[2 * pair + 1] * page_vec;
@@ -277,6 +291,7 @@ CISR_EXPORT int cisr_page_copy(void* pool, const int* pairs, int n_pairs, int n_
 // ---------------------------------------------------------------- block table updates
 // table[idx[i]] = val[i]; the host sends one value per entry, so the order does not matter.
 __global__ void table_update_kernel(int* __restrict__ table, const int* __restrict__ idx, const int* __restrict__ val, int n) {
+    CISR_TRACE_SCOPE(TRACE_TABLE_UPDATE);
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n && idx[i] >= 0) table[idx[i]] = val[i];
 }

@@ -19,11 +19,7 @@
 // frees its tensor memory and returns, and the host reports the failure.
 //
 // Parity: this is the product runtime/blas.py:41-56 of the reference hands to cuBLAS (C^T = W * X^T).
-#include <cuda.h>
-
-#include "common.cuh"
-
-#include <unordered_map>
+#include "tma.cuh"
 
 namespace {
 typedef __nv_bfloat16 bf16;
@@ -35,31 +31,6 @@ struct Epilogue {                       // what the epilogue variants need beyon
     const float* cos_t; const float* sin_t; bf16* q_out; bf16* k_cache; bf16* v_cache; const int* positions;
     const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size; int hq; int hkv; int dim;
 };
-constexpr unsigned MAX_POLLS = 1u << 20;   // a stage is ready within microseconds; this is seconds
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Polls until the barrier's phase with the given parity has completed; false when it gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (unsigned i = 0; i < MAX_POLLS; ++i) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 
@@ -225,6 +196,7 @@ template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const Epilogue ep, int m, int n, int k, int tiles_m, int tiles_n, int* __restrict__ error) {
+    CISR_TRACE_SCOPE(TRACE_GEMM_TCGEN05);
     extern __shared__ unsigned char smem_raw[];
     typedef Smem<BN, STAGES> S;
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024-byte aligned
@@ -242,7 +214,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 4); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_init_fence();
     }
     if (warp == 1) {    // one warp allocates two accumulators' columns of tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
@@ -253,25 +225,45 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    pdl_trigger();      // under programmatic dependent launch the next kernel may begin its own set-up now
 
     if (warp == 0) {
         if (lane == 0) {
+            auto load_b = [&](int s, int kb, int n0) {
+                unsigned char* b_tile = tiles + s * (S::A_BYTES + S::B_BYTES) + S::A_BYTES;
+                if (EPI == EPI_SWIGLU) {      // two boxes of BN/2 rows: gate rows n0.., up rows inter + n0..
+                    tma_load_2d(b_tile, &map_w, kb * BK, n0, full_bar + s);
+                    tma_load_2d(b_tile + S::B_BYTES / 2, &map_w, kb * BK, ep.inter + n0, full_bar + s);
+                } else {
+                    tma_load_2d(b_tile, &map_w, kb * BK, n0, full_bar + s);
+                }
+            };
+            // The weights do not come from the kernel before this one: the first stages' weight tiles are requested
+            // before the wait on that kernel, the activation tiles after it.
+            const int early = k_blocks < STAGES ? k_blocks : STAGES;
+            if ((int)blockIdx.x < total_tiles) {
+                const int n0 = ((int)blockIdx.x / tiles_m) * TILE_N;
+                for (int kb = 0; kb < early; ++kb) {
+                    mbar_expect_tx(full_bar + kb, (uint32_t)(S::A_BYTES + S::B_BYTES));
+                    load_b(kb, kb, n0);
+                }
+            }
+            pdl_wait();
+            CISR_TRACE_WAITED();
             int kbg = 0;                                                      // k blocks issued so far, over all tiles
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;   // neighbours share the weight tile
                 for (int kb = 0; kb < k_blocks; ++kb, ++kbg) {
                     const int s = kbg % STAGES;
+                    if (kbg < early) {        // this stage's barrier is armed and its weight tile on the way already
+                        tma_load_2d(tiles + s * (S::A_BYTES + S::B_BYTES), &map_a, kb * BK, m0, full_bar + s);
+                        continue;
+                    }
                     ok = mbar_wait(empty_bar + s, ((kbg / STAGES) & 1) ^ 1);  // the MMAs that read this stage are done
                     if (!ok) break;
                     mbar_expect_tx(full_bar + s, (uint32_t)(S::A_BYTES + S::B_BYTES));
                     tma_load_2d(tiles + s * (S::A_BYTES + S::B_BYTES), &map_a, kb * BK, m0, full_bar + s);
-                    unsigned char* b_tile = tiles + s * (S::A_BYTES + S::B_BYTES) + S::A_BYTES;
-                    if (EPI == EPI_SWIGLU) {      // two boxes of BN/2 rows: gate rows n0.., up rows inter + n0..
-                        tma_load_2d(b_tile, &map_w, kb * BK, n0, full_bar + s);
-                        tma_load_2d(b_tile + S::B_BYTES / 2, &map_w, kb * BK, ep.inter + n0, full_bar + s);
-                    } else {
-                        tma_load_2d(b_tile, &map_w, kb * BK, n0, full_bar + s);
-                    }
+                    load_b(s, kb, n0);
                 }
             }
         }
@@ -303,6 +295,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         const int quarter = warp & 3;                                          // the 32 lanes this warp may read
         int it = 0;
+        pdl_wait();      // outputs may alias what the kernel before still reads; step metadata is older than that kernel
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
             const int acc = it & 1;
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
@@ -323,47 +316,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiled g_encode = nullptr;
+bool g_pdl = false;
 int* g_error = nullptr;          // device flag, owned by the caller (see cisr_gemm_tcgen05_init)
-
-int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(bf16)};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : -20 - (int)r;
-}
-
-struct MapKey {
-    const void* base; int rows, cols, box_rows;
-    bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.base) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^ (size_t)k.box_rows;
-    }
-};
-std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;     // a map describes geometry only, so it stays right while the address does
-
-int cached_map(const CUtensorMap** out, const void* base, int rows, int cols, int box_rows) {
-    const MapKey key{base, rows, cols, box_rows};
-    auto it = g_maps.find(key);
-    if (it == g_maps.end()) {
-        if (g_maps.size() > 4096) g_maps.clear();
-        CUtensorMap map;
-        const int status = make_map(&map, base, rows, cols, box_rows);
-        if (status) return status;
-        it = g_maps.emplace(key, map).first;
-    }
-    *out = &it->second;
-    return 0;
-}
 
 template <int BN, int STAGES, int EPI>
 int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k, int tiles_n, cudaStream_t s) {
@@ -389,9 +343,8 @@ int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k
         slots = sms * per_sm;
     }
     const int tiles_m = (m + BM - 1) / BM, total = tiles_m * tiles_n;
-    gemm_tcgen05_kernel<BN, STAGES, EPI><<<total < slots ? total : slots, 192, S::TOTAL, s>>>(*map_a, *map_w, ep, m, n, k, tiles_m,
-                                                                                      tiles_n, g_error);
-    return launch_status();
+    return launch_kernel(gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(total < slots ? total : slots), dim3(192), S::TOTAL, s, g_pdl,
+                         *map_a, *map_w, ep, m, n, k, tiles_m, tiles_n, g_error);
 }
 
 // 128 x 256 tiles read a third less from L2 per flop than 128 x 128; worth it once there are enough of them to
@@ -405,16 +358,12 @@ bool operands_ok(const void* a, const void* w, int k) {
 
 // `error_flag`: one zeroed int in device memory that a kernel sets when one of its waits ran out.
 CISR_EXPORT int cisr_gemm_tcgen05_init(int* error_flag) {
-    if (!g_encode) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult query;
-        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query);
-        if (e != cudaSuccess || query != cudaDriverEntryPointSuccess || !fn) return -15;
-        g_encode = (EncodeTiled)fn;
-    }
+    if (int status = tma_load_encoder()) return status;
     g_error = error_flag;
     return 0;
 }
+
+CISR_EXPORT void cisr_gemm_tcgen05_set_pdl(int on) { g_pdl = on != 0; }
 
 // Three pipeline stages keep a CTA near 100 KB of shared memory, so two CTAs share an SM and one's epilogue overlaps
 // the other's main loop.

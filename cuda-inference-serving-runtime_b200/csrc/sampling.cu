@@ -21,6 +21,7 @@ constexpr int SAMPLE_THREADS = 256;
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
               const long long* __restrict__ seed, const int* __restrict__ counter, int* __restrict__ out) {
+    CISR_TRACE_SCOPE(TRACE_SAMPLE);
     __shared__ float s_val[SAMPLE_THREADS];
     __shared__ int s_idx[SAMPLE_THREADS];
     __shared__ float s_pre[SAMPLE_THREADS + 1];
@@ -92,6 +93,7 @@ CISR_EXPORT int cisr_sample(const float* logits, int rows, int vocab, const floa
 // the host.  Rows with live == 0 (padding) stay as they are.
 __global__ void decode_advance_kernel(int* token_ids, int* positions, int* ctx_len, int* counter,
                                       const int* __restrict__ sampled, const int* __restrict__ live, int rows) {
+    CISR_TRACE_SCOPE(TRACE_DECODE_ADVANCE);
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= rows || !live[i]) return;
     token_ids[i] = sampled[i];

@@ -45,6 +45,7 @@ struct SkinnyArgs {
     const bf16* act;                               // ACT prologue
     const float* x; const float* delta; const void* norm_w; int norm_w_bf16; float eps; float* x_out; const int* rows;
     int m; int rt; int ks;
+    int sums_in_smem;                              // NORM prologue: x + delta staged as float in shared memory (one pass over global memory)
     float* out_f32; bf16* out_bf16; int inter;      // PLAIN / SWIGLU
     // ROPE
     const float* cos_t; const float* sin_t; int rot_half; int interleaved; bf16* q_out; bf16* k_cache; bf16* v_cache;
@@ -64,8 +65,12 @@ __device__ __forceinline__ uint4 load_weights(const bf16* p) {
 }
 
 // The token operand in shared memory: hs[MT * 8][ldh] bfloat16, rows >= m zero.  All warps take part.
+// NORM prologue: `nw` holds the norm weights as float (fetched before the wait on the previous kernel).  With `sums`
+// (float [MT * 8][k]) every row is read from global memory once: all of a lane's loads are issued before the first
+// is used, the sum x + delta is kept in shared memory while the warp adds up its squares, and the second pass
+// reads it from there.  Without `sums` (rows too long for shared memory) the second pass reads global memory again.
 template <int MT>
-__device__ void stage_tokens(const SkinnyArgs& a, bf16* hs, int ldh) {
+__device__ void stage_tokens(const SkinnyArgs& a, bf16* hs, int ldh, const float* nw, float* sums) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
     const int k = a.k, k8 = k / 8;
     if (a.act) {
@@ -78,6 +83,7 @@ __device__ void stage_tokens(const SkinnyArgs& a, bf16* hs, int ldh) {
         return;
     }
     const int k4 = k / 4;
+    constexpr int U = 6;                           // float4 loads of x (and of delta) in flight per lane
     for (int r = warp; r < MT * 8; r += nwarp) {
         bf16* dst = hs + r * ldh;
         if (r >= a.m) {
@@ -87,31 +93,44 @@ __device__ void stage_tokens(const SkinnyArgs& a, bf16* hs, int ldh) {
         const size_t src = (size_t)(a.rows ? a.rows[r] : r) * k;
         const float4* xr = reinterpret_cast<const float4*>(a.x + src);
         const float4* dr = a.delta ? reinterpret_cast<const float4*>(a.delta + src) : nullptr;
+        float4* row_sums = sums ? reinterpret_cast<float4*>(sums + (size_t)r * k) : nullptr;
+        const bool write_x = a.x_out && blockIdx.x == 0;
         float sq = 0.f;
-#pragma unroll 4
-        for (int c = lane; c < k4; c += 32) {
-            float4 v = xr[c];
-            if (dr) { const float4 d = dr[c]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
-            sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        for (int base = 0; base < k4; base += 32 * U) {
+            float4 xv[U], dv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int c = base + lane + 32 * u;
+                xv[u] = make_float4(0.f, 0.f, 0.f, 0.f); dv[u] = xv[u];
+                if (c < k4) { xv[u] = xr[c]; if (dr) dv[u] = dr[c]; }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int c = base + lane + 32 * u;
+                float4 v = xv[u];
+                v.x += dv[u].x; v.y += dv[u].y; v.z += dv[u].z; v.w += dv[u].w;
+                sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                if (c < k4) {
+                    if (row_sums) row_sums[c] = v;
+                    if (write_x) reinterpret_cast<float4*>(a.x_out + src)[c] = v;
+                }
+            }
         }
         sq = warp_sum(sq);
         const float scale = rsqrtf(sq / (float)k + a.eps);
-        const bool write_x = a.x_out && blockIdx.x == 0;
+        __syncwarp();                              // the lanes read back only what they wrote themselves; cheap insurance
 #pragma unroll 4
         for (int c = lane; c < k4; c += 32) {
-            float4 v = xr[c];
-            if (dr) { const float4 d = dr[c]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
-            if (write_x) reinterpret_cast<float4*>(a.x_out + src)[c] = v;
-            float w0, w1, w2, w3;
-            if (a.norm_w_bf16) {
-                const bf16* wp = (const bf16*)a.norm_w + 4 * c;
-                w0 = __bfloat162float(wp[0]); w1 = __bfloat162float(wp[1]); w2 = __bfloat162float(wp[2]); w3 = __bfloat162float(wp[3]);
+            float4 v;
+            if (row_sums) {
+                v = row_sums[c];
             } else {
-                const float4 wv = reinterpret_cast<const float4*>(a.norm_w)[c];
-                w0 = wv.x; w1 = wv.y; w2 = wv.z; w3 = wv.w;
+                v = xr[c];
+                if (dr) { const float4 d = dr[c]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
             }
-            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * scale * w0, v.y * scale * w1);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * scale * w2, v.w * scale * w3);
+            const float4 wv = reinterpret_cast<const float4*>(nw)[c];
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * scale * wv.x, v.y * scale * wv.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * scale * wv.z, v.w * scale * wv.w);
             uint2 packed;
             packed.x = *reinterpret_cast<uint32_t*>(&lo); packed.y = *reinterpret_cast<uint32_t*>(&hi);
             *reinterpret_cast<uint2*>(dst + 4 * c) = packed;
@@ -121,10 +140,14 @@ __device__ void stage_tokens(const SkinnyArgs& a, bf16* hs, int ldh) {
 
 template <int MT, int EPI>
 __global__ void __launch_bounds__(512) skinny_kernel(const SkinnyArgs a) {
+    CISR_TRACE_SCOPE(EPI == EPI_ROPE ? TRACE_SKINNY_ROPE : EPI == EPI_SWIGLU ? TRACE_SKINNY_SWIGLU : TRACE_SKINNY_PLAIN);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int ldh = a.k + 8;
     bf16* hs = reinterpret_cast<bf16*>(smem_raw);
     float* red = reinterpret_cast<float*>(hs + MT * 8 * ldh);   // [KS][RT * 16][MT * 8]
+    float* nw = red + (size_t)a.ks * a.rt * 16 * MT * 8;         // NORM: [k] norm weights as float
+    float* sums = a.sums_in_smem ? nw + a.k : nullptr;           // NORM: [MT * 8][k] x + delta
+    float* tables = nw + (a.act ? 0 : a.k) + (a.sums_in_smem ? (size_t)MT * 8 * a.k : 0);   // ROPE: [2][m][rot_half] cos, sin
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, t = lane & 3;
     const int RT = a.rt, KS = a.ks;
     const int rt = warp % RT, ks = warp / RT;
@@ -156,11 +179,23 @@ __global__ void __launch_bounds__(512) skinny_kernel(const SkinnyArgs a) {
         const int page = a.block_table[(size_t)a.req_slot[a.token_req[tid]] * a.table_width + pos / a.page_size];
         cache_row[tid] = page < 0 ? -1 : (long long)page * a.hkv * a.page_size + pos % a.page_size;
     }
+    // The norm weights and the rotation tables (made at the start of the step) do not come from the kernel before either.
+    if (!a.act) {
+        for (int c = tid; c < a.k; c += blockDim.x)
+            nw[c] = a.norm_w_bf16 ? __bfloat162float(((const bf16*)a.norm_w)[c]) : ((const float*)a.norm_w)[c];
+    }
+    if (EPI == EPI_ROPE && a.rot_half > 0) {
+        const int n_rot = a.m * a.rot_half;
+        for (int c = tid; c < n_rot; c += blockDim.x) { tables[c] = a.cos_t[c]; tables[n_rot + c] = a.sin_t[c]; }
+    }
     pdl_trigger();
     pdl_wait();
+    CISR_TRACE_WAITED();
+    if (!a.act) __syncthreads();                  // the norm weights are in shared memory
 
-    stage_tokens<MT>(a, hs, ldh);
+    stage_tokens<MT>(a, hs, ldh, nw, sums);
     __syncthreads();
+    CISR_TRACE_MARK(0);
 
     float acc[MT][4];
 #pragma unroll
@@ -193,6 +228,7 @@ __global__ void __launch_bounds__(512) skinny_kernel(const SkinnyArgs a) {
         }
     }
 
+    CISR_TRACE_MARK(1);
     // partial sums: red[ks][rt * 16 + row][token]
     const int rows_cta = RT * 16, mw = MT * 8;
 #pragma unroll
@@ -202,6 +238,7 @@ __global__ void __launch_bounds__(512) skinny_kernel(const SkinnyArgs a) {
         dst[(r + 8) * mw] = acc[mt][2]; dst[(r + 8) * mw + 1] = acc[mt][3];
     }
     __syncthreads();
+    CISR_TRACE_MARK(2);
 
     if (EPI == EPI_PLAIN) {
         for (int e = tid; e < rows_cta * a.m; e += blockDim.x) {
@@ -242,7 +279,7 @@ __global__ void __launch_bounds__(512) skinny_kernel(const SkinnyArgs a) {
                 int f, other; bool first;
                 if (a.interleaved) { f = d >> 1; first = !(d & 1); other = first ? d + 1 : d - 1; }
                 else { first = d < a.rot_half; f = first ? d : d - a.rot_half; other = first ? d + a.rot_half : d - a.rot_half; }
-                const float c = a.cos_t[(size_t)mrow * a.rot_half + f], s = a.sin_t[(size_t)mrow * a.rot_half + f];
+                const float c = tables[mrow * a.rot_half + f], s = tables[a.m * a.rot_half + mrow * a.rot_half + f];
                 const float o = red[(size_t)other * mw + mrow];
                 v = first ? v * c - o * s : v * c + o * s;
             }
@@ -266,12 +303,17 @@ int launch_epilogue(SkinnyArgs& a, cudaStream_t s) {
     else if (EPI == EPI_SWIGLU) { a.rt = 1; a.ks = SKINNY_KS; grid = (a.inter + 7) / 8; }
     else if (MT <= 2) { a.rt = 1; a.ks = SKINNY_KS; grid = (a.n + 15) / 16; }
     else { a.rt = 4; a.ks = 2; grid = (a.n + 63) / 64; }       // more tokens: stage them once per 64 features
-    size_t smem = sizeof(bf16) * (size_t)(MT * 8) * (a.k + 8) + sizeof(float) * (size_t)a.ks * a.rt * 16 * MT * 8;
+    const size_t extra = (a.act ? 0 : sizeof(float) * (size_t)a.k) +
+                         (EPI == EPI_ROPE ? sizeof(float) * 2 * (size_t)a.m * a.rot_half : 0);
+    size_t smem = sizeof(bf16) * (size_t)(MT * 8) * (a.k + 8) + sizeof(float) * (size_t)a.ks * a.rt * 16 * MT * 8 + extra;
     if (smem > 220 * 1024 && a.ks > 1 && EPI == EPI_PLAIN) {   // long rows and many tokens: give up the K split for room
         a.ks = 1;
-        smem = sizeof(bf16) * (size_t)(MT * 8) * (a.k + 8) + sizeof(float) * (size_t)a.rt * 16 * MT * 8;
+        smem = sizeof(bf16) * (size_t)(MT * 8) * (a.k + 8) + sizeof(float) * (size_t)a.rt * 16 * MT * 8 + extra;
     }
     if (smem > 220 * 1024) return -3;
+    const size_t sums_bytes = sizeof(float) * (size_t)(MT * 8) * a.k;
+    a.sums_in_smem = !a.act && smem + sums_bytes <= 100 * 1024;   // keep two CTAs per SM
+    if (a.sums_in_smem) smem += sums_bytes;
     static size_t configured = 48 * 1024;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(skinny_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -308,6 +350,7 @@ CISR_EXPORT int cisr_skinny_gemm(const void* w, int n, int k, const void* act, c
     SkinnyArgs a;
     a.w = (const bf16*)w; a.n = n; a.k = k; a.act = (const bf16*)act; a.x = x; a.delta = delta; a.norm_w = norm_w;
     a.norm_w_bf16 = norm_w_dtype == CISR_BF16; a.eps = eps; a.x_out = x_out; a.rows = rows; a.m = m; a.rt = 1; a.ks = 1;
+    a.sums_in_smem = 0;
     a.out_f32 = out_f32; a.out_bf16 = (bf16*)out_bf16; a.inter = inter; a.cos_t = cos_t; a.sin_t = sin_t;
     a.rot_half = rot_half; a.interleaved = interleaved; a.q_out = (bf16*)q_out; a.k_cache = (bf16*)k_cache;
     a.v_cache = (bf16*)v_cache; a.positions = positions; a.token_req = token_req; a.req_slot = req_slot;

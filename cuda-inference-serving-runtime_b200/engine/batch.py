@@ -19,8 +19,10 @@ import torch
 
 from ..ops import kernels
 
-SM_COUNT_TARGET = 296      # two CTAs per SM on a 148-SM part: what the decode split aims to fill
+CTA_TARGET = 444           # three CTAs per SM on a 148-SM part: what the decode split aims to fill
 SPLIT_QUANTUM = 64         # key ranges of the split are multiples of this
+SPLIT_MIN = 256            # a CTA's four warps each take tiles of up to 64 keys: a shorter range leaves warps idle
+CLUSTER_MAX = 16           # key ranges of one request and head that one thread-block cluster can merge
 
 
 @dataclass
@@ -64,7 +66,7 @@ class StepContext:
 
         Ranges start at multiples of the range size in absolute positions, so which keys
         fall together does not depend on the batch; the range size is chosen to give the
-        device about two CTAs per SM.
+        device about three CTAs per SM, and up to 16 ranges are merged inside one thread-block cluster.
         """
         if self.fixed_splits is not None:
             return self.fixed_splits
@@ -73,10 +75,13 @@ class StepContext:
 
 def plan_decode_splits(n_decode: int, kv_heads: int, max_ctx: int) -> Tuple[int, int]:
     ctas = max(1, n_decode * kv_heads)
-    wanted = max(1, -(-SM_COUNT_TARGET // ctas))
+    wanted = max(1, -(-CTA_TARGET // ctas))
     size = -(-max(1, max_ctx) // wanted)
-    size = max(SPLIT_QUANTUM, -(-size // SPLIT_QUANTUM) * SPLIT_QUANTUM)
-    return size, max(1, -(-max_ctx // size))
+    size = max(SPLIT_MIN, -(-size // SPLIT_QUANTUM) * SPLIT_QUANTUM)
+    n_splits = max(1, -(-max_ctx // size))
+    if n_splits > CLUSTER_MAX:       # whole clusters: the ranges beyond the context are empty
+        n_splits = -(-n_splits // CLUSTER_MAX) * CLUSTER_MAX
+    return size, n_splits
 
 
 class PinnedRing:

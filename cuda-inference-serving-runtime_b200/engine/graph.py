@@ -205,8 +205,12 @@ class ShapeGraph:
             torch.cuda.synchronize()
             before = dict(kernels.LAUNCHES)
             self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
-                self._run(ctx, update_views)
+            kernels.set_pdl(os.environ.get("CISR_PDL", "1") != "0")
+            try:
+                with torch.cuda.graph(self.graph):
+                    self._run(ctx, update_views)
+            finally:
+                kernels.set_pdl(False)
             self.launches = {k: kernels.LAUNCHES[k] - before[k] for k in before}
         self.graph.replay()
         self.replays += 1

@@ -81,8 +81,16 @@ def _digest(source: Path, defines: Mapping[str, object], extra: Sequence[str]) -
     return h.hexdigest()[:16]
 
 
+def _all_defines(defines: Optional[Mapping[str, object]]) -> dict:
+    """The caller's defines, plus CISR_TRACE=1 when the environment asks for the kernel timeline build."""
+    merged = dict(defines or {})
+    if os.environ.get("CISR_TRACE", "0") not in ("", "0"):
+        merged["CISR_TRACE"] = 1
+    return merged
+
+
 def library_path(source_name: str, defines: Optional[Mapping[str, object]] = None, extra: Sequence[str] = ()) -> Path:
-    defines = dict(defines or {})
+    defines = _all_defines(defines)
     source = CSRC / source_name
     tag = "_".join(f"{k.lower()}{v}" for k, v in sorted(defines.items()))
     stem = source.stem + (f"_{tag}" if tag else "")
@@ -92,7 +100,7 @@ def library_path(source_name: str, defines: Optional[Mapping[str, object]] = Non
 def compile_library(source_name: str, defines: Optional[Mapping[str, object]] = None, extra: Sequence[str] = (),
                     verbose: bool = True) -> Path:
     """Build (if not built yet) and return the path of the shared object."""
-    defines = dict(defines or {})
+    defines = _all_defines(defines)
     source = CSRC / source_name
     if not source.exists():
         raise BuildError(f"kernel source {source} is missing")

@@ -8,6 +8,7 @@ CUDA device or without the compiled kernels these functions fail.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -38,6 +39,7 @@ def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+_pdl_state = {"on": False}
 LAUNCHES = {"own": 0, "library": 0}   # kernels launched so far: this package's own, and vendor-library products
 
 
@@ -199,10 +201,40 @@ def attention_library(head_dim: int, dtype: torch.dtype, kind: str = "auto"):
             getattr(lib, name).restype = ctypes.c_int
         assert lib.cisr_attn_head_dim() == head_dim
         lib._tensor_core = source == "attention_mma.cu"
+        lib._tensor_maps = False
         if lib._tensor_core:
             lib.cisr_attn_set_pdl(int(_pdl_state["on"]))
+            lib.cisr_attn_decode_tma_ok.restype = ctypes.c_int
+            if head_dim % 64 == 0:          # the variant whose tiles arrive by tensor-map copies
+                lib.cisr_attn_tma_init.restype = ctypes.c_int
+                lib.cisr_attn_decode_tma.restype = ctypes.c_int
+                lib.cisr_attn_set_clusters(int(_cluster_state["on"]))
+                _check(lib.cisr_attn_tma_init(_p(_error_flag())), "attention tensor-map init", own=0)
+                lib._tensor_maps = True
         _attention_libs[key] = lib
     return lib
+
+
+_error_state = {}
+_cluster_state = {"on": os.environ.get("CISR_CLUSTERS", "0") not in ("", "0")}
+
+
+def set_clusters(on: bool) -> None:
+    """Whether the decode attention merges the key ranges of a request inside thread-block clusters, or writes every
+    range's partial sum for the merge kernel (the default: inside a chain of kernels that start early, clusters of 16
+    did not all become resident at once and the step was slower; CISR_CLUSTERS=1 in the environment turns them on)."""
+    _cluster_state["on"] = bool(on)
+    for lib in _attention_libs.values():
+        if lib._tensor_maps:
+            lib.cisr_attn_set_clusters(int(on))
+
+
+def _error_flag() -> torch.Tensor:
+    """One int on the device that a kernel sets when one of its bounded waits ran out."""
+    flag = _error_state.get("flag")
+    if flag is None:
+        flag = _error_state["flag"] = torch.zeros(1, dtype=torch.int32, device="cuda")
+    return flag
 
 
 def attention_jobs(head_dim: int, dtype: torch.dtype):
@@ -230,8 +262,12 @@ def attn_prefill(q, out, k_cache, v_cache, req_slot, block_table, tile_req, tile
 
 
 def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, q_start, ctx_len, partial, stats, hq, hkv,
-                page_size, scale, window, split_size, n_splits, kind: str = "auto") -> None:
-    """Attention of single new tokens, split over key ranges of `split_size`, merged into out."""
+                page_size, scale, window, split_size, n_splits, kind: str = "auto", staging: str = "auto") -> None:
+    """Attention of single new tokens, split over key ranges of `split_size`, merged into out.
+
+    `staging` picks how the tensor-core kernel brings key and value tiles in: "tensor_map" (one bulk copy per
+    page), "gather" (a 16-byte copy per thread), or "auto": tensor maps where the head size (a multiple of 64), the
+    page size (a multiple of 8 that divides 64 or is a multiple of it) and the range size allow them."""
     dim = k_cache.shape[-1]
     _need(q, k_cache.dtype, "q"); _need(out, k_cache.dtype, "out"); _need(k_cache, None, "k_cache", 4)
     _need(v_cache, k_cache.dtype, "v_cache", 4); _need(partial, torch.float32, "partial"); _need(stats, torch.float32, "stats")
@@ -240,10 +276,19 @@ def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec,
     if partial.numel() < n_dec * hq * n_splits * dim or stats.numel() < n_dec * hq * n_splits * 2:
         raise KernelError("attn_decode: scratch for partial sums is too small")
     lib = attention_library(dim, k_cache.dtype, kind)
-    args = [_p(q), _p(out), _p(k_cache), _p(v_cache), _p(req_slot), _p(block_table), block_table.shape[1], _p(dec_req), n_dec,
-            _p(q_start), _p(ctx_len), _p(partial), _p(stats), hq, hkv, page_size, ctypes.c_float(scale), int(window or 0),
-            split_size, n_splits, _stream()]
-    _check(lib.cisr_attn_decode(*args), "attn_decode", own=2)
+    tail = [_p(req_slot), _p(block_table), block_table.shape[1], _p(dec_req), n_dec, _p(q_start), _p(ctx_len), _p(partial),
+            _p(stats), hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), split_size, n_splits, _stream()]
+    if staging not in ("auto", "tensor_map", "gather"):
+        raise KernelError(f"unknown staging {staging!r}")
+    tensor_maps = (lib._tensor_maps and lib.cisr_attn_decode_tma_ok(page_size, split_size) and k_cache.is_contiguous()
+                   and v_cache.is_contiguous() and k_cache.data_ptr() % 16 == 0 and v_cache.data_ptr() % 16 == 0
+                   and k_cache.shape[0] * hkv * page_size < 2 ** 31)
+    if staging == "tensor_map" and not tensor_maps:
+        raise KernelError("attn_decode: tensor-map staging does not take this head size, page size, range size or cache")
+    if tensor_maps and staging != "gather":
+        _check(lib.cisr_attn_decode_tma(_p(q), _p(out), _p(k_cache), _p(v_cache), k_cache.shape[0], *tail), "attn_decode", own=2)
+    else:
+        _check(lib.cisr_attn_decode(_p(q), _p(out), _p(k_cache), _p(v_cache), *tail), "attn_decode", own=2)
 
 
 # ------------------------------------------------------------------ sampling
@@ -349,13 +394,13 @@ def set_pdl(on: bool) -> None:
     """Launch the decode-path kernels with programmatic dependent launch (a kernel may fetch its weights while the
     kernel before it is still running)."""
     _skinny().cisr_skinny_set_pdl(int(on))
+    _elementwise().cisr_elementwise_set_pdl(int(on))
+    if "lib" in _tcgen05_state:
+        _tcgen05_state["lib"].cisr_gemm_tcgen05_set_pdl(int(on))
     for (source, _, _), lib in list(_attention_libs.items()):
         if source == "attention_mma.cu":
             lib.cisr_attn_set_pdl(int(on))
     _pdl_state["on"] = bool(on)
-
-
-_pdl_state = {"on": False}
 
 
 def skinny_jobs():
@@ -441,9 +486,9 @@ def _tcgen05():
         lib.cisr_gemm_tcgen05.restype = ctypes.c_int
         lib.cisr_gemm_tcgen05_swiglu.restype = ctypes.c_int
         lib.cisr_gemm_tcgen05_rope.restype = ctypes.c_int
-        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
-        _check(lib.cisr_gemm_tcgen05_init(_p(flag)), "tcgen05 gemm init", own=0)
-        _tcgen05_state["lib"], _tcgen05_state["flag"] = lib, flag
+        _check(lib.cisr_gemm_tcgen05_init(_p(_error_flag())), "tcgen05 gemm init", own=0)
+        lib.cisr_gemm_tcgen05_set_pdl(int(_pdl_state["on"]))
+        _tcgen05_state["lib"] = lib
     return lib
 
 
@@ -505,7 +550,11 @@ def gemm_tcgen05_rope(a: torch.Tensor, w: torch.Tensor, rope: dict) -> None:
 
 def raise_if_kernel_gave_up() -> None:
     """Reads the flag a kernel sets when one of its bounded waits ran out (synchronises the device)."""
-    flag = _tcgen05_state.get("flag")
-    if flag is not None and int(flag.item()) != 0:
-        flag.zero_()
-        raise KernelError("a tcgen05 matrix product gave up waiting on a barrier; its output is not valid")
+    flag = _error_state.get("flag")
+    if flag is not None:
+        code = int(flag.item())
+        if code != 0:
+            flag.zero_()
+            what = "an attention kernel gave up waiting on a tensor-map copy" if code == 3 else \
+                "a tcgen05 matrix product gave up waiting on a barrier"
+            raise KernelError(f"{what}; its output is not valid")

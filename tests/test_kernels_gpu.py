@@ -115,15 +115,17 @@ def paged(k_dense, v_dense, page_size, n_pages, seed, dtype):
     return kc, vc, perm.astype(np.int32)
 
 
-def run_attention(q_all, k_all, v_all, q_lens, page_size, dtype, window=None, split_size=None, seed=0, width=64, kind="auto"):
-    """Requests given as whole sequences; the last q_lens[r] positions of each are this step's queries."""
+def run_attention(q_all, k_all, v_all, q_lens, page_size, dtype, window=None, split_size=None, seed=0, width=64, kind="auto",
+                  staging="auto", fill=0.0):
+    """Requests given as whole sequences; the last q_lens[r] positions of each are this step's queries.
+    Cache rows that no request has written hold `fill`."""
     k = kernels()
     R = len(q_all)
     hq, d = q_all[0].shape[1:]
     hkv = k_all[0].shape[1]
     n_pages = sum(-(-x.shape[0] // page_size) for x in k_all) + 3
-    kc = torch.zeros((n_pages, hkv, page_size, d), dtype=dtype)
-    vc = torch.zeros_like(kc)
+    kc = torch.full((n_pages, hkv, page_size, d), fill, dtype=dtype)
+    vc = torch.full_like(kc, fill)
     table = np.full((R + 1, width), -1, dtype=np.int32)
     perm = np.random.default_rng(seed).permutation(n_pages)
     used = 0
@@ -160,7 +162,7 @@ def run_attention(q_all, k_all, v_all, q_lens, page_size, dtype, window=None, sp
         partial = torch.full((len(dec_req), hq, n_splits, d), float("nan"), device=dev())
         stats = torch.full((len(dec_req), hq, n_splits, 2), float("nan"), device=dev())
         k.attn_decode(qd, out, kcd, vcd, req_slot, tab, i32(dec_req), len(dec_req), i32(q_start), i32(ctx), partial, stats,
-                      split_size=size, n_splits=n_splits, **args)
+                      split_size=size, n_splits=n_splits, staging=staging, **args)
     refs = []
     for r in range(R):
         qq = q_all[r].to(dtype).double(); kk = k_all[r].to(dtype).double(); vv = v_all[r].to(dtype).double()
@@ -186,6 +188,42 @@ def test_attention_mixed_portions_and_decode(d, hq, hkv, dtype, kind):
     out, ref = run_attention([x[0] for x in data], [x[1] for x in data], [x[2] for x in data], q_lens, 8, dtype, seed=d, kind=kind)
     assert torch.isfinite(out).all()
     close(out, ref, *ATT_TOL[dtype], "attention")
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(64, 9, 3), (128, 8, 2), (64, 40, 2)])
+@pytest.mark.parametrize("page_size", [8, 16, 64, 128])
+@pytest.mark.parametrize("staging,clusters", [("tensor_map", True), ("tensor_map", False), ("gather", False)])
+def test_decode_attention_by_tensor_map_copies_and_by_gather(d, hq, hkv, page_size, staging, clusters):
+    """Single tokens over contexts at tile, page and key-range edges, with both ways of staging the tiles.  Cache rows
+    that nobody wrote hold NaN: a value row beyond the newest key must not reach the output through a zero weight.
+    Forty query heads on two key heads take two launches of sixteen and four rows.  Ranges of 192 keys: eleven, merged
+    in one thread-block cluster; of 64: thirty-three, three clusters of eleven and the merge kernel; clusters off:
+    every range through the merge kernel."""
+    k = kernels()
+    lens = [1, 63, 64, 65, 200, 449, 512, 1000, 2100]
+    data = [random_qkv(t, hq, hkv, d, 7 * d + i, sharp=2.0) for i, t in enumerate(lens)]
+    k.set_clusters(clusters)
+    try:
+        for window, split_size in ((None, 192), (100, 192), (None, 64)):
+            out, ref = run_attention([x[0] for x in data], [x[1] for x in data], [x[2] for x in data], [1] * len(lens), page_size,
+                                     torch.bfloat16, window=window, split_size=split_size, seed=d + page_size, width=272,
+                                     staging=staging, fill=float("nan"))
+            assert torch.isfinite(out).all()
+            close(out, ref, *ATT_TOL[torch.bfloat16], f"decode attention, {staging}, window {window}, ranges of {split_size}")
+    finally:
+        k.set_clusters(False)
+
+
+def test_tensor_map_staging_refuses_what_it_cannot_take():
+    k = kernels()
+    i32 = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32), device=dev())
+    for d, page, split in ((48, 16, 64), (64, 12, 64), (64, 16, 100)):
+        q = torch.zeros(1, 2, d, dtype=torch.bfloat16, device=dev())
+        kc = torch.zeros(4, 1, page, d, dtype=torch.bfloat16, device=dev())
+        partial = torch.empty(1, 2, 2, d, device=dev()); stats = torch.empty(1, 2, 2, 2, device=dev())
+        with pytest.raises(k.KernelError, match="tensor-map staging"):
+            k.attn_decode(q, torch.empty_like(q), kc, kc.clone(), i32([0]), i32(np.zeros((1, 8))), i32([0]), 1, i32([0]), i32([5]),
+                          partial, stats, 2, 1, page, d ** -0.5, None, split, 2, staging="tensor_map")
 
 
 @pytest.mark.parametrize("needle", [0, 15, 16, 63, 64, 255, 256, 511, 640])
@@ -219,27 +257,30 @@ def test_attention_window_edge(window, dtype):
         close(out, ref, 5e-5 if dtype == torch.float32 else 0.3, 1e-5 if dtype == torch.float32 else 2e-2, f"window {window}")
 
 
-def test_attention_ignores_pages_that_the_window_has_passed():
-    """Entries of passed pages are -1 in the table; the kernels must not follow them."""
+@pytest.mark.parametrize("dtype,d", [(torch.float32, 16), (torch.bfloat16, 64)])
+def test_attention_ignores_pages_that_the_window_has_passed(dtype, d):
+    """Entries of passed pages are -1 in the table; the kernels must not follow them (bfloat16 heads of 64: the
+    decode kernel that stages by tensor-map copies fetches such a page from beyond the cache, as zeros)."""
     k = kernels()
-    t, hq, hkv, d, window, page = 100, 2, 1, 16, 20, 8
+    t, hq, hkv, window, page = 100, 2, 1, 20, 8
     q, k_, v = random_qkv(t, hq, hkv, d, 5)
-    kc, vc, pages = paged(k_, v, page, 20, 1, torch.float32)
+    q, k_, v = q.to(dtype).float(), k_.to(dtype).float(), v.to(dtype).float()
+    kc, vc, pages = paged(k_, v, page, 20, 1, dtype)
     i32 = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32), device=dev())
     for q_len in (1, 3):
         table = np.full((1, 16), -1, dtype=np.int32)
         table[0, :len(pages)] = pages
         dead = (t - q_len - window + 1) // page       # pages wholly before what the step's first query sees
         table[0, :dead] = -1
-        out = torch.empty(q_len, hq, d, device=dev())
-        common = (q[-q_len:].contiguous().to(dev()), out, kc.to(dev()), vc.to(dev()), i32([0]), i32(table))
+        out = torch.empty(q_len, hq, d, dtype=dtype, device=dev())
+        common = (q[-q_len:].contiguous().to(dtype).to(dev()), out, kc.to(dev()), vc.to(dev()), i32([0]), i32(table))
         if q_len == 1:
             partial = torch.empty(1, hq, 2, d, device=dev()); stats = torch.empty(1, hq, 2, 2, device=dev())
             k.attn_decode(*common, i32([0]), 1, i32([0]), i32([t]), partial, stats, hq, hkv, page, d ** -0.5, window, 64, 2)
         else:
             k.attn_prefill(*common, i32([0]), i32([0]), i32([0]), i32([q_len]), i32([t]), hq, hkv, page, d ** -0.5, window)
         ref = pl.causal_attention(q.double(), k_.double(), v.double(), window)[-q_len:]
-        close(out, ref, 3e-6, 1e-5, "window with freed pages")
+        close(out, ref, *ATT_TOL[dtype], "window with freed pages")
 
 
 @pytest.mark.parametrize("interleaved,rot", [(False, 32), (True, 32), (False, 16)])
