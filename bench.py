@@ -201,12 +201,15 @@ def entry_point_decode(model, batch: int, context: int, steps: int, warmup: int,
     seconds = time.perf_counter() - t0
     decoded = sum(t["decode_tokens"] for t in engine.trace[-steps:])
     graph = engine.stepper._ahead[0] if engine.stepper._ahead else None
-    h2d = graph.host.numel() * 4 if graph is not None else 0
+    # per step the host sends the block-table update lists (tokens are fed back on the device) and reads the sampled
+    # tokens with the kernels' status word
+    h2d = (graph.dev.numel() - graph.upd_start) * 4 if graph is not None else 0
+    d2h = (graph.rows + 1) * 4 if graph is not None else batch * 4
     for r in list(engine.active):
         engine.cancel(r.key)
     del engine
     torch.cuda.empty_cache()
-    return decoded / seconds, h2d, batch * 4
+    return decoded / seconds, h2d, d2h
 
 
 def prefill_run(model, tokens: int, seed: int, reps: int = 5, profile: bool = False):

@@ -1006,7 +1006,7 @@ CISR_EXPORT int cisr_attn_decode_tma_ok(int page_size, int split_size) {
 }
 
 #if HEAD_DIM % 64 == 0
-namespace { int* g_error = nullptr; bool g_clusters = false; }
+namespace { int* g_error = nullptr; bool g_clusters = false; int g_last_launches = 0; }
 
 // `error_flag`: one zeroed int in device memory that a kernel sets when a wait on a copy ran out.
 CISR_EXPORT int cisr_attn_tma_init(int* error_flag) {
@@ -1072,6 +1072,7 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
     }
     const int n_parts = n_splits / cluster;
     cudaStream_t s = (cudaStream_t)stream;
+    g_last_launches = (group + 15) / 16 + ((n_parts == 1 && cluster > 1) ? 0 : 1);
     for (int row0 = 0; row0 < group; row0 += 16) {
         status = launch_kernel_cluster(attn_decode_tma_kernel, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), smem, s, g_pdl, cluster,
                                        *map_k, *map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
@@ -1088,6 +1089,9 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
 #ifdef DEC_TRACE
 CISR_EXPORT int cisr_attn_trace_read(void* host, int bytes) { return (int)cudaMemcpyFromSymbol(host, g_trace, (size_t)bytes); }
 #endif
+
+// Kernels launched by the last cisr_attn_decode_tma call (the merge kernel is left out when one cluster covers all ranges).
+CISR_EXPORT int cisr_attn_decode_tma_launches() { return g_last_launches; }
 
 // 0 turns the clusters off (every key range then writes its partial sum and the merge kernel runs).
 CISR_EXPORT void cisr_attn_set_clusters(int on) { g_clusters = on != 0; }

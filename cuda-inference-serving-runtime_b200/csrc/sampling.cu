@@ -91,22 +91,36 @@ CISR_EXPORT int cisr_sample(const float* logits, int rows, int vocab, const floa
 // After a decode step whose tokens were chosen on the device: feed each live row's token back as its next
 // input and move its position, context length and sample counter on by one, so the next step can run without
 // the host.  Rows with live == 0 (padding) stay as they are.
+// With `ring` ([ring_slots][rows + 1] ints) the sampled tokens of all rows and, behind them, *status_in (the kernels'
+// "gave up on a wait" flag) are also written to slot (*step_index % ring_slots), and *step_index moves on by one: the
+// host copies a slot out while later steps, which write other slots, already run.  One block; any number of rows.
 __global__ void decode_advance_kernel(int* token_ids, int* positions, int* ctx_len, int* counter,
-                                      const int* __restrict__ sampled, const int* __restrict__ live, int rows) {
+                                      const int* __restrict__ sampled, const int* __restrict__ live, int rows,
+                                      const int* status_in, int* ring, int ring_slots, int* step_index) {
     CISR_TRACE_SCOPE(TRACE_DECODE_ADVANCE);
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= rows || !live[i]) return;
-    token_ids[i] = sampled[i];
-    positions[i] += 1;
-    ctx_len[i] += 1;
-    counter[i] += 1;
+    int* slot = nullptr;
+    if (ring) {
+        slot = ring + (size_t)(*step_index % ring_slots) * (rows + 1);
+        __syncthreads();                           // every thread has read the index before thread 0 moves it on
+        if (threadIdx.x == 0) { *step_index += 1; slot[rows] = status_in ? *status_in : 0; }
+    }
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) {
+        if (slot) slot[i] = sampled[i];
+        if (!live[i]) continue;
+        token_ids[i] = sampled[i];
+        positions[i] += 1;
+        ctx_len[i] += 1;
+        counter[i] += 1;
+    }
 }
 
 CISR_EXPORT int cisr_decode_advance(int* token_ids, int* positions, int* ctx_len, int* counter, const int* sampled,
-                                    const int* live, int rows, void* stream) {
+                                    const int* live, int rows, const int* status_in, int* ring, int ring_slots,
+                                    int* step_index, void* stream) {
     if (rows <= 0) return 0;
-    decode_advance_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>(token_ids, positions, ctx_len, counter,
-                                                                                 sampled, live, rows);
+    if (ring && (ring_slots <= 0 || !step_index)) return -2;
+    decode_advance_kernel<<<1, 128, 0, (cudaStream_t)stream>>>(token_ids, positions, ctx_len, counter, sampled, live, rows,
+                                                               status_in, ring, ring_slots, step_index);
     return launch_status();
 }
 

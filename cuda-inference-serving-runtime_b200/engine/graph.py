@@ -16,6 +16,9 @@ steps can run back to back without the host (`run_ahead`).
 """
 from __future__ import annotations
 
+import collections
+import contextlib
+import gc
 import os
 from collections import OrderedDict
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -28,6 +31,22 @@ from ..sampling import sample_tokens
 from .batch import HostBatch, StepContext, StepEntry
 
 MIN_CONTEXT_BUCKET = 256
+RING_SLOTS = 4
+
+
+@contextlib.contextmanager
+def no_collection():
+    """No automatic garbage collection inside: destroying an older CUDA graph (a captured step of a stepper that is no
+    longer referenced, found by a collection that an allocation happens to trigger) is not permitted while a stream is
+    capturing and would invalidate the capture."""
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was_enabled:
+            gc.enable()
 
 
 def bucket_of(n: int, minimum: int = 1) -> int:
@@ -73,6 +92,11 @@ class DecodeGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.tokens = torch.zeros(rows, dtype=torch.int32, device=device)
+        # every replay also leaves its tokens, and the kernels' error flag, in the next slot of a small ring, so the host
+        # can copy step k out while steps k + 1 .. k + RING_SLOTS - 1 run
+        self.ring = torch.zeros((RING_SLOTS, rows + 1), dtype=torch.int32, device=device)
+        self.step_index = torch.zeros(1, dtype=torch.int32, device=device)
+        self.slot_copies = collections.deque()      # (replay number, event) of copies out of ring slots still to be confirmed
         # the update lists are the tail of the buffer; two pinned copies of that tail, used in turn, let a step's lists be
         # written while the copy of the step before may still be on its way
         self.upd_start = min((self.offsets[f"upd_idx{g.index}"][0] for g in cache.page_groups), default=total)
@@ -111,7 +135,7 @@ class DecodeGraph:
         self.dev.copy_(self.host, non_blocking=True)
 
     def upload_updates(self, updates) -> None:
-        """Send only new block-table update lists (the rest of the buffer holds what the device fed back to itself)."""
+        """Send this step's block-table update lists (the rest of the buffer holds what the device fed back to itself)."""
         if self.upd_start >= self.dev.numel():
             return
         self.upd_turn ^= 1
@@ -144,7 +168,7 @@ class DecodeGraph:
                       self.d("counter"), out=self.tokens)
         if advance:
             kernels.decode_advance(self.d("token_ids"), self.d("positions"), self.d("ctx_len"), self.d("counter"),
-                                   self.tokens, self.d("live"))
+                                   self.tokens, self.d("live"), ring=self.ring, step_index=self.step_index)
 
     def capture(self) -> None:
         """Warm up once outside the graph (library set-up, kernel attributes), then capture."""
@@ -159,7 +183,7 @@ class DecodeGraph:
         pdl = os.environ.get("CISR_PDL", "1") != "0"
         kernels.set_pdl(pdl)        # inside the graph a kernel may fetch its weights while the one before it still runs
         try:
-            with torch.cuda.graph(self.graph):
+            with no_collection(), torch.cuda.graph(self.graph):
                 self._run(advance=True)
         finally:
             kernels.set_pdl(False)
@@ -168,6 +192,10 @@ class DecodeGraph:
     def replay(self) -> None:
         self.graph.replay()
         self.replays += 1
+
+    def last_slot(self) -> torch.Tensor:
+        """The ring slot the last replay wrote: its tokens, then the kernels' error flag."""
+        return self.ring[(self.replays - 1) % RING_SLOTS]
 
 
 class ShapeGraph:
@@ -207,7 +235,7 @@ class ShapeGraph:
             self.graph = torch.cuda.CUDAGraph()
             kernels.set_pdl(os.environ.get("CISR_PDL", "1") != "0")
             try:
-                with torch.cuda.graph(self.graph):
+                with no_collection(), torch.cuda.graph(self.graph):
                     self._run(ctx, update_views)
             finally:
                 kernels.set_pdl(False)

@@ -220,6 +220,11 @@ class Engine:
             remaining -= n
         return plan
 
+    def _staged(self, tokens):
+        """The last step's tokens as a handle whose read does not wait for later steps, where the stepper offers one."""
+        stage = getattr(self.stepper, "stage_last_tokens", None)
+        return stage() if stage is not None else tokens
+
     def _tick_deferred(self) -> bool:
         """Finish a decode step whose tokens were left on the device, launching the step after it first when nothing
         about the batch can change in between: the device feeds its own tokens back, so the host's read of step k
@@ -231,12 +236,19 @@ class Engine:
                   and all(len(r.generated) + 2 <= r.max_new_tokens for r in reqs))
         if stable and self.stepper.can_run_ahead():
             try:
-                ran = self.stepper.decode_ahead(1)
-                ahead = ran[0] if ran.shape[0] == 1 else None
+                if getattr(self.stepper, "stage_last_tokens", None) is not None:
+                    ahead = self._staged(None) if self.stepper.decode_ahead(1, history=False) == 1 else None
+                else:
+                    ran = self.stepper.decode_ahead(1)
+                    ahead = ran[0] if ran.shape[0] == 1 else None
             except OutOfPages:
                 ahead = None
-        chosen = tokens_dev.to("cpu").tolist()        # waits for step k only; step k + 1 is already queued behind it
-        self.stepper.check_kernels()
+        # waits for step k only: its copy to the host was queued before step k + 1
+        if hasattr(tokens_dev, "read"):
+            chosen = tokens_dev.read()                 # checks the kernels' error flag as of that step, too
+        else:
+            chosen = tokens_dev.to("cpu").tolist()
+            self.stepper.check_kernels()
         completed = time.perf_counter()
         decoded = 0
         for r, token in zip(reqs, chosen):
@@ -281,7 +293,7 @@ class Engine:
         if (self.lookahead and can_ahead is not None and can_ahead() and len(choosing) == len(plan)
                 and all(r.status == "decode" for r in choosing)):
             # a pure decode step from a graph: leave its tokens on the device until the next tick
-            self._deferred = (list(choosing), self.stepper.last_tokens, began)
+            self._deferred = (list(choosing), self._staged(self.stepper.last_tokens), began)
             return True
         chosen = self.choose(logits, choosing) if choosing else []
         check = getattr(self.stepper, "check_kernels", None)

@@ -11,7 +11,7 @@ logits for every row; here a request brings any number of tokens and names the r
 """
 from __future__ import annotations
 
-from typing import Dict, Optional, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -101,6 +101,18 @@ def commit_step(cache: CacheManager, entries: Sequence[StepEntry]) -> None:
         cache.commit(e.key, len(e.tokens))
 
 
+class StagedTokens:
+    """Sampled tokens on their way to pinned host memory; read() waits for that copy only."""
+
+    def __init__(self, pinned: torch.Tensor, event: "torch.cuda.Event", n: int, status_at: int):
+        self.pinned, self.event, self.n, self.status_at = pinned, event, n, status_at
+
+    def read(self) -> List[int]:
+        self.event.synchronize()
+        kernels.raise_for_code(int(self.pinned[self.status_at]))
+        return self.pinned[:self.n].tolist()
+
+
 class Stepper:
     """`graph=True` replays steps made only of single new tokens from captured CUDA graphs (see engine/graph.py);
     it is ignored when a mixer of the model reads the step through host values."""
@@ -109,11 +121,16 @@ class Stepper:
         if not model.loaded:
             raise RuntimeError("the model has no weights yet")
         self.model = model
+        self.max_slots = max_slots
         self.cache: CacheManager = model.make_cache(n_pages, page_size, max_slots)
         self.ring = PinnedRing()
         self.last_context: Optional[StepContext] = None
         self.last_extras: Dict[str, torch.Tensor] = {}
         self.last_tokens: Optional[torch.Tensor] = None     # tokens a graph step sampled itself
+        self._last_graph = None                             # the graph whose buffer `last_tokens` views, if it does
+        self._stage_slots = None                            # pinned buffers and events for stage_last_tokens
+        self._copy_stream = None                            # where staged copies run
+        self._stage_next = 0
         self.graphs = None
         if graph and all(layer.mixer.graph_safe for layer in model.layers):
             from .graph import DecodeGraphs
@@ -179,19 +196,23 @@ class Stepper:
         graph.upload()
         if fresh:
             graph.capture()
+        self._before_replay(graph)
         graph.replay()
         commit_step(cache, entries)
         self.last_context, self.last_extras = None, {}
         self.last_tokens = graph.tokens[:n].clone()       # a later replay overwrites the graph's own buffer
+        self._last_graph = None
         self._ahead = (graph, [e.key for e in entries])
         return graph.logits[:n]
 
-    def decode_ahead(self, steps: int) -> torch.Tensor:
+    def decode_ahead(self, steps: int, history: bool = True) -> Optional[torch.Tensor]:
         """Run up to `steps` more decode steps of the batch of the last step without the host in between.
 
         Each step feeds every request the token the step before sampled for it (on the device).  Valid only
         right after a step that ran from a graph; stops early at the graph's context limit.  Pages for all
-        the steps are reserved first, all or nothing.  Returns the sampled tokens, int32 [steps run, requests].
+        the steps are reserved first, all or nothing.  Returns the sampled tokens, int32 [steps run, requests];
+        with history=False nothing is kept but the last step's tokens (`last_tokens`, a view of the graph's own
+        buffer that the next replay overwrites: stage or copy it before), and the return value is the number of steps.
         """
         if self._ahead is None:
             raise RuntimeError("decode_ahead follows a step of single tokens that ran from a CUDA graph")
@@ -199,21 +220,78 @@ class Stepper:
         cache = self.cache
         longest = max(cache.length(k) for k in keys)
         steps = min(steps, graph.ctx_bucket - longest, self.model.spec.max_positions - longest)
-        if steps <= 0:
-            return torch.empty((0, len(keys)), dtype=torch.int32, device=self.model.device)
-        cache.reserve([(k, steps) for k in keys])
         device = self.model.device
+        if steps <= 0:
+            return torch.empty((0, len(keys)), dtype=torch.int32, device=device) if history else 0
+        cache.reserve([(k, steps) for k in keys])
         # new pages reach the device through the graph's own update lists (a pinned copy that does not wait for the step
         # in flight); applying the same list again in the later replays of this call changes nothing
         graph.upload_updates(self._flush_tables(graph.n_updates))
-        history = torch.empty((steps, graph.rows), dtype=torch.int32, device=device)
+        kept = torch.empty((steps, graph.rows), dtype=torch.int32, device=device) if history else None
         for i in range(steps):
+            self._before_replay(graph)
             graph.replay()
-            history[i].copy_(graph.tokens, non_blocking=True)
+            if kept is not None:
+                kept[i].copy_(graph.tokens, non_blocking=True)
         for k in keys:
             cache.commit(k, steps)
-        self.last_tokens = history[steps - 1, :len(keys)]
-        return history[:, :len(keys)]
+        if kept is None:
+            self.last_tokens = graph.tokens[:len(keys)]
+            self._last_graph = graph
+            return steps
+        self.last_tokens = kept[steps - 1, :len(keys)]
+        self._last_graph = None
+        return kept[:, :len(keys)]
 
     def can_run_ahead(self) -> bool:
         return self._ahead is not None
+
+    def _before_replay(self, graph) -> None:
+        """The coming replay writes the ring slot that the replay RING_SLOTS before it wrote: a staged copy out of that
+        slot must have run.  It has, steps ago, unless the host ran that far ahead of its own reads."""
+        from .graph import RING_SLOTS
+        copies = graph.slot_copies
+        while copies and graph.replays - copies[0][0] >= RING_SLOTS:
+            number, event = copies.popleft()
+            if not event.query():
+                torch.cuda.current_stream().wait_event(event)
+
+    def stage_last_tokens(self) -> "StagedTokens":
+        """Queue the copy of the last step's sampled tokens to pinned host memory right behind that step.
+
+        Reading the returned handle waits for that copy alone, not for steps queued after it, so the host can look at
+        step k's tokens while step k + 1 runs."""
+        if self.last_tokens is None:
+            raise RuntimeError("the last step did not sample its tokens on the device")
+        if self._stage_slots is None:
+            self._stage_slots = [(torch.zeros(2 * self.max_slots + 2, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+                                 for _ in range(4)]
+        pinned, event = self._stage_slots[self._stage_next]
+        self._stage_next = (self._stage_next + 1) % len(self._stage_slots)
+        n = self.last_tokens.numel()
+        graph = self._last_graph
+        # The copy runs on a stream of its own, behind an event that marks the end of the step: the next step on the
+        # main stream then starts without waiting for the copy engine.
+        main = torch.cuda.current_stream()
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream()
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(done)
+            if graph is not None:
+                # the ring slot that step wrote: its tokens, then the kernels' error flag as of that step.  Later
+                # replays write other slots, so nothing on the main stream has to wait for this copy.
+                pinned[:graph.rows + 1].copy_(graph.last_slot(), non_blocking=True)
+                status_at = graph.rows
+                graph.slot_copies.append((graph.replays - 1, event))
+            else:
+                pinned[:n].copy_(self.last_tokens, non_blocking=True)
+                flag = kernels.error_flag_tensor()      # the kernels' "gave up on a wait" flag travels with the tokens
+                if flag is not None:
+                    pinned[n:n + 1].copy_(flag, non_blocking=True)
+                else:
+                    pinned[n] = 0
+                status_at = n
+            event.record(self._copy_stream)
+        return StagedTokens(pinned, event, n, status_at)

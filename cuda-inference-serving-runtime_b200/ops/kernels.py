@@ -208,6 +208,7 @@ def attention_library(head_dim: int, dtype: torch.dtype, kind: str = "auto"):
             if head_dim % 64 == 0:          # the variant whose tiles arrive by tensor-map copies
                 lib.cisr_attn_tma_init.restype = ctypes.c_int
                 lib.cisr_attn_decode_tma.restype = ctypes.c_int
+                lib.cisr_attn_decode_tma_launches.restype = ctypes.c_int
                 lib.cisr_attn_set_clusters(int(_cluster_state["on"]))
                 _check(lib.cisr_attn_tma_init(_p(_error_flag())), "attention tensor-map init", own=0)
                 lib._tensor_maps = True
@@ -286,9 +287,10 @@ def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec,
     if staging == "tensor_map" and not tensor_maps:
         raise KernelError("attn_decode: tensor-map staging does not take this head size, page size, range size or cache")
     if tensor_maps and staging != "gather":
-        _check(lib.cisr_attn_decode_tma(_p(q), _p(out), _p(k_cache), _p(v_cache), k_cache.shape[0], *tail), "attn_decode", own=2)
+        status = lib.cisr_attn_decode_tma(_p(q), _p(out), _p(k_cache), _p(v_cache), k_cache.shape[0], *tail)
+        _check(status, "attn_decode", own=lib.cisr_attn_decode_tma_launches() if status == 0 else 0)
     else:
-        _check(lib.cisr_attn_decode(_p(q), _p(out), _p(k_cache), _p(v_cache), *tail), "attn_decode", own=2)
+        _check(lib.cisr_attn_decode(_p(q), _p(out), _p(k_cache), _p(v_cache), *tail), "attn_decode", own=-(-(hq // hkv) // 16) + 1)
 
 
 # ------------------------------------------------------------------ sampling
@@ -316,13 +318,24 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Opti
     return out
 
 
-def decode_advance(token_ids, positions, ctx_len, counter, sampled, live) -> None:
-    """Feed sampled tokens back as the next inputs of live rows and advance their positions, lengths and counters."""
+def decode_advance(token_ids, positions, ctx_len, counter, sampled, live, ring: Optional[torch.Tensor] = None,
+                   step_index: Optional[torch.Tensor] = None) -> None:
+    """Feed sampled tokens back as the next inputs of live rows and advance their positions, lengths and counters.
+
+    `ring` (int32 [slots, rows + 1]) with `step_index` (one int32): the sampled tokens and the kernels' error flag also
+    go to slot step_index % slots, and step_index moves on by one."""
     for name, t in (("token_ids", token_ids), ("positions", positions), ("ctx_len", ctx_len), ("counter", counter),
                     ("sampled", sampled), ("live", live)):
         _need(t, torch.int32, name, 1)
+    slots = 0
+    if ring is not None:
+        _need(ring, torch.int32, "ring", 2); _need(step_index, torch.int32, "step_index", 1)
+        if ring.shape[1] != token_ids.numel() + 1:
+            raise KernelError("decode_advance: ring must be [slots, rows + 1]")
+        slots = ring.shape[0]
     _check(_sampling().cisr_decode_advance(_p(token_ids), _p(positions), _p(ctx_len), _p(counter), _p(sampled), _p(live),
-                                           token_ids.numel(), _stream()), "decode_advance")
+                                           token_ids.numel(), _p(_error_state.get("flag")), _p(ring), slots, _p(step_index),
+                                           _stream()), "decode_advance")
 
 
 def uniform_host(seed: int, counter: int) -> float:
@@ -546,6 +559,23 @@ def gemm_tcgen05_rope(a: torch.Tensor, w: torch.Tensor, rope: dict) -> None:
         _p(a), _p(w), m, k, _p(rope["cos"]), _p(rope["sin"]), _p(rope["q_out"]), _p(rope["k_cache"]), _p(rope["v_cache"]),
         _p(rope["positions"]), _p(rope["token_req"]), _p(rope["req_slot"]), _p(rope["block_table"]),
         rope["block_table"].shape[1], rope["page_size"], hq, hkv, dim, _stream()), "gemm_tcgen05_rope")
+
+
+def error_flag_tensor() -> Optional[torch.Tensor]:
+    """The device flag, for callers that copy it to the host behind a step of their own (None before any kernel that
+    can give up was loaded)."""
+    return _error_state.get("flag")
+
+
+def raise_for_code(code: int) -> None:
+    """The error for a value read from the flag; clears the flag on the device."""
+    if code != 0:
+        flag = _error_state.get("flag")
+        if flag is not None:
+            flag.zero_()
+        what = "an attention kernel gave up waiting on a tensor-map copy" if code == 3 else \
+            "a tcgen05 matrix product gave up waiting on a barrier"
+        raise KernelError(f"{what}; its output is not valid")
 
 
 def raise_if_kernel_gave_up() -> None:

@@ -104,6 +104,35 @@ def test_decode_ahead_feeds_tokens_back_on_the_device(model_dir):
         stepper.step([StepEntry("a", [1, 2], [])]); stepper.decode_ahead(2)
 
 
+def test_staged_tokens_are_read_one_step_behind_the_device(model_dir):
+    """Step k + 1 is launched before the host reads step k's tokens from the ring slot that step wrote; the ring has four
+    slots and the run is longer than that, so slots are used again."""
+    from cisr_b200 import Model, StepEntry, Stepper
+
+    cfg, weights, path = model_dir
+    model = Model.from_pretrained(path, dtype="float32")
+    stepper = Stepper(model, n_pages=40, page_size=8, max_slots=3, graph=True)
+    prompts = {"a": tm.random_tokens(cfg, 9, 4), "b": tm.random_tokens(cfg, 17, 5)}
+    expected = {k: pl.generate_greedy(cfg, tm.torch_weights(weights), p, 13) for k, p in prompts.items()}
+    first = {}
+    for k, p in prompts.items():
+        stepper.create(k)
+        first[k] = int(stepper.step([StepEntry(k, p, [len(p) - 1])]).argmax())
+    stepper.step([StepEntry(k, [first[k]], [0]) for k in prompts])
+    got = [stepper.stage_last_tokens().read()]            # the first graph step: staged from its own copy
+    pending = None
+    for _ in range(11):
+        assert stepper.decode_ahead(1, history=False) == 1
+        handle = stepper.stage_last_tokens()
+        if pending is not None:
+            got.append(pending.read())
+        pending = handle
+    got.append(pending.read())
+    for col, k in enumerate(prompts):
+        assert [first[k]] + [row[col] for row in got] == expected[k]
+    stepper.cache.check()
+
+
 def test_a_mixer_that_reads_host_values_turns_graphs_off(model_dir):
     from cisr_b200 import Model, Stepper
     from cisr_b200.parts import Mixer
