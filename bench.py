@@ -242,6 +242,42 @@ def prefill_run(model, tokens: int, seed: int, reps: int = 5, profile: bool = Fa
     return ms
 
 
+def decode_timeline(model, batch: int, context: int, seed: int, path: str) -> int:
+    """The last of a few decode steps, launch by launch, from the kernels' own clock stamps (a development build of the
+    kernels, about a tenth slower than the ordinary one: compare shares and gaps, not absolutes)."""
+    import numpy as np
+    import torch
+    from cisr_b200 import StepEntry, Stepper
+    from cisr_b200.ops import trace
+
+    if not trace.enabled():
+        print("--timeline needs CISR_TRACE=1 in the environment (the kernels are then built with their recording code)")
+        return 2
+    page, steps, warmup = 16, 3, 4
+    stepper = Stepper(model, n_pages=batch * (-(-context // page) + 1), page_size=page, max_slots=batch, graph=True)
+    keys = [f"r{i}" for i in range(batch)]
+    last = fill_requests(stepper, keys, context - steps - warmup - 1, model.spec.vocab_size, seed)
+    stepper.step([StepEntry(k, [last[k]], [0]) for k in keys])
+    stepper.decode_ahead(warmup)
+    torch.cuda.synchronize()
+    trace.read()                                     # drop what the prompt and the warm-up recorded
+    stepper.decode_ahead(steps)
+    torch.cuda.synchronize()
+    records = trace.read()
+    start = records[records["kernel"] == 1]["entered"].max() - 20000      # the last step: from just before its embedding launch
+    step = records[records["entered"] >= start]
+    previous_end = None
+    print(f"{'kernel':28s} {'CTAs':>5s} {'first entry':>12s} {'released':>10s} {'last exit':>10s} {'after the one before':>21s}   (ns)")
+    for launch in trace.summary(step):
+        gap = "" if previous_end is None else str(launch["end"] - previous_end)
+        released = "" if launch["released"] is None else str(launch["released"])
+        print(f"{launch['kernel']:28s} {launch['ctas']:5d} {launch['begin']:12d} {released:>10s} {launch['end']:10d} {gap:>21s}")
+        previous_end = launch["end"]
+    trace.write_chrome_trace(step, path)
+    print(f"wrote {path}: {step.size} CTAs of one decode step")
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
@@ -257,6 +293,10 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and batch 64 points")
     parser.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                         help="decode: only the device-timed decode steps; prefill: only the 2048-token prompt (for profiling)")
+    parser.add_argument("--timeline", metavar="FILE", default=None,
+                        help="with CISR_TRACE=1 in the environment: run a few decode steps with kernels that record when each "
+                             "CTA entered, got past its wait and left; print the last step launch by launch and write it "
+                             "to FILE in the Trace Event format (chrome://tracing, Perfetto)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -275,6 +315,8 @@ def main() -> int:
     layers = raw["num_hidden_layers"]
     dtype_bytes = 2 if args.dtype == "bfloat16" else 4
 
+    if args.timeline:
+        return decode_timeline(model, args.batch, args.context, args.seed, args.timeline)
     if args.only == "prefill":
         ms = prefill_run(model, PREFILL_TOKENS, args.seed, reps=2, profile=True)
         print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(ms, 3)}))
