@@ -407,6 +407,8 @@ def set_pdl(on: bool) -> None:
     """Launch the decode-path kernels with programmatic dependent launch (a kernel may fetch its weights while the
     kernel before it is still running)."""
     _skinny().cisr_skinny_set_pdl(int(on))
+    if "lib" in _stream_state:
+        _stream_state["lib"].cisr_stream_set_pdl(int(on))
     _elementwise().cisr_elementwise_set_pdl(int(on))
     if "lib" in _tcgen05_state:
         _tcgen05_state["lib"].cisr_gemm_tcgen05_set_pdl(int(on))
@@ -417,13 +419,26 @@ def set_pdl(on: bool) -> None:
 
 
 def skinny_jobs():
-    return [("skinny_gemm.cu", {}, ())]
+    return [("skinny_gemm.cu", {}, ()), ("stream_gemm.cu", {}, ())]
+
+
+def stream_takes(tokens: int, w: torch.Tensor) -> bool:
+    """Whether skinny_gemm(kind="auto") hands this product to the persistent streaming kernel (stream_gemm.cu): a large
+    bfloat16 weight matrix, at most 16 tokens, the tokens and at least three 16 KB stages in shared memory.  (The
+    epilogues add their own conditions; where they fail the latency kernels take over.)"""
+    if w.dtype != torch.bfloat16 or not 0 < tokens <= STREAM_MAX_TOKENS or w.shape[1] % 8 or w.numel() * 2 < STREAM_MIN_BYTES:
+        return False
+    padded = 8 if tokens <= 8 else 16
+    fixed = 1024 + 64 + 4 * 8 * 16 * padded + tokens * (w.shape[1] + 8) * 2
+    return fixed + 3 * (16384 + 16) <= 224 * 1024 - 8192          # 8 KB kept for the rotation tables of the ROPE epilogue
 
 
 def skinny_ok(tokens: int, w: torch.Tensor) -> bool:
-    """Shapes the weight-streaming kernels take: bfloat16 weights, at most 64 tokens, K a multiple of 8."""
+    """Shapes the weight-streaming kernels take: bfloat16 weights, at most 16 tokens, K a multiple of 8."""
     if w.dtype != torch.bfloat16 or not 0 < tokens <= SKINNY_MAX_TOKENS or w.shape[1] % 8:
         return False
+    if stream_takes(tokens, w):
+        return True
     padded = -(-tokens // 8) * 8
     return padded * (w.shape[1] + 8) * 2 + 64 * padded * 4 * 2 <= 200 * 1024     # the tokens and the partial sums fit in shared memory
 
@@ -431,8 +446,12 @@ def skinny_ok(tokens: int, w: torch.Tensor) -> bool:
 def skinny_gemm(w: torch.Tensor, tokens: int, *, act: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None,
                 delta: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
                 x_out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None, epilogue: int = EPI_PLAIN,
-                out: Optional[torch.Tensor] = None, rope: Optional[dict] = None) -> None:
-    """out = prologue(input) @ w^T with a fused epilogue; see csrc/skinny_gemm.cu.
+                out: Optional[torch.Tensor] = None, rope: Optional[dict] = None, kind: str = "auto") -> None:
+    """out = prologue(input) @ w^T with a fused epilogue; see csrc/skinny_gemm.cu and csrc/stream_gemm.cu.
+
+    `kind`: "latency" (skinny_gemm.cu: a CTA per 16 output rows, weights straight to registers), "stream"
+    (stream_gemm.cu: persistent CTAs, weights through a ring of tensor-map copies; up to 16 tokens), or "auto": the
+    streaming kernel for weight matrices of 8 MB and more where it takes the shape.
 
     Input is either `act` (bfloat16 [tokens, K]) or the norm prologue (`x`, optional `delta`, `norm_w`, `eps`,
     optional `x_out` receiving x + delta, optional `rows` picking rows of x).  PLAIN writes float `out`
@@ -475,15 +494,40 @@ def skinny_gemm(w: torch.Tensor, tokens: int, *, act: Optional[torch.Tensor] = N
             _need(r[name], torch.int32, name)
         if r["rot_half"]:
             _need(r["cos"], torch.float32, "cos", 2); _need(r["sin"], torch.float32, "sin", 2)
-    status = _skinny().cisr_skinny_gemm(
-        _p(w), n, k, _p(act), _p(x), _p(delta), _p(norm_w), dtype_code(norm_w.dtype) if norm_w is not None else 0,
-        ctypes.c_float(eps), _p(x_out), _p(rows), tokens, epilogue, _p(out_f32), _p(out_b16),
-        n // 2 if epilogue == EPI_SWIGLU else 0, _p(r.get("cos")), _p(r.get("sin")), int(r.get("rot_half", 0)),
-        int(bool(r.get("interleaved", False))), _p(r.get("q_out")), _p(r.get("k_cache")), _p(r.get("v_cache")),
-        _p(r.get("positions")), _p(r.get("token_req")), _p(r.get("req_slot")), _p(r.get("block_table")),
-        r["block_table"].shape[1] if rope else 0, int(r.get("page_size", 0)), int(r.get("hq", 0)), int(r.get("hkv", 0)),
-        int(r.get("dim", 0)), _stream())
-    _check(status, "skinny_gemm")
+    args = (_p(w), n, k, _p(act), _p(x), _p(delta), _p(norm_w), dtype_code(norm_w.dtype) if norm_w is not None else 0,
+            ctypes.c_float(eps), _p(x_out), _p(rows), tokens, epilogue, _p(out_f32), _p(out_b16),
+            n // 2 if epilogue == EPI_SWIGLU else 0, _p(r.get("cos")), _p(r.get("sin")), int(r.get("rot_half", 0)),
+            int(bool(r.get("interleaved", False))), _p(r.get("q_out")), _p(r.get("k_cache")), _p(r.get("v_cache")),
+            _p(r.get("positions")), _p(r.get("token_req")), _p(r.get("req_slot")), _p(r.get("block_table")),
+            r["block_table"].shape[1] if rope else 0, int(r.get("page_size", 0)), int(r.get("hq", 0)), int(r.get("hkv", 0)),
+            int(r.get("dim", 0)), _stream())
+    if kind not in ("auto", "latency", "stream"):
+        raise KernelError(f"unknown kind {kind!r}")
+    if kind == "stream" or (kind == "auto" and tokens <= STREAM_MAX_TOKENS and w.numel() * 2 >= STREAM_MIN_BYTES):
+        status = _stream_lib().cisr_stream_gemm(*args)
+        if status != -2:                  # -2: not a shape for the streaming kernel
+            _check(status, "stream_gemm")
+            return
+        if kind == "stream":
+            raise KernelError("stream_gemm does not take this shape")
+    _check(_skinny().cisr_skinny_gemm(*args), "skinny_gemm")
+
+
+STREAM_MAX_TOKENS = 16
+STREAM_MIN_BYTES = 8 << 20       # smaller weight matrices are latency-bound: the kernels of skinny_gemm.cu serve them better
+_stream_state = {}
+
+
+def _stream_lib():
+    lib = _stream_state.get("lib")
+    if lib is None:
+        lib = load_library("stream_gemm.cu")
+        lib.cisr_stream_gemm.restype = ctypes.c_int
+        lib.cisr_stream_init.restype = ctypes.c_int
+        _check(lib.cisr_stream_init(_p(_error_flag())), "stream gemm init", own=0)
+        lib.cisr_stream_set_pdl(int(_pdl_state["on"]))
+        _stream_state["lib"] = lib
+    return lib
 
 
 # ------------------------------------------------------------------ tcgen05 + TMA matrix product
@@ -561,6 +605,11 @@ def gemm_tcgen05_rope(a: torch.Tensor, w: torch.Tensor, rope: dict) -> None:
         rope["block_table"].shape[1], rope["page_size"], hq, hkv, dim, _stream()), "gemm_tcgen05_rope")
 
 
+_GAVE_UP = {1: "a tcgen05 matrix product gave up waiting on a barrier",
+            3: "an attention kernel gave up waiting on a tensor-map copy",
+            4: "a weight-streaming product gave up waiting on a tensor-map copy"}
+
+
 def error_flag_tensor() -> Optional[torch.Tensor]:
     """The device flag, for callers that copy it to the host behind a step of their own (None before any kernel that
     can give up was loaded)."""
@@ -573,18 +622,11 @@ def raise_for_code(code: int) -> None:
         flag = _error_state.get("flag")
         if flag is not None:
             flag.zero_()
-        what = "an attention kernel gave up waiting on a tensor-map copy" if code == 3 else \
-            "a tcgen05 matrix product gave up waiting on a barrier"
-        raise KernelError(f"{what}; its output is not valid")
+        raise KernelError(f"{_GAVE_UP.get(code, _GAVE_UP[1])}; its output is not valid")
 
 
 def raise_if_kernel_gave_up() -> None:
     """Reads the flag a kernel sets when one of its bounded waits ran out (synchronises the device)."""
     flag = _error_state.get("flag")
     if flag is not None:
-        code = int(flag.item())
-        if code != 0:
-            flag.zero_()
-            what = "an attention kernel gave up waiting on a tensor-map copy" if code == 3 else \
-                "a tcgen05 matrix product gave up waiting on a barrier"
-            raise KernelError(f"{what}; its output is not valid")
+        raise_for_code(int(flag.item()))

@@ -25,8 +25,12 @@ def linear(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 def norm_fusable(h, tokens: int, w: torch.Tensor) -> bool:
     """Whether `h` is a pending norm that this product can compute in its own prologue."""
     from .base import PendingNorm
-    return (isinstance(h, PendingNorm) and h.fusable() and tokens <= kernels.SKINNY_NORM_MAX_TOKENS
-            and kernels.skinny_ok(tokens, w))
+    if not (isinstance(h, PendingNorm) and h.fusable() and tokens <= kernels.SKINNY_NORM_MAX_TOKENS
+            and kernels.skinny_ok(tokens, w)):
+        return False
+    # The persistent streaming kernel would redo the norm of every token in each of its CTAs, in front of a full ring
+    # of weights: beyond two tokens the norm kernel, once, and the activation prologue are faster.
+    return not (kernels.stream_takes(tokens, w) and tokens > 2)
 
 
 def as_tensor(h) -> torch.Tensor:

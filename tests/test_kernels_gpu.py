@@ -395,15 +395,20 @@ def test_unsupported_head_size_is_refused_clearly():
 
 
 @pytest.mark.parametrize("m", [1, 5, 8, 9, 16, 33, 64])
-@pytest.mark.parametrize("n,kk", [(100, 64), (576, 576), (49, 1536), (960, 240), (3000, 72)])
-def test_skinny_gemm_plain(m, n, kk):
-    """The weight-streaming product against a float64 product, from activations and from the fused norm."""
+@pytest.mark.parametrize("n,kk", [(100, 64), (576, 576), (49, 1536), (960, 240), (3000, 72), (5000, 1000)])
+@pytest.mark.parametrize("kind", ["latency", "stream"])
+def test_skinny_gemm_plain(m, n, kk, kind):
+    """The weight-streaming products (a CTA per 16 rows; persistent CTAs fed by tensor-map copies) against a float64
+    product, from activations and from the fused norm.  N and K that are no multiples of the tiles; K = 1000 ends in
+    the middle of a 64-wide box."""
     k = kernels()
+    if kind == "stream" and m > k.STREAM_MAX_TOKENS:
+        pytest.skip("the streaming kernel takes up to 16 tokens")
     g = torch.Generator().manual_seed(m * n + kk)
     w = (0.1 * torch.randn(n, kk, generator=g)).to(torch.bfloat16)
     a = torch.randn(m, kk, generator=g).to(torch.bfloat16)
     out = torch.full((m, n), float("nan"), device=dev())
-    k.skinny_gemm(w.to(dev()), m, act=a.to(dev()), epilogue=k.EPI_PLAIN, out=out)
+    k.skinny_gemm(w.to(dev()), m, act=a.to(dev()), epilogue=k.EPI_PLAIN, out=out, kind=kind)
     close(out, a.double() @ w.double().T, 2e-5 * math.sqrt(kk), 1e-5, "skinny plain")
     if m <= k.SKINNY_NORM_MAX_TOKENS:
         x = torch.randn(m + 3, kk, generator=g) * 2
@@ -412,15 +417,18 @@ def test_skinny_gemm_plain(m, n, kk):
         rows = torch.randperm(m + 3, generator=g)[:m].to(torch.int32)
         out2 = torch.full((m, n), float("nan"), device=dev())
         k.skinny_gemm(w.to(dev()), m, x=x.to(dev()), delta=delta.to(dev()), norm_w=nw.to(dev()), eps=1e-5, rows=rows.to(dev()),
-                      epilogue=k.EPI_PLAIN, out=out2)
+                      epilogue=k.EPI_PLAIN, out=out2, kind=kind)
         h = pl.rms_norm((x + delta).double()[rows.long()], nw.double(), 1e-5).to(torch.bfloat16).double()
         close(out2, h @ w.double().T, 2e-2, 2e-2, "skinny plain with norm prologue")
 
 
 @pytest.mark.parametrize("m", [1, 7, 16, 40])
-@pytest.mark.parametrize("inter,kk", [(176, 64), (1536, 576), (250, 96), (13, 40)])
-def test_skinny_gemm_swiglu_and_residual_output(m, inter, kk):
+@pytest.mark.parametrize("inter,kk", [(176, 64), (1536, 576), (250, 96), (13, 40), (2504, 1000)])
+@pytest.mark.parametrize("kind", ["latency", "stream"])
+def test_skinny_gemm_swiglu_and_residual_output(m, inter, kk, kind):
     k = kernels()
+    if kind == "stream" and (m > k.STREAM_MAX_TOKENS or inter % 8):
+        pytest.skip("the streaming kernel takes up to 16 tokens and feature counts that are multiples of 8")
     g = torch.Generator().manual_seed(m + inter)
     w = (0.2 * torch.randn(2 * inter, kk, generator=g)).to(torch.bfloat16)
     x = torch.randn(m, kk, generator=g)
@@ -432,21 +440,25 @@ def test_skinny_gemm_swiglu_and_residual_output(m, inter, kk):
         x_out = torch.full_like(x, float("nan")).to(dev())
         xd = x.to(dev())
         k.skinny_gemm(w.to(dev()), m, x=xd, delta=delta.to(dev()), norm_w=nw.to(dev()), eps=2e-6, x_out=x_out,
-                      epilogue=k.EPI_SWIGLU, out=act)
+                      epilogue=k.EPI_SWIGLU, out=act, kind=kind)
         close(x_out, x.double() + delta.double(), 1e-6, 1e-6, "residual sum written by CTA 0")
         assert torch.equal(xd.cpu(), x)                                   # the input stream is not touched
     else:
-        k.skinny_gemm(w.to(dev()), m, act=h.to(dev()), epilogue=k.EPI_SWIGLU, out=act)
+        k.skinny_gemm(w.to(dev()), m, act=h.to(dev()), epilogue=k.EPI_SWIGLU, out=act, kind=kind)
     gu = h.double() @ w.double().T
     ref = gu[:, :inter] / (1 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
     close(act, ref, 2e-2, 2e-2, "skinny swiglu")
 
 
 @pytest.mark.parametrize("m", [1, 8, 11, 30])
-@pytest.mark.parametrize("dim,hq,hkv,rot,interleaved", [(64, 9, 3, 64, False), (16, 2, 2, 16, False), (48, 5, 1, 32, True), (128, 2, 1, 128, False)])
-def test_skinny_gemm_rope_matches_the_separate_kernels(m, dim, hq, hkv, rot, interleaved):
+@pytest.mark.parametrize("dim,hq,hkv,rot,interleaved", [(64, 9, 3, 64, False), (16, 2, 2, 16, False), (48, 5, 1, 32, True), (128, 2, 1, 128, False),
+                                                        (96, 3, 1, 96, True), (32, 4, 2, 32, False)])
+@pytest.mark.parametrize("kind", ["latency", "stream"])
+def test_skinny_gemm_rope_matches_the_separate_kernels(m, dim, hq, hkv, rot, interleaved, kind):
     """Fused norm + q/k/v product + rotation + cache write against product -> rope_store on the same inputs."""
     k = kernels()
+    if kind == "stream" and (m > k.STREAM_MAX_TOKENS or dim % 32 or rot != dim):
+        pytest.skip("the streaming kernel takes up to 16 tokens, head sizes in steps of 32 and whole-head rotation")
     hidden, page, theta = 96, 4, 10000.0
     g = torch.Generator().manual_seed(m * dim)
     w = (0.2 * torch.randn((hq + 2 * hkv) * dim, hidden, generator=g)).to(torch.bfloat16).to(dev())
@@ -464,7 +476,7 @@ def test_skinny_gemm_rope_matches_the_separate_kernels(m, dim, hq, hkv, rot, int
         q = torch.zeros(m, hq, dim, dtype=torch.bfloat16, device=dev())
         kc = torch.zeros(36, hkv, page, dim, dtype=torch.bfloat16, device=dev()); vc = torch.zeros_like(kc)
         if fused:
-            k.skinny_gemm(w, m, act=hbf, epilogue=k.EPI_ROPE,
+            k.skinny_gemm(w, m, act=hbf, epilogue=k.EPI_ROPE, kind=kind,
                           rope=dict(cos=cos, sin=sin, rot_half=half, interleaved=interleaved, q_out=q, k_cache=kc, v_cache=vc,
                                     positions=positions, token_req=token_req, req_slot=req_slot, block_table=table, page_size=page,
                                     hq=hq, hkv=hkv, dim=dim))
