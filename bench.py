@@ -142,12 +142,15 @@ def fill_requests(stepper, keys, context: int, vocab: int, seed: int, chunk: int
     return last
 
 
+PAGE_SIZE = 16       # --page-size changes it for every run of the process
+
+
 def device_decode(model, batch: int, context: int, steps: int, warmup: int, seed: int):
     """tokens/s of `steps` decode steps ending at `context` tokens per request, timed with CUDA events."""
     import torch
     from cisr_b200 import StepEntry, Stepper
 
-    page = 16
+    page = PAGE_SIZE
     start_ctx = context - steps - warmup - 1
     pages = batch * (-(-context // page) + 1)
     stepper = Stepper(model, n_pages=pages, page_size=page, max_slots=batch, graph=True)
@@ -181,7 +184,7 @@ def entry_point_decode(model, batch: int, context: int, steps: int, warmup: int,
     import torch
     from cisr_b200 import Engine, Request
 
-    page = 16
+    page = PAGE_SIZE
     prompt_len = context - steps - warmup - 2
     engine = Engine.for_model(model, pages=batch * (-(-context // page) + 2), page_size=page, max_active=batch,
                               token_budget=max(2048, batch), prefill_chunk=2048, policy="decode_first", graph=True)
@@ -219,7 +222,7 @@ def prefill_run(model, tokens: int, seed: int, reps: int = 5, profile: bool = Fa
 
     rng = np.random.default_rng(seed + 2)
     ids = rng.integers(0, model.spec.vocab_size, size=tokens).tolist()
-    stepper = Stepper(model, n_pages=-(-tokens // 16) + 1, page_size=16, max_slots=1, graph=True)
+    stepper = Stepper(model, n_pages=-(-tokens // PAGE_SIZE) + 1, page_size=PAGE_SIZE, max_slots=1, graph=True)
     times = []
     for rep in range(reps + 3):
         stepper.create("p")
@@ -253,7 +256,7 @@ def decode_timeline(model, batch: int, context: int, seed: int, path: str) -> in
     if not trace.enabled():
         print("--timeline needs CISR_TRACE=1 in the environment (the kernels are then built with their recording code)")
         return 2
-    page, steps, warmup = 16, 3, 4
+    page, steps, warmup = PAGE_SIZE, 3, 4
     stepper = Stepper(model, n_pages=batch * (-(-context // page) + 1), page_size=page, max_slots=batch, graph=True)
     keys = [f"r{i}" for i in range(batch)]
     last = fill_requests(stepper, keys, context - steps - warmup - 1, model.spec.vocab_size, seed)
@@ -293,6 +296,7 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and batch 64 points")
     parser.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                         help="decode: only the device-timed decode steps; prefill: only the 2048-token prompt (for profiling)")
+    parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the trace program uses 16)")
     parser.add_argument("--timeline", metavar="FILE", default=None,
                         help="with CISR_TRACE=1 in the environment: run a few decode steps with kernels that record when each "
                              "CTA entered, got past its wait and left; print the last step launch by launch and write it "
@@ -307,6 +311,8 @@ def main() -> int:
         print(f"bench.py measures one GPU: this engine is single-GPU by design (--gpus {args.gpus} is not run)")
         return 2
     args.warmup = max(args.warmup, 3)
+    global PAGE_SIZE
+    PAGE_SIZE = args.page_size
 
     import torch
 
@@ -350,7 +356,7 @@ def main() -> int:
                    "layers": layers, "layers_of_preset": full_layers, "hidden_size": raw["hidden_size"],
                    "intermediate_size": raw["intermediate_size"], "heads": raw["num_attention_heads"],
                    "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"], "vocab_size": raw["vocab_size"],
-                   "page_size": 16, "decode": "cuda graph, tokens fed back on device", "peaks": peak_source,
+                   "page_size": PAGE_SIZE, "decode": "cuda graph, tokens fed back on device", "peaks": peak_source,
                    "l2": "inputs larger than L2 (weights + cache per step), no flush"},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches["own"] * args.steps, "library_gemm_launches": launches["library"] * args.steps,

@@ -1,0 +1,400 @@
+// Causal grouped-query attention of prompt portions on the 5th-generation tensor cores, for head sizes 64 and 128
+// (bfloat16 cache).  One CTA per (128-query tile, query head); scores and the output accumulate in tensor memory.
+//
+//   warp 0      producer: the query tile once, then key and value tiles (128 keys at head size 64, 64 at 128) into a
+//               four-stage ring, by
+//               tensor-map copies (cp.async.bulk.tensor.2d, 128-byte swizzle), one box per page and 64 columns
+//   warp 1      one thread issues the products: S = Q K^T (tcgen05.mma kind::f16, M = 128, N = 128, K = 16 steps,
+//               Q and K both K-major) into one of two score buffers in tensor memory, and O += P V (N = head size,
+//               V as the MN-major B operand straight from its [key][dim] tile); the score product of tile j + 1 is
+//               issued before the output product of tile j, so it runs while the softmax warps work on tile j
+//   warps 2..5  softmax: thread r owns query row r (tensor-memory lane r): it reads its row of S with tcgen05.ld,
+//               keeps the running max and sum in float, writes P = 2^(s - m) as bfloat16 into shared memory in the
+//               layout the tensor core reads (K-major, swizzled), and rescales its row of O in tensor memory only
+//               when the max has grown by more than 8 (a stale max is exact arithmetic as long as 2^(s - m) stays
+//               small; the final division by the sum uses the same max)
+//
+// Exactness: scores are scaled by scale * log2(e) in float after the product, exponentials are base 2 (ex2.approx),
+// the sum and the max are float, P is rounded to bfloat16 once.  The keys a query sees and their order do not depend
+// on the batch: tiles start at multiples of 128 in absolute positions.
+//
+// Every wait on an mbarrier is bounded; a role whose wait ran out raises the CTA's abort flag and the device flag
+// (5), the other roles leave at their next wait, tensor memory is freed, and the host reports the failure.
+//
+// Parity: the online softmax of runtime/reference.py:18-27 and kernels/ops.cu:88-123 of the reference, tiled.
+// Cache layout: [pages, kv_heads, page_size, HEAD_DIM]; page sizes: multiples of 8 that divide 128 or are multiples of it.
+#include "tcgen05.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=64 or 128"
+#endif
+#if HEAD_DIM != 64 && HEAD_DIM != 128
+#error "the tcgen05 attention takes head sizes 64 and 128"
+#endif
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int D = HEAD_DIM;
+constexpr int NSUB = D / 64;                  // 64-column sub-tiles of Q, K and V rows
+constexpr int BN = D == 64 ? 128 : 64;        // keys per tile: a tile's keys and values are 32 KB at either head size
+constexpr int SUB_BYTES = 128 * 128;          // one 128-row x 64-column sub-tile (queries, probabilities)
+constexpr int KV_SUB = BN * 128;              // one BN-key x 64-column sub-tile (keys, values)
+constexpr int Q_BYTES = NSUB * SUB_BYTES;
+constexpr int KV_BYTES = NSUB * KV_SUB;       // a K tile, or a V tile
+constexpr int P_BYTES = (BN / 64) * SUB_BYTES;   // 128 rows x BN keys in 64-key sub-tiles
+constexpr int STAGES = 4;                     // key/value tiles on their way: a copy takes several tiles' worth of time to land
+constexpr size_t SMEM_FIXED = 1024 + Q_BYTES + STAGES * 2 * KV_BYTES + P_BYTES + 256 + 4 * 128 * sizeof(float);
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_STEP = 8.f;           // the max may lag by this much (base-2 exponent) before O is rescaled
+constexpr int SOFTMAX_THREADS = 256;          // two groups of four warps: each thread has half of a query row's columns
+constexpr int THREADS = 64 + SOFTMAX_THREADS;
+constexpr int HALF = BN / 2;                  // score columns per softmax thread and tile
+bool g_pdl = false;
+int* g_error = nullptr;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, int cache_rows,
+                            const int* __restrict__ req_slot, const int* __restrict__ block_table, int table_width,
+                            const int* __restrict__ tile_req, const int* __restrict__ tile_q0,
+                            const int* __restrict__ q_start, const int* __restrict__ q_len,
+                            const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window,
+                            int* __restrict__ error) {
+    CISR_TRACE_SCOPE(TRACE_ATTN_PREFILL);
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = base;                                   // [NSUB][128 queries][128 B]
+    unsigned char* KVs = Qs + Q_BYTES;                          // [STAGES][K tile | V tile], each [NSUB][BN keys][128 B]
+    unsigned char* Ps = KVs + STAGES * 2 * KV_BYTES;            // [BN / 64][128 queries][128 B]: 64 keys per sub-tile
+    uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + P_BYTES);
+    uint64_t* q_full = bars;                                    // the query tile has landed
+    uint64_t* kv_full = bars + 1;                               // [STAGES] a stage's keys and values have landed
+    uint64_t* kv_empty = kv_full + STAGES;                      // [STAGES] the products that read the stage are done
+    uint64_t* s_full = kv_empty + STAGES;                       // [2] a score buffer is complete
+    uint64_t* s_empty = s_full + 2;                             // [2] the softmax threads have read it
+    uint64_t* p_full = s_empty + 2;                             // P is in shared memory (and O rescaled)
+    uint64_t* pv_done = p_full + 1;                             // the output product of a tile is done
+    static_assert(1 + 2 * STAGES + 6 <= 15, "the barriers and the two words behind them fit 128 bytes");
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+    float* exchange = reinterpret_cast<float*>(bars + 16);      // [2 sets][2 groups][128 rows]: the groups' maxima of a tile, then their sums
+    int* pages = reinterpret_cast<int*>(exchange + 4 * BM);     // block table entries of this tile's key range
+
+    pdl_trigger();
+    const int tile = blockIdx.x, head = blockIdx.y;
+    const int req = tile_req[tile], q0 = tile_q0[tile];
+    const int rows = min(BM, q_len[req] - q0);
+    const int tok0 = q_start[req] + q0;
+    const int ctx = ctx_len[req];
+    const int qpos0 = ctx - q_len[req] + q0;
+    const int kvh = head / (hq / hkv);
+    const int* table = block_table + (size_t)req_slot[req] * table_width;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    const int k_end = qpos0 + rows;                                                       // the last row sees keys up to its own position
+    const int k_begin = ((window > 0 ? max(0, qpos0 - window + 1) : 0) / BN) * BN;
+    const int n_tiles = (k_end - k_begin + BN - 1) / BN;
+    const int first_page = k_begin / page_size;
+    for (int i = tid; i <= (k_end - 1) / page_size - first_page; i += THREADS) pages[i] = table[first_page + i];
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(s_full + s, 1); mbar_init(s_empty + s, SOFTMAX_THREADS); }
+        mbar_init(p_full, SOFTMAX_THREADS);
+        mbar_init(pv_done, 1);
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) {    // two score buffers of 128 columns and the output: 512 columns, all of this SM's tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base + 256;
+    pdl_wait();          // the queries, and this step's keys and values, come from the kernel before
+    CISR_TRACE_WAITED();
+
+    auto gave_up = [&]() {
+        atomicExch(error, 5);
+        *(volatile int*)abort_flag = 1;
+    };
+    auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {     // false: leave (this or another role gave up)
+        if (*(volatile int*)abort_flag) return false;
+        if (mbar_wait(bar, parity)) return true;
+        gave_up();
+        return false;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            mbar_expect_tx(q_full, (uint32_t)Q_BYTES);
+            for (int sub = 0; sub < NSUB; ++sub) tma_load_2d(Qs + sub * SUB_BYTES, &map_q, head * D + sub * 64, tok0, q_full);
+        }
+        const int box_rows = min(page_size, BN), boxes = BN / box_rows;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j % STAGES;
+            bool ok = true;
+            if (j >= STAGES) ok = wait(kv_empty + s, ((j / STAGES) & 1) ^ 1);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            unsigned char* Ks = KVs + s * 2 * KV_BYTES;
+            if (lane == 0) mbar_expect_tx(kv_full + s, (uint32_t)(2 * KV_BYTES));
+            __syncwarp();
+            for (int b = lane; b < 2 * NSUB * boxes; b += 32) {
+                const int i = b % boxes, sub = (b / boxes) % NSUB, is_v = b / (boxes * NSUB);
+                const int kpos = k_begin + j * BN + i * box_rows;
+                const int page = kpos < k_end ? pages[kpos / page_size - first_page] : -1;
+                const int row = page < 0 ? cache_rows : (page * hkv + kvh) * page_size + kpos % page_size;   // beyond the cache: zeros
+                tma_load_2d(Ks + is_v * KV_BYTES + sub * KV_SUB + i * box_rows * 128, is_v ? &map_v : &map_k, sub * 64, row, kv_full + s);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ products
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_idesc(BN);
+            constexpr uint32_t idesc_o = umma_idesc(D) | UMMA_B_MN_MAJOR;
+            auto output_product = [&](int j) {                    // O += P(j) V(j)
+                const unsigned char* Vs = KVs + (j % STAGES) * 2 * KV_BYTES + KV_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < BN / 16; ++ks) {            // 16 keys per step: P along its K (32 bytes), V two 8-row groups down
+                    const uint64_t desc_p = umma_desc(Ps + (ks >> 2) * SUB_BYTES) + 2 * (ks & 3);
+                    const uint64_t desc_v = umma_desc_mn_major(Vs + ks * 16 * 128, KV_SUB);
+                    umma_bf16(tmem_o, desc_p, desc_v, idesc_o, (j | ks) != 0);
+                }
+                umma_commit(pv_done);
+                umma_commit(kv_empty + j % STAGES);
+            };
+            bool ok = wait(q_full, 0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1, ph = (j >> 1) & 1;              // the score buffer and its phase
+                ok = wait(kv_full + j % STAGES, (j / STAGES) & 1) && wait(s_empty + s, ph ^ 1);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const unsigned char* Ks = KVs + (j % STAGES) * 2 * KV_BYTES;
+#pragma unroll
+                for (int kd = 0; kd < D / 16; ++kd) {             // 16 of the head's dimensions per step
+                    const uint64_t desc_q = umma_desc(Qs + (kd >> 2) * SUB_BYTES) + 2 * (kd & 3);
+                    const uint64_t desc_k = umma_desc(Ks + (kd >> 2) * KV_SUB) + 2 * (kd & 3);
+                    umma_bf16(tmem_base + (uint32_t)(s * BN), desc_q, desc_k, idesc_s, kd != 0);
+                }
+                umma_commit(s_full + s);
+                if (j > 0) {
+                    ok = wait(p_full, (j - 1) & 1);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    output_product(j - 1);
+                }
+            }
+            if (ok && wait(p_full, (n_tiles - 1) & 1)) {
+                tcgen05_fence_after();
+                output_product(n_tiles - 1);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax and output
+        // Two groups of four warps; thread (group, r) has columns [64 * group, 64 * group + 64) of query row r of every
+        // score tile.  The two threads of a row exchange their maxima through shared memory, so both follow the same
+        // max; each keeps the sum of its own half, added at the end.
+        const int quarter = warp & 3;                              // the 32 tensor-memory lanes this warp may touch
+        const int group = (warp - 2) >> 2;
+        const int row = quarter * 32 + lane;
+        const int qpos = qpos0 + row;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const float scale2 = scale * LOG2E;
+        auto softmax_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory"); };
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        // (Requesting the scores of tile j + 1 while tile j is worked on, into a second set of registers, was slower.)
+        auto request = [&](int j, uint32_t* dst) {
+            const uint32_t addr = tmem_base + lane_base + (uint32_t)((j & 1) * BN + group * HALF);
+#pragma unroll
+            for (int c0 = 0; c0 < HALF; c0 += 32) tmem_load32_nowait(addr + c0, dst + c0);
+        };
+        uint32_t raw[HALF];
+        // A warp whose wait ran out keeps walking the tiles (every later wait returns at once) so that the barrier between
+        // the two groups is reached the same number of times by all.
+        auto step = [&](int j) {
+            const int s = j & 1;
+            if (ok) ok = __all_sync(0xffffffffu, wait(s_full + s, (j >> 1) & 1));
+            const int kt = k_begin + j * BN;                       // the tile's first key
+            const int k0 = kt + group * HALF;                     // this thread's first key
+            // tiles on the diagonal, at the window's start and at the end of the keys need the per-element mask
+            const bool edge = kt + BN - 1 > qpos0 || kt + BN > k_end || (window > 0 && kt <= qpos0 + BM - 1 - window);
+            auto masked = [&](int kpos) { return kpos > qpos || kpos >= k_end || (window > 0 && kpos <= qpos - window); };
+            float m_tile = -INFINITY;
+            if (ok) {
+                tcgen05_fence_after();
+                request(j, raw);
+                tmem_load_wait();              // this tile's half row of scores is in registers: the buffer can take tile j + 2
+                tcgen05_fence_before();
+                mbar_arrive(s_empty + s);
+                if (edge) {
+#pragma unroll
+                    for (int c = 0; c < HALF; ++c)
+                        if (masked(k0 + c)) raw[c] = __float_as_uint(-INFINITY);
+                }
+                // this half's max (the scale is positive: the max of the raw scores, scaled)
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int c = 0; c < HALF; c += 4) {
+                    mx[0] = fmaxf(mx[0], __uint_as_float(raw[c])); mx[1] = fmaxf(mx[1], __uint_as_float(raw[c + 1]));
+                    mx[2] = fmaxf(mx[2], __uint_as_float(raw[c + 2])); mx[3] = fmaxf(mx[3], __uint_as_float(raw[c + 3]));
+                }
+                m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;
+            }
+            // the two threads of a row exchange their maxima (a read of the partner's half from tensor memory instead
+            // costs a second load round trip, which was slower); every warp reaches this barrier in every iteration
+            float* slot = exchange + (j & 1) * 2 * BM;           // two sets: a thread a tile ahead writes the other one
+            slot[group * BM + row] = m_tile;
+            softmax_sync();
+            m_tile = fmaxf(m_tile, slot[(group ^ 1) * BM + row]);
+            if (!ok) return;
+            // the max in use moves only when it lags by more than RESCALE_STEP; the first finite max is taken as it is
+            float alpha = 1.f;
+            if (m_tile > m_used + RESCALE_STEP || (m_used == -INFINITY && m_tile > -INFINITY)) {
+                alpha = m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_tile);
+                m_used = m_tile;
+            }
+            const float m_ref = m_used == -INFINITY ? 0.f : m_used;
+            // P = 2^(s - m), rounded to bfloat16 for the product; the sum keeps the unrounded values
+            float sums[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t* packed = raw;                               // pair c / 2 takes the place of scores already used
+#pragma unroll
+            for (int c = 0; c < HALF; c += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(raw[c]), scale2, -m_ref));       // -inf (masked) gives 0
+                const float p1 = fast_exp2(fmaf(__uint_as_float(raw[c + 1]), scale2, -m_ref));
+                sums[(c >> 1) & 3] += p0 + p1;
+                __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+            }
+            const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            // P's buffer and O are free once the output product of the tile before is done
+            if (j > 0) ok = __all_sync(0xffffffffu, wait(pv_done, (j - 1) & 1));
+            if (!ok) return;
+            tcgen05_fence_after();
+            if (group == 0 && j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {   // tensor-memory access is warp-wide: all lanes go, most with alpha 1
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t acc[32];
+                    tmem_load32(tmem_o + lane_base + c0, acc);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) acc[c] = __float_as_uint(__uint_as_float(acc[c]) * alpha);
+                    tmem_store32(tmem_o + lane_base + c0, acc);
+                }
+            }
+            l = l * alpha + sum;
+#pragma unroll
+            for (int q = 0; q < HALF / 8; ++q) {                  // 16-byte chunks of the row, in 64-key sub-tiles, swizzled
+                const int chunk = group * (HALF / 8) + q;
+                *reinterpret_cast<uint4*>(Ps + (chunk >> 3) * SUB_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4)) =
+                    make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            }
+            tcgen05_fence_before();
+            if (k_begin + j * BN + BN > k_end) {
+                // Value rows beyond the last key were never written, or are left over from another request: they must
+                // not meet the zero probabilities of those keys (0 * NaN).  The stage has landed (S came from it).
+                unsigned char* Vs = KVs + (j % STAGES) * 2 * KV_BYTES + KV_BYTES;
+                for (int e = tid - 64; e < BN * NSUB * 8; e += SOFTMAX_THREADS) {
+                    const int r = e / (NSUB * 8), c = e - r * (NSUB * 8);
+                    if (k_begin + j * BN + r >= k_end)
+                        *reinterpret_cast<uint4*>(Vs + (c >> 3) * KV_SUB + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and the zeroed rows) before the tensor core reads them
+            mbar_arrive(p_full);
+        };
+        for (int j = 0; j < n_tiles; ++j) step(j);
+        if (ok) ok = wait(pv_done, (n_tiles - 1) & 1);
+        const bool all_ok = __all_sync(0xffffffffu, ok);
+        if (!all_ok) *(volatile int*)abort_flag = 1;
+        // the row's sum: both halves; each group then writes half of the output columns
+        exchange[group * BM + row] = l;
+        softmax_sync();
+        if (all_ok && !*(volatile int*)abort_flag) {
+            tcgen05_fence_after();
+            const float total = exchange[row] + exchange[BM + row];
+            const float inv = total > 0.f ? 1.f / total : 0.f;
+            bf16* dst = out + ((size_t)(tok0 + row) * hq + head) * D;
+#pragma unroll 1
+            for (int c0 = group * (D / 2); c0 < (group + 1) * (D / 2); c0 += 32) {
+                uint32_t acc[32];
+                tmem_load32(tmem_o + lane_base + c0, acc);          // warp-wide, also for rows beyond the portion
+                if (row < rows) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(acc[8 * q + 2 * e]) * inv,
+                                                                        __uint_as_float(acc[8 * q + 2 * e + 1]) * inv);
+                            w[e] = *reinterpret_cast<uint32_t*>(&pair);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c0 + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+}
+}  // namespace
+
+CISR_EXPORT int cisr_attn_tcgen05_head_dim() { return D; }
+CISR_EXPORT int cisr_attn_tcgen05_tile() { return BM; }
+CISR_EXPORT void cisr_attn_tcgen05_set_pdl(int on) { g_pdl = on != 0; }
+
+// `error_flag`: one zeroed int in device memory that the kernel sets (to 5) when one of its waits ran out.
+CISR_EXPORT int cisr_attn_tcgen05_init(int* error_flag) {
+    if (int status = tma_load_encoder()) return status;
+    g_error = error_flag;
+    return 0;
+}
+
+// 1 when the kernel takes this page size.
+CISR_EXPORT int cisr_attn_tcgen05_ok(int page_size) {
+    return page_size > 0 && page_size % 8 == 0 && (BN % page_size == 0 || page_size % BN == 0);
+}
+
+// Attention of portions: q, out [n_tokens, hq, D]; tiles of 128 queries given as (request, first query) pairs.
+CISR_EXPORT int cisr_attn_prefill_tcgen05(const void* q, void* out, int n_tokens, const void* k_cache, const void* v_cache,
+                                          int n_pages, const int* req_slot, const int* block_table, int table_width,
+                                          const int* tile_req, const int* tile_q0, int n_tiles, const int* q_start,
+                                          const int* q_len, const int* ctx_len, int hq, int hkv, int page_size, float scale,
+                                          int window, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (!g_encode || !g_error) return -13;
+    if (hq % hkv || !cisr_attn_tcgen05_ok(page_size)) return -2;
+    const long long cache_rows = (long long)n_pages * hkv * page_size;
+    if (cache_rows <= 0 || cache_rows >= (1ll << 31) || (((uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)q | (uintptr_t)out) & 15)) return -2;
+    const int box_rows = page_size < BN ? page_size : BN;
+    const CUtensorMap *map_q, *map_k, *map_v;
+    int status = cached_map(&map_q, q, n_tokens, hq * D, BM, 64);
+    if (status) return status;
+    if ((status = cached_map(&map_k, k_cache, cache_rows, D, box_rows, 64))) return status;
+    if ((status = cached_map(&map_v, v_cache, cache_rows, D, box_rows, 64))) return status;
+    const size_t smem = SMEM_FIXED + sizeof(int) * ((size_t)table_width + 4);     // a tile's key range spans at most the table
+    if (smem > 225 * 1024) return -3;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    return launch_kernel(attn_prefill_tcgen05_kernel, dim3(n_tiles, hq), dim3(THREADS), smem, (cudaStream_t)stream, g_pdl, *map_q,
+                         *map_k, *map_v, (bf16*)out, (int)cache_rows, req_slot, block_table, table_width, tile_req, tile_q0,
+                         q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, g_error);
+}

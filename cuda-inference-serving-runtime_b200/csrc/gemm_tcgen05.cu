@@ -19,57 +19,18 @@
 // frees its tensor memory and returns, and the host reports the failure.
 //
 // Parity: this is the product runtime/blas.py:41-56 of the reference hands to cuBLAS (C^T = W * X^T).
-#include "tma.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 typedef __nv_bfloat16 bf16;
 enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ROPE = 2 };
-constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr int BK = 64, UMMA_K = 16;     // BM = 128 (tcgen05.cuh)
 
 struct Epilogue {                       // what the epilogue variants need beyond the accumulator
     float* out_f32; bf16* out_bf16; int inter;
     const float* cos_t; const float* sin_t; bf16* q_out; bf16* k_cache; bf16* v_cache; const int* positions;
     const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size; int hq; int hkv; int dim;
 };
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16) in the 128-byte
-// swizzle: 8-row groups 1024 bytes apart (stride byte offset), leading byte offset unused, descriptor version 1.
-__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
-    uint64_t desc = 0;
-    desc |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);       // start address, 16-byte units
-    desc |= (uint64_t)1 << 16;                                  // leading byte offset (ignored for swizzled K-major)
-    desc |= (uint64_t)(1024 >> 4) << 32;                        // stride byte offset: 8 rows x 128 bytes
-    desc |= (uint64_t)1 << 46;                                  // descriptor version of this architecture
-    desc |= (uint64_t)2 << 61;                                  // 128-byte swizzle
-    return desc;
-}
-// Instruction descriptor of kind::f16: float accumulator, bfloat16 A and B, both K-major, M = 128, N = bn.
-__host__ __device__ constexpr uint32_t umma_idesc(int bn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// 32 consecutive accumulator columns of this thread's lane (its output row)
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
 // 32 floats -> 32 bfloat16 (64 bytes) at dst; `count` of them are valid
 __device__ __forceinline__ void store_bf16x32(bf16* dst, const float (&v)[32], int count) {
     if (count >= 32 && ((uintptr_t)dst & 15) == 0) {

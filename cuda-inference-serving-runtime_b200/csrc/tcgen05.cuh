@@ -1,0 +1,89 @@
+// tcgen05 (5th-generation tensor core) wrappers shared by the kernels that keep accumulators in tensor memory:
+// shared-memory and instruction descriptors for kind::f16 with M = 128, the MMA and commit instructions issued by one
+// thread, and tensor-memory loads and stores of a thread's own lane (its accumulator row).
+#pragma once
+#include "tma.cuh"
+
+namespace {
+constexpr int BM = 128;      // accumulator rows of every product here: one tensor-memory lane per row
+
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16) in the 128-byte
+// swizzle: 8-row groups 1024 bytes apart (stride byte offset), leading byte offset unused, descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);       // start address, 16-byte units
+    desc |= (uint64_t)1 << 16;                                  // leading byte offset (ignored for swizzled K-major)
+    desc |= (uint64_t)(1024 >> 4) << 32;                        // stride byte offset: 8 rows x 128 bytes
+    desc |= (uint64_t)1 << 46;                                  // descriptor version of this architecture
+    desc |= (uint64_t)2 << 61;                                  // 128-byte swizzle
+    return desc;
+}
+// Instruction descriptor of kind::f16: float accumulator, bfloat16 A and B, both K-major, M = 128, N = bn.
+__host__ __device__ constexpr uint32_t umma_idesc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 32 consecutive accumulator columns of this thread's lane (its output row)
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+
+// The same without the wait: several loads can be on their way before tmem_load_wait()
+__device__ __forceinline__ void tmem_load32_nowait(uint32_t taddr, uint32_t* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// The same 32 columns written back (a row scaled in place)
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                   "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                   "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory descriptor of an MN-major tile (the MN dimension contiguous: rows are K, 64 MN elements = 128 bytes
+// per row) in the 128-byte swizzle: 8-row groups along K 1024 bytes apart (stride byte offset); blocks of 64 MN
+// elements `mn_block_bytes` apart (leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_major(const void* tile, uint32_t mn_block_bytes) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
+    desc |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16;
+    desc |= (uint64_t)(1024 >> 4) << 32;
+    desc |= (uint64_t)1 << 46;
+    desc |= (uint64_t)2 << 61;
+    return desc;
+}
+constexpr uint32_t UMMA_B_MN_MAJOR = 1u << 16;      // instruction-descriptor bit: the B operand is MN-major
+}  // namespace

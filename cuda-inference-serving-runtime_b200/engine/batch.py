@@ -56,7 +56,8 @@ class StepContext:
         self.token_ids = self.positions = self.token_req = None
         self.req_slot = self.q_start = self.q_len = self.ctx_len = None
         self.tile_req = self.tile_q0 = self.dec_req = None
-        self.n_tiles = self.n_decode = 0
+        self.wide_req = self.wide_q0 = None      # the same portions cut into tiles of kernels.WIDE_TILE queries
+        self.n_tiles = self.n_wide = self.n_decode = 0
         self.logit_rows = None
         self.max_decode_ctx = 0
         self.fixed_splits: Optional[Tuple[int, int]] = None
@@ -135,6 +136,8 @@ def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarr
     tile = kernels.PREFILL_TILE
     tile_req: List[int] = []
     tile_q0: List[int] = []
+    wide_req: List[int] = []
+    wide_q0: List[int] = []
     dec_req: List[int] = []
     max_decode_ctx = 0
     for r, n in enumerate(host.q_len):
@@ -145,11 +148,15 @@ def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarr
             for q0 in reversed(range(0, n, tile)):     # a portion's last tile has the longest key loop: launch it first
                 tile_req.append(r)
                 tile_q0.append(q0)
+            for q0 in reversed(range(0, n, kernels.WIDE_TILE)):
+                wide_req.append(r)
+                wide_q0.append(q0)
     segments: List[Tuple[str, np.ndarray]] = [
         ("token_ids", token_ids), ("positions", positions), ("token_req", token_req),
         ("req_slot", np.asarray(host.slots, dtype=np.int32)), ("q_start", np.asarray(host.q_start, dtype=np.int32)),
         ("q_len", q_len), ("ctx_len", np.asarray(host.ctx_len, dtype=np.int32)),
         ("tile_req", np.asarray(tile_req, dtype=np.int32)), ("tile_q0", np.asarray(tile_q0, dtype=np.int32)),
+        ("wide_req", np.asarray(wide_req, dtype=np.int32)), ("wide_q0", np.asarray(wide_q0, dtype=np.int32)),
         ("dec_req", np.asarray(dec_req, dtype=np.int32)), ("logit_rows", np.asarray(host.logit_rows, dtype=np.int32)),
     ]
     for g, (idx, val) in enumerate(table_updates):
@@ -192,7 +199,8 @@ def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarr
     ctx.token_ids, ctx.positions, ctx.token_req = view("token_ids"), view("positions"), view("token_req")
     ctx.req_slot, ctx.q_start, ctx.q_len, ctx.ctx_len = view("req_slot"), view("q_start"), view("q_len"), view("ctx_len")
     ctx.tile_req, ctx.tile_q0, ctx.dec_req = view("tile_req"), view("tile_q0"), view("dec_req")
-    ctx.n_tiles, ctx.n_decode = len(tile_req), len(dec_req)
+    ctx.wide_req, ctx.wide_q0 = view("wide_req"), view("wide_q0")
+    ctx.n_tiles, ctx.n_wide, ctx.n_decode = len(tile_req), len(wide_req), len(dec_req)
     ctx.logit_rows = view("logit_rows")
     ctx.max_decode_ctx = max_decode_ctx if static is None else max(static.max_decode_ctx, max_decode_ctx)
     updates = [(view(f"upd_idx{g}"), view(f"upd_val{g}")) for g in range(len(table_updates))]

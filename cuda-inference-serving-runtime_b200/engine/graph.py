@@ -159,7 +159,7 @@ class DecodeGraph:
         ctx = StepContext(model.device, host)
         ctx.token_ids, ctx.positions, ctx.token_req = self.d("token_ids"), self.d("positions"), self.d("token_req")
         ctx.req_slot, ctx.q_start, ctx.q_len, ctx.ctx_len = self.d("req_slot"), self.d("q_start"), self.d("q_len"), self.d("ctx_len")
-        ctx.tile_req = ctx.tile_q0 = self.d("dec_req")[:0]
+        ctx.tile_req = ctx.tile_q0 = ctx.wide_req = ctx.wide_q0 = self.d("dec_req")[:0]
         ctx.dec_req, ctx.n_tiles, ctx.n_decode = self.d("dec_req"), 0, self.rows
         ctx.logit_rows = self.d("logit_rows")
         ctx.max_decode_ctx = self.ctx_bucket
@@ -208,7 +208,7 @@ class ShapeGraph:
         tokens = sum(q_lens)
         self.stepper = stepper
         capacity = tokens // max(1, cache.page_size) + 2 * len(q_lens) + 8
-        ints = 4 * tokens + 8 * len(q_lens) + 2 * (tokens // 64 + len(q_lens)) + n_rows * 8 + 2 * capacity * max(1, len(cache.page_groups)) + 256
+        ints = 4 * tokens + 8 * len(q_lens) + 4 * (tokens // 64 + len(q_lens) + 4) + n_rows * 8 + 2 * capacity * max(1, len(cache.page_groups)) + 256
         self.static = StaticMeta(stepper.model.device, ints, capacity, ctx_bucket)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None

@@ -244,6 +244,59 @@ def attention_jobs(head_dim: int, dtype: torch.dtype):
     return (source, defines, ())
 
 
+def attention_tcgen05_jobs(head_dim: int, dtype: torch.dtype):
+    """The build jobs of the tcgen05 prompt attention, where this head size and storage type have one."""
+    if dtype == torch.bfloat16 and head_dim in TCGEN05_HEAD_DIMS:
+        return [("attention_tcgen05.cu", {"HEAD_DIM": head_dim}, ())]
+    return []
+
+
+TCGEN05_HEAD_DIMS = (64, 128)
+WIDE_TILE = 128                  # queries per tile of the tcgen05 prompt attention
+_attention_tcgen05_libs = {}
+
+
+def _attention_tcgen05(head_dim: int):
+    lib = _attention_tcgen05_libs.get(head_dim)
+    if lib is None:
+        lib = load_library("attention_tcgen05.cu", {"HEAD_DIM": head_dim})
+        for name in ("cisr_attn_prefill_tcgen05", "cisr_attn_tcgen05_init", "cisr_attn_tcgen05_ok", "cisr_attn_tcgen05_tile"):
+            getattr(lib, name).restype = ctypes.c_int
+        assert lib.cisr_attn_tcgen05_tile() == WIDE_TILE
+        _check(lib.cisr_attn_tcgen05_init(_p(_error_flag())), "tcgen05 attention init", own=0)
+        lib.cisr_attn_tcgen05_set_pdl(int(_pdl_state["on"]))
+        _attention_tcgen05_libs[head_dim] = lib
+    return lib
+
+
+def attn_prefill_wide_ok(q: torch.Tensor, k_cache: torch.Tensor, page_size: int) -> bool:
+    """Whether the tcgen05 prompt attention takes these tensors: bfloat16, head size 64 or 128, a page size that is a
+    multiple of 8 and divides 128 or is a multiple of it, 16-byte aligned contiguous buffers."""
+    dim = k_cache.shape[-1]
+    return (k_cache.dtype == torch.bfloat16 and q.dtype == torch.bfloat16 and dim in TCGEN05_HEAD_DIMS
+            and page_size % 8 == 0 and (128 % page_size == 0 or page_size % 128 == 0)
+            and k_cache.is_contiguous() and q.is_contiguous() and q.data_ptr() % 16 == 0 and k_cache.data_ptr() % 16 == 0
+            and k_cache.shape[0] * k_cache.shape[1] * page_size < 2 ** 31)
+
+
+def attn_prefill_wide(q, out, k_cache, v_cache, req_slot, block_table, wide_req, wide_q0, q_start, q_len, ctx_len, hq, hkv,
+                      page_size, scale, window) -> None:
+    """Attention of portions on tcgen05: q, out [tokens, hq, D]; tiles of 128 queries as (request, first query)."""
+    dim = k_cache.shape[-1]
+    _need(q, torch.bfloat16, "q", 3); _need(out, torch.bfloat16, "out", 3); _need(k_cache, torch.bfloat16, "k_cache", 4)
+    _need(v_cache, torch.bfloat16, "v_cache", 4)
+    for name, t in (("req_slot", req_slot), ("block_table", block_table), ("wide_req", wide_req), ("wide_q0", wide_q0),
+                    ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len)):
+        _need(t, torch.int32, name)
+    if not attn_prefill_wide_ok(q, k_cache, page_size):
+        raise KernelError("attn_prefill_wide: not a head size, page size or buffer for the tcgen05 attention")
+    lib = _attention_tcgen05(dim)
+    _check(lib.cisr_attn_prefill_tcgen05(_p(q), _p(out), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(req_slot),
+                                         _p(block_table), block_table.shape[1], _p(wide_req), _p(wide_q0), wide_req.numel(),
+                                         _p(q_start), _p(q_len), _p(ctx_len), hq, hkv, page_size, ctypes.c_float(scale),
+                                         int(window or 0), _stream()), "attn_prefill_wide")
+
+
 PREFILL_TILE = 64
 
 
@@ -409,6 +462,8 @@ def set_pdl(on: bool) -> None:
     _skinny().cisr_skinny_set_pdl(int(on))
     if "lib" in _stream_state:
         _stream_state["lib"].cisr_stream_set_pdl(int(on))
+    for lib in _attention_tcgen05_libs.values():
+        lib.cisr_attn_tcgen05_set_pdl(int(on))
     _elementwise().cisr_elementwise_set_pdl(int(on))
     if "lib" in _tcgen05_state:
         _tcgen05_state["lib"].cisr_gemm_tcgen05_set_pdl(int(on))
@@ -607,7 +662,8 @@ def gemm_tcgen05_rope(a: torch.Tensor, w: torch.Tensor, rope: dict) -> None:
 
 _GAVE_UP = {1: "a tcgen05 matrix product gave up waiting on a barrier",
             3: "an attention kernel gave up waiting on a tensor-map copy",
-            4: "a weight-streaming product gave up waiting on a tensor-map copy"}
+            4: "a weight-streaming product gave up waiting on a tensor-map copy",
+            5: "the tcgen05 attention gave up waiting on a barrier"}
 
 
 def error_flag_tensor() -> Optional[torch.Tensor]:

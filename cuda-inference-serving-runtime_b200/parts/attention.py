@@ -53,7 +53,7 @@ class GQAAttention(Mixer):
 
     def kernel_jobs(self):
         return ([("elementwise.cu", {}, ()), kernels.attention_jobs(self.dim, self.dtype)]
-                + kernels.gemm_jobs(self.dtype) + self.position.kernel_jobs()
+                + kernels.attention_tcgen05_jobs(self.dim, self.dtype) + kernels.gemm_jobs(self.dtype) + self.position.kernel_jobs()
                 + (kernels.skinny_jobs() if self.dtype == torch.bfloat16 else []))
 
     def cache_use(self) -> CacheUse:
@@ -98,7 +98,10 @@ class GQAAttention(Mixer):
                                cache.k if cache.write else None, cache.v if cache.write else None,
                                ctx.token_req, ctx.positions, ctx.req_slot, cache.block_table, cache.page_size, hq, hkv, dim)
         out = torch.empty((tokens, hq, dim), dtype=self.dtype, device=device)
-        if ctx.n_tiles:
+        if ctx.n_tiles and kernels.attn_prefill_wide_ok(q, cache.k, cache.page_size):
+            kernels.attn_prefill_wide(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, ctx.wide_req, ctx.wide_q0,
+                                      ctx.q_start, ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, self.scale, self.window)
+        elif ctx.n_tiles:
             kernels.attn_prefill(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, ctx.tile_req, ctx.tile_q0, ctx.q_start,
                                  ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, self.scale, self.window)
         if ctx.n_decode:

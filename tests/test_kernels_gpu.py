@@ -116,7 +116,7 @@ def paged(k_dense, v_dense, page_size, n_pages, seed, dtype):
 
 
 def run_attention(q_all, k_all, v_all, q_lens, page_size, dtype, window=None, split_size=None, seed=0, width=64, kind="auto",
-                  staging="auto", fill=0.0):
+                  staging="auto", fill=0.0, wide=False):
     """Requests given as whole sequences; the last q_lens[r] positions of each are this step's queries.
     Cache rows that no request has written hold `fill`."""
     k = kernels()
@@ -153,7 +153,15 @@ def run_attention(q_all, k_all, v_all, q_lens, page_size, dtype, window=None, sp
     args = dict(hq=hq, hkv=hkv, page_size=page_size, scale=d ** -0.5, window=window, kind=kind)
     kcd, vcd, qd = kc.to(dev()), vc.to(dev()), q.to(dev()).contiguous()
     req_slot = i32(np.arange(1, R + 1)); tab = i32(table)
-    if tile_req:
+    if tile_req and wide:       # the tcgen05 kernel: tiles of 128 queries
+        wide_req, wide_q0 = [], []
+        for r, n in enumerate(q_lens):
+            if n > 1:
+                for q0 in reversed(range(0, n, k.WIDE_TILE)):
+                    wide_req.append(r); wide_q0.append(q0)
+        k.attn_prefill_wide(qd, out, kcd, vcd, req_slot, tab, i32(wide_req), i32(wide_q0), i32(q_start), i32(q_lens), i32(ctx),
+                            hq, hkv, page_size, d ** -0.5, window)
+    elif tile_req:
         k.attn_prefill(qd, out, kcd, vcd, req_slot, tab, i32(tile_req), i32(tile_q0), i32(q_start), i32(q_lens), i32(ctx), **args)
     if dec_req:
         max_ctx = int(max(ctx[r] for r in dec_req))
@@ -212,6 +220,35 @@ def test_decode_attention_by_tensor_map_copies_and_by_gather(d, hq, hkv, page_si
             close(out, ref, *ATT_TOL[torch.bfloat16], f"decode attention, {staging}, window {window}, ranges of {split_size}")
     finally:
         k.set_clusters(False)
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(64, 9, 3), (128, 4, 2), (64, 2, 2)])
+@pytest.mark.parametrize("page_size", [8, 16, 128, 256])
+@pytest.mark.parametrize("window", [None, 100])
+def test_prompt_attention_on_tcgen05(d, hq, hkv, page_size, window):
+    """Whole prompts and portions with earlier context in one launch: lengths at and around the 128-query and 128-key
+    tile edges, one longer than three tiles; cache rows that nobody wrote hold NaN (a value row beyond the last key
+    must not reach the output through a zero weight).  Single tokens in the same step go to the decode kernel."""
+    lens, q_lens = [200, 77, 130, 128, 301, 129, 515, 1], [200, 13, 2, 128, 44, 129, 515, 1]
+    data = [random_qkv(t, hq, hkv, d, 11 * d + i, sharp=2.0) for i, t in enumerate(lens)]
+    out, ref = run_attention([x[0] for x in data], [x[1] for x in data], [x[2] for x in data], q_lens, page_size, torch.bfloat16,
+                             window=window, seed=d + page_size, width=128, fill=float("nan"), wide=True)
+    assert torch.isfinite(out).all()
+    close(out, ref, *ATT_TOL[torch.bfloat16], f"tcgen05 prompt attention, pages of {page_size}, window {window}")
+
+
+@pytest.mark.parametrize("needle", [0, 127, 128, 255, 256, 600])
+def test_prompt_attention_on_tcgen05_finds_one_far_key(needle):
+    """One key is made to stand out for the last query of a 700-token prompt: the output must be that key's value."""
+    t, hq, hkv, d = 700, 6, 2, 64
+    q, k_, v = random_qkv(t, hq, hkv, d, needle)
+    q[-1] = q[-1] / q[-1].norm(dim=-1, keepdim=True) * 6
+    for h in range(hkv):
+        k_[needle, h] = q[-1, h * 3] * 4
+    v[needle] = 100.0
+    out, ref = run_attention([q], [k_], [v], [t], 16, torch.bfloat16, seed=needle, wide=True)
+    close(out, ref, 0.5, 2e-2, f"needle at {needle}")
+    assert out[-1, 0, 0].item() > 99.0 and out[-1, 3, 0].item() > 99.0
 
 
 def test_tensor_map_staging_refuses_what_it_cannot_take():
