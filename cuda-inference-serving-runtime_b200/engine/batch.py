@@ -76,7 +76,7 @@ class StepContext:
 
 def plan_decode_splits(n_decode: int, kv_heads: int, max_ctx: int) -> Tuple[int, int]:
     ctas = max(1, n_decode * kv_heads)
-    wanted = max(1, -(-CTA_TARGET // ctas))
+    wanted = max(1, CTA_TARGET // ctas)          # rounded down: one wave of CTAs, not a wave and a bit
     size = -(-max(1, max_ctx) // wanted)
     size = max(SPLIT_MIN, -(-size // SPLIT_QUANTUM) * SPLIT_QUANTUM)
     n_splits = max(1, -(-max_ctx // size))

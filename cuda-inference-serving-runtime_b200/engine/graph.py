@@ -56,6 +56,16 @@ def bucket_of(n: int, minimum: int = 1) -> int:
     return b
 
 
+def context_bucket_of(n: int) -> int:
+    """The context bound a decode graph is captured for: powers of two up to 1024, then quarter steps between them
+    (1280, 1536, 1792, 2048, 2560, ...), so that at most a fifth of a step's key ranges lie beyond the context."""
+    b = bucket_of(n, MIN_CONTEXT_BUCKET)
+    if b <= 1024:
+        return b
+    quarter = b // 8                      # b / 2 < n <= b: steps of a quarter of b / 2
+    return b // 2 + -(-(n - b // 2) // quarter) * quarter
+
+
 def _align(n: int) -> int:
     return (n + 3) & ~3
 
@@ -256,7 +266,7 @@ class DecodeGraphs:
         self.hits = self.misses = self.evictions = 0
 
     def get(self, n_rows: int, max_ctx: int) -> Tuple[DecodeGraph, bool]:
-        key = (bucket_of(n_rows), bucket_of(max_ctx, MIN_CONTEXT_BUCKET))
+        key = (bucket_of(n_rows), context_bucket_of(max_ctx))
         graph = self.graphs.get(key)
         if graph is not None:
             self.graphs.move_to_end(key)
@@ -272,7 +282,7 @@ class DecodeGraphs:
 
     def shape(self, q_lens: Tuple[int, ...], n_rows: int, max_decode_ctx: int) -> Optional[ShapeGraph]:
         """The graph of a step shape, from the second time the shape is seen (a shape seen once is not worth a capture)."""
-        key = (q_lens, n_rows, bucket_of(max_decode_ctx, MIN_CONTEXT_BUCKET) if max_decode_ctx else 0)
+        key = (q_lens, n_rows, context_bucket_of(max_decode_ctx) if max_decode_ctx else 0)
         graph = self.shapes.get(key)
         if graph is not None:
             self.shapes.move_to_end(key)
