@@ -587,7 +587,7 @@ def _stream_lib():
 
 # ------------------------------------------------------------------ tcgen05 + TMA matrix product
 _tcgen05_state = {}
-TCGEN05_MIN_TOKENS = 128         # below one 128-row tile the weight-streaming kernels or the library serve better
+TCGEN05_MIN_TOKENS = int(os.environ.get("CISR_TCGEN05_MIN_TOKENS", "128"))   # below one 128-row tile the weight-streaming kernels or the library serve better
 
 
 def _tcgen05():

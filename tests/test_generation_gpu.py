@@ -125,3 +125,40 @@ def test_command_line_prints_the_reference_fields(tiny, tmp_path):
                             capture_output=True, text=True, cwd=str(replay.ROOT), timeout=600)
     assert single.returncode == 0, single.stderr[-3000:]
     assert len(json.loads(single.stdout)["requests"][0]["generated"]) == 3
+
+
+def test_kernel_timeline_records_every_launch_of_a_step(tiny):
+    """A development build of the kernels (CISR_TRACE=1 in the environment of a fresh process) records when each CTA
+    entered and left; a step of the tiny model leaves records of known kernels in launch order, and the Trace Event
+    file is valid JSON."""
+    cfg, weights, path = tiny["a"]
+    script = f"""
+import json, os, sys, tempfile
+sys.path.insert(0, {str(replay.ROOT)!r})
+from cisr_b200 import Model, StepEntry, Stepper
+from cisr_b200.ops import trace
+import torch
+model = Model.from_pretrained({str(path)!r}, dtype="float32")
+stepper = Stepper(model, n_pages=8, page_size=16, max_slots=2)
+stepper.create("a")
+stepper.step([StepEntry("a", [1, 2, 3, 4, 5], [4])])
+torch.cuda.synchronize()
+records = trace.read()
+names = [trace.KERNEL_NAMES[int(k)] for k in records["kernel"]]
+assert records.size > 0 and (records["left"] >= records["entered"]).all()
+assert names[0] in ("table_update", "embedding", "rotary_table"), names[:3]
+assert "attention (CUDA cores)" in names and "add_rmsnorm" in names
+launches = trace.summary(records)
+assert [l["begin"] for l in launches] == sorted(l["begin"] for l in launches)
+out = os.path.join(tempfile.mkdtemp(), "step.json")
+trace.write_chrome_trace(records, out)
+events = json.load(open(out))["traceEvents"]
+assert len(events) >= records.size
+assert trace.read().size == 0          # reading empties the buffers
+print("timeline ok", records.size, len(launches))
+"""
+    import os
+    env = dict(os.environ, CISR_TRACE="1")
+    done = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env, timeout=240)
+    assert done.returncode == 0, done.stdout + done.stderr
+    assert "timeline ok" in done.stdout
