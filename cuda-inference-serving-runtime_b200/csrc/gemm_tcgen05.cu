@@ -314,12 +314,18 @@ bool wide_tiles(int m, int tiles_n256) { return (long long)((m + BM - 1) / BM) *
 
 // Fewer 128 x 128 tiles than SMs: every CTA runs one tile, alone on its SM, and the time is the ring's round trips to
 // L2 (a stage is asked for again only after its product), not the tensor pipe.  A deeper ring with the whole SM's
-// shared memory hides them.  CISR_GEMM_DEEP=0 turns it off.
-bool few_tiles(int m, int tiles_n128) {
+// shared memory hides them, and while 128 x 64 tiles still fit the device at one per SM, twice as many CTAs share
+// the weights.  Returns 64 or 128 for the tile width of the deep ring, 0 for the ordinary choice (also with
+// CISR_GEMM_DEEP=0).  `cols`: output columns a 128-wide tile covers (64 features for the gated product).
+int few_tiles(int m, int n, int cols) {
     static int sms = 0, on = -1;
     if (!sms) { int device = 0; cudaGetDevice(&device); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device); }
     if (on < 0) { const char* e = getenv("CISR_GEMM_DEEP"); on = !(e && e[0] == '0'); }
-    return on && (long long)((m + BM - 1) / BM) * tiles_n128 <= sms;
+    if (!on) return 0;
+    const long long tiles_m = (m + BM - 1) / BM;
+    if (tiles_m * ((n + cols / 2 - 1) / (cols / 2)) <= sms) return 64;
+    if (tiles_m * ((n + cols - 1) / cols) <= sms) return 128;
+    return 0;
 }
 
 bool operands_ok(const void* a, const void* w, int k) {
@@ -345,9 +351,11 @@ CISR_EXPORT int cisr_gemm_tcgen05(const void* a, const void* w, float* out, int 
     Epilogue ep = {};
     ep.out_f32 = out;
     cudaStream_t s = (cudaStream_t)stream;
-    if (n <= 64) return launch<64, 4, EPI_PLAIN>(a, w, ep, m, n, k, (n + 63) / 64, s);
+    if (n <= 64) return launch<64, 8, EPI_PLAIN>(a, w, ep, m, n, k, (n + 63) / 64, s);
     if (wide_tiles(m, (n + 255) / 256)) return launch<256, 4, EPI_PLAIN>(a, w, ep, m, n, k, (n + 255) / 256, s);
-    if (few_tiles(m, (n + 127) / 128)) return launch<128, 6, EPI_PLAIN>(a, w, ep, m, n, k, (n + 127) / 128, s);
+    const int deep = few_tiles(m, n, 128);
+    if (deep == 64) return launch<64, 8, EPI_PLAIN>(a, w, ep, m, n, k, (n + 63) / 64, s);
+    if (deep == 128) return launch<128, 6, EPI_PLAIN>(a, w, ep, m, n, k, (n + 127) / 128, s);
     return launch<128, 3, EPI_PLAIN>(a, w, ep, m, n, k, (n + 127) / 128, s);
 }
 
@@ -360,8 +368,9 @@ CISR_EXPORT int cisr_gemm_tcgen05_swiglu(const void* a, const void* w, void* out
     ep.out_bf16 = (bf16*)out; ep.inter = inter;
     if (wide_tiles(m, (inter + 127) / 128))
         return launch<256, 4, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 127) / 128, (cudaStream_t)stream);
-    if (few_tiles(m, (inter + 63) / 64))
-        return launch<128, 6, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 63) / 64, (cudaStream_t)stream);
+    const int deep = few_tiles(m, inter, 64);
+    if (deep == 64) return launch<64, 8, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 31) / 32, (cudaStream_t)stream);
+    if (deep == 128) return launch<128, 6, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 63) / 64, (cudaStream_t)stream);
     return launch<128, 3, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 63) / 64, (cudaStream_t)stream);
 }
 
@@ -381,6 +390,8 @@ CISR_EXPORT int cisr_gemm_tcgen05_rope(const void* a, const void* w, int m, int 
     ep.table_width = table_width; ep.page_size = page_size; ep.hq = hq; ep.hkv = hkv; ep.dim = dim;
     const int n = (hq + 2 * hkv) * dim;
     if (wide_tiles(m, (n + 255) / 256)) return launch<256, 4, EPI_ROPE>(a, w, ep, m, n, k, (n + 255) / 256, (cudaStream_t)stream);
-    if (few_tiles(m, (n + 127) / 128)) return launch<128, 6, EPI_ROPE>(a, w, ep, m, n, k, (n + 127) / 128, (cudaStream_t)stream);
+    const int deep = few_tiles(m, n, 128);
+    if (deep == 64 && dim == 64) return launch<64, 8, EPI_ROPE>(a, w, ep, m, n, k, (n + 63) / 64, (cudaStream_t)stream);   // a whole head per tile
+    if (deep) return launch<128, 6, EPI_ROPE>(a, w, ep, m, n, k, (n + 127) / 128, (cudaStream_t)stream);
     return launch<128, 3, EPI_ROPE>(a, w, ep, m, n, k, (n + 127) / 128, (cudaStream_t)stream);
 }
