@@ -108,8 +108,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (tid == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(s_full + s, 1); mbar_init(s_empty + s, SOFTMAX_THREADS); }
-        mbar_init(p_full, SOFTMAX_THREADS);
+        for (int s = 0; s < 2; ++s) { mbar_init(s_full + s, 1); mbar_init(s_empty + s, SOFTMAX_THREADS / 32); }
+        mbar_init(p_full, SOFTMAX_THREADS / 32);       // one arrival per softmax warp, by its first lane after the warp has met
         mbar_init(pv_done, 1);
         *abort_flag = 0;
         mbar_init_fence();
@@ -239,7 +239,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 request(j, raw);
                 tmem_load_wait();              // this tile's half row of scores is in registers: the buffer can take tile j + 2
                 tcgen05_fence_before();
-                mbar_arrive(s_empty + s);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_empty + s);
                 if (edge) {
 #pragma unroll
                     for (int c = 0; c < HALF; ++c)
@@ -313,7 +314,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and the zeroed rows) before the tensor core reads them
-            mbar_arrive(p_full);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
         };
         for (int j = 0; j < n_tiles; ++j) step(j);
         if (ok) ok = wait(pv_done, (n_tiles - 1) & 1);

@@ -465,6 +465,7 @@ def set_pdl(on: bool) -> None:
     for lib in _attention_tcgen05_libs.values():
         lib.cisr_attn_tcgen05_set_pdl(int(on))
     _elementwise().cisr_elementwise_set_pdl(int(on))
+    _sampling().cisr_sampling_set_pdl(int(on))
     if "lib" in _tcgen05_state:
         _tcgen05_state["lib"].cisr_gemm_tcgen05_set_pdl(int(on))
     for (source, _, _), lib in list(_attention_libs.items()):
