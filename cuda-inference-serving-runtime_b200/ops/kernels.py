@@ -609,8 +609,14 @@ def tcgen05_jobs():
     return [("gemm_tcgen05.cu", {}, ())]
 
 
-def tcgen05_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
-    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] >= TCGEN05_MIN_TOKENS
+# The product with rotation and cache write as its epilogue replaces two launches (the library's product and the rotate
+# kernel), which pays from far fewer tokens on than the plain product does against the library's.
+TCGEN05_FUSED_MIN_TOKENS = int(os.environ.get("CISR_TCGEN05_FUSED_MIN_TOKENS", "17"))
+
+
+def tcgen05_ok(a: torch.Tensor, w: torch.Tensor, fused: bool = False) -> bool:
+    least = min(TCGEN05_MIN_TOKENS, TCGEN05_FUSED_MIN_TOKENS) if fused else TCGEN05_MIN_TOKENS
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] >= least
             and a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 

@@ -79,7 +79,7 @@ class GQAAttention(Mixer):
             else:
                 kernels.skinny_gemm(self.qkv, tokens, act=as_tensor(h), epilogue=kernels.EPI_ROPE, rope=rope)
         elif (cache.write and rot is not None and kernels.tcgen05_rope_ok(dim, rot.rot_half, rot.interleaved)
-              and kernels.tcgen05_ok(as_tensor(h) if isinstance(h, torch.Tensor) else h.materialize_once(), self.qkv)):
+              and kernels.tcgen05_ok(as_tensor(h) if isinstance(h, torch.Tensor) else h.materialize_once(), self.qkv, fused=True)):
             # many tokens: rotation and cache write are the epilogue of the tcgen05 product
             kernels.gemm_tcgen05_rope(h if isinstance(h, torch.Tensor) else h.materialize_once(), self.qkv, dict(
                 cos=rot.cos, sin=rot.sin, q_out=q, k_cache=cache.k, v_cache=cache.v, positions=ctx.positions,
