@@ -41,9 +41,13 @@ constexpr int SUB_BYTES = 128 * 128;          // one 128-row x 64-column sub-til
 constexpr int KV_SUB = BN * 128;              // one BN-key x 64-column sub-tile (keys, values)
 constexpr int Q_BYTES = NSUB * SUB_BYTES;
 constexpr int KV_BYTES = NSUB * KV_SUB;       // a K tile, or a V tile
-constexpr int P_BYTES = (BN / 64) * SUB_BYTES;   // 128 rows x BN keys in 64-key sub-tiles
-constexpr int STAGES = 4;                     // key/value tiles on their way: a copy takes several tiles' worth of time to land
-constexpr size_t SMEM_FIXED = 1024 + Q_BYTES + STAGES * 2 * KV_BYTES + P_BYTES + 256 + 4 * 128 * sizeof(float);
+constexpr int P_COL0 = 384;                   // tensor memory: scores [0, 2 BN), output [256, 256 + D), probabilities from here
+constexpr int P_COLS = BN / 2;                // a tile's probabilities: bfloat16 pairs, two buffers
+#ifndef ATTN_STAGES
+#define ATTN_STAGES 4
+#endif
+constexpr int STAGES = ATTN_STAGES;           // key/value tiles on their way: a copy takes several tiles' worth of time to land
+constexpr size_t SMEM_FIXED = 1024 + Q_BYTES + STAGES * 2 * KV_BYTES + 256 + 4 * 128 * sizeof(float);
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.f;           // the max may lag by this much (base-2 exponent) before O is rescaled
 constexpr int SOFTMAX_THREADS = 256;          // two groups of four warps: each thread has half of a query row's columns
@@ -74,8 +78,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* Qs = base;                                   // [NSUB][128 queries][128 B]
     unsigned char* KVs = Qs + Q_BYTES;                          // [STAGES][K tile | V tile], each [NSUB][BN keys][128 B]
-    unsigned char* Ps = KVs + STAGES * 2 * KV_BYTES;            // [BN / 64][128 queries][128 B]: 64 keys per sub-tile
-    uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + P_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(KVs + STAGES * 2 * KV_BYTES);
     uint64_t* q_full = bars;                                    // the query tile has landed
     uint64_t* kv_full = bars + 1;                               // [STAGES] a stage's keys and values have landed
     uint64_t* kv_empty = kv_full + STAGES;                      // [STAGES] the products that read the stage are done
@@ -83,10 +86,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint64_t* s_empty = s_full + 2;                             // [2] the softmax threads have read it
     uint64_t* p_full = s_empty + 2;                             // P is in shared memory (and O rescaled)
     uint64_t* pv_done = p_full + 1;                             // the output product of a tile is done
-    static_assert(1 + 2 * STAGES + 6 <= 15, "the barriers and the two words behind them fit 128 bytes");
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    static_assert(1 + 2 * STAGES + 6 <= 23, "the barriers and the two words behind them fit 192 bytes");
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
-    float* exchange = reinterpret_cast<float*>(bars + 16);      // [2 sets][2 groups][128 rows]: the groups' maxima of a tile, then their sums
+    float* exchange = reinterpret_cast<float*>(bars + 24);      // [2 sets][2 groups][128 rows]: the groups' maxima of a tile, then their sums
     int* pages = reinterpret_cast<int*>(exchange + 4 * BM);     // block table entries of this tile's key range
 
     pdl_trigger();
@@ -131,6 +134,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         *(volatile int*)abort_flag = 1;
     };
     auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {     // false: leave (this or another role gave up)
+        if (mbar_test(bar, parity)) return true;                  // the usual case: the phase is over already
         if (*(volatile int*)abort_flag) return false;
         if (mbar_wait(bar, parity)) return true;
         gave_up();
@@ -167,11 +171,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             constexpr uint32_t idesc_o = umma_idesc(D) | UMMA_B_MN_MAJOR;
             auto output_product = [&](int j) {                    // O += P(j) V(j)
                 const unsigned char* Vs = KVs + (j % STAGES) * 2 * KV_BYTES + KV_BYTES;
+                const uint32_t tmem_p = tmem_base + (uint32_t)(P_COL0 + (j & 1) * P_COLS);
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {            // 16 keys per step: P along its K (32 bytes), V two 8-row groups down
-                    const uint64_t desc_p = umma_desc(Ps + (ks >> 2) * SUB_BYTES) + 2 * (ks & 3);
+                for (int ks = 0; ks < BN / 16; ++ks) {            // 16 keys per step: 8 columns of P, V two 8-row groups down
                     const uint64_t desc_v = umma_desc_mn_major(Vs + ks * 16 * 128, KV_SUB);
-                    umma_bf16(tmem_o, desc_p, desc_v, idesc_o, (j | ks) != 0);
+                    umma_bf16_ts(tmem_o, tmem_p + 8 * ks, desc_v, idesc_o, (j | ks) != 0);
                 }
                 umma_commit(pv_done);
                 umma_commit(kv_empty + j % STAGES);
@@ -233,27 +237,53 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // tiles on the diagonal, at the window's start and at the end of the keys need the per-element mask
             const bool edge = kt + BN - 1 > qpos0 || kt + BN > k_end || (window > 0 && kt <= qpos0 + BM - 1 - window);
             auto masked = [&](int kpos) { return kpos > qpos || kpos >= k_end || (window > 0 && kpos <= qpos - window); };
-            float m_tile = -INFINITY;
-            if (ok) {
-                tcgen05_fence_after();
+            // One pass when the row already has a max in use: the exponentials are taken against it while the tile's own
+            // max is found, and only a tile whose max turns out more than RESCALE_STEP above it is done again (from the
+            // scores, which stay in tensor memory until this tile's P is handed over).  A warp with a row that has no
+            // max yet (the first tile, or only masked keys so far) finds the max first.
+            auto fetch = [&]() {
                 request(j, raw);
-                tmem_load_wait();              // this tile's half row of scores is in registers: the buffer can take tile j + 2
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(s_empty + s);
+                tmem_load_wait();
                 if (edge) {
 #pragma unroll
                     for (int c = 0; c < HALF; ++c)
                         if (masked(k0 + c)) raw[c] = __float_as_uint(-INFINITY);
                 }
-                // this half's max (the scale is positive: the max of the raw scores, scaled)
-                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            };
+            uint32_t* packed = raw;                               // pair c / 2 takes the place of scores already used
+            // P = 2^(s - m), rounded to bfloat16 for the product; the sum keeps the unrounded values; also the max of the scores
+            auto exponentials = [&](float m_ref, float& mx_out) -> float {
+                float sums[4] = {0.f, 0.f, 0.f, 0.f}, mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-                for (int c = 0; c < HALF; c += 4) {
-                    mx[0] = fmaxf(mx[0], __uint_as_float(raw[c])); mx[1] = fmaxf(mx[1], __uint_as_float(raw[c + 1]));
-                    mx[2] = fmaxf(mx[2], __uint_as_float(raw[c + 2])); mx[3] = fmaxf(mx[3], __uint_as_float(raw[c + 3]));
+                for (int c = 0; c < HALF; c += 2) {
+                    const float a = __uint_as_float(raw[c]), b = __uint_as_float(raw[c + 1]);
+                    mx[0] = fmaxf(mx[0], a); mx[1] = fmaxf(mx[1], b);
+                    const float p0 = fast_exp2(fmaf(a, scale2, -m_ref));       // -inf (masked) gives 0
+                    const float p1 = fast_exp2(fmaf(b, scale2, -m_ref));
+                    sums[(c >> 1) & 3] += p0 + p1;
+                    __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                    packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
                 }
-                m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;
+                mx_out = fmaxf(mx[0], mx[1]);
+                return (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            };
+            float m_tile = -INFINITY, sum = 0.f;
+            bool ahead = false;                                   // the exponentials were taken before the max was known
+            if (ok) {
+                tcgen05_fence_after();
+                fetch();                       // this tile's half row of scores is in registers
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_empty + s);
+                ahead = __all_sync(0xffffffffu, m_used != -INFINITY);
+                float mx = -INFINITY;
+                if (ahead) {
+                    sum = exponentials(m_used, mx);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < HALF; ++c) mx = fmaxf(mx, __uint_as_float(raw[c]));
+                }
+                m_tile = mx * scale2;          // the scale is positive: the max of the raw scores, scaled
             }
             // the two threads of a row exchange their maxima (a read of the partner's half from tensor memory instead
             // costs a second load round trip, which was slower); every warp reaches this barrier in every iteration
@@ -264,28 +294,28 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!ok) return;
             // the max in use moves only when it lags by more than RESCALE_STEP; the first finite max is taken as it is
             float alpha = 1.f;
-            if (m_tile > m_used + RESCALE_STEP || (m_used == -INFINITY && m_tile > -INFINITY)) {
+            const bool moved = m_tile > m_used + RESCALE_STEP || (m_used == -INFINITY && m_tile > -INFINITY);
+            if (moved) {
                 alpha = m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_tile);
                 m_used = m_tile;
             }
             const float m_ref = m_used == -INFINITY ? 0.f : m_used;
-            // P = 2^(s - m), rounded to bfloat16 for the product; the sum keeps the unrounded values
-            float sums[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t* packed = raw;                               // pair c / 2 takes the place of scores already used
-#pragma unroll
-            for (int c = 0; c < HALF; c += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(raw[c]), scale2, -m_ref));       // -inf (masked) gives 0
-                const float p1 = fast_exp2(fmaf(__uint_as_float(raw[c + 1]), scale2, -m_ref));
-                sums[(c >> 1) & 3] += p0 + p1;
-                __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-                packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+            if (!ahead) {
+                float unused;
+                sum = exponentials(m_ref, unused);
+            } else if (__any_sync(0xffffffffu, moved)) {          // tensor-memory access is warp-wide: every lane does its row again
+                tcgen05_fence_after();
+                fetch();
+                float unused;
+                sum = exponentials(m_ref, unused);
             }
-            const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
-            // P's buffer and O are free once the output product of the tile before is done
-            if (j > 0) ok = __all_sync(0xffffffffu, wait(pv_done, (j - 1) & 1));
+            const bool rescale = __any_sync(0xffffffffu, alpha != 1.f);
+            // O is free once the output product of the tile before is done.  P's buffer (one of two) was read by the
+            // product of two tiles back, which the issuing thread sent before this tile's scores: their arrival covers it.
+            if (j > 0 && rescale) ok = __all_sync(0xffffffffu, wait(pv_done, (j - 1) & 1));
             if (!ok) return;
             tcgen05_fence_after();
-            if (group == 0 && j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {   // tensor-memory access is warp-wide: all lanes go, most with alpha 1
+            if (group == 0 && j > 0 && rescale) {                 // all lanes go, most with alpha 1
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t acc[32];
@@ -296,12 +326,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
             l = l * alpha + sum;
+            // the thread's half row of P into tensor memory, where the output product reads it as its A operand
+            const uint32_t p_addr = tmem_base + lane_base + (uint32_t)(P_COL0 + (j & 1) * P_COLS + group * (HALF / 2));
 #pragma unroll
-            for (int q = 0; q < HALF / 8; ++q) {                  // 16-byte chunks of the row, in 64-key sub-tiles, swizzled
-                const int chunk = group * (HALF / 8) + q;
-                *reinterpret_cast<uint4*>(Ps + (chunk >> 3) * SUB_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4)) =
-                    make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-            }
+            for (int c0 = 0; c0 < HALF / 2; c0 += 16) tmem_store16_nowait(p_addr + c0, packed + c0);
+            tmem_store_wait();
             tcgen05_fence_before();
             if (k_begin + j * BN + BN > k_end) {
                 // Value rows beyond the last key were never written, or are left over from another request: they must
@@ -312,8 +341,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (k_begin + j * BN + r >= k_end)
                         *reinterpret_cast<uint4*>(Vs + (c >> 3) * KV_SUB + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroed rows before the tensor core reads them
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and the zeroed rows) before the tensor core reads them
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         };
