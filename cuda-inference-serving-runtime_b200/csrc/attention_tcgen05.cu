@@ -6,13 +6,17 @@
 //               tensor-map copies (cp.async.bulk.tensor.2d, 128-byte swizzle), one box per page and 64 columns
 //   warp 1      one thread issues the products: S = Q K^T (tcgen05.mma kind::f16, M = 128, N = 128, K = 16 steps,
 //               Q and K both K-major) into one of two score buffers in tensor memory, and O += P V (N = head size,
-//               V as the MN-major B operand straight from its [key][dim] tile); the score product of tile j + 1 is
-//               issued before the output product of tile j, so it runs while the softmax warps work on tile j
-//   warps 2..5  softmax: thread r owns query row r (tensor-memory lane r): it reads its row of S with tcgen05.ld,
-//               keeps the running max and sum in float, writes P = 2^(s - m) as bfloat16 into shared memory in the
-//               layout the tensor core reads (K-major, swizzled), and rescales its row of O in tensor memory only
-//               when the max has grown by more than 8 (a stale max is exact arithmetic as long as 2^(s - m) stays
-//               small; the final division by the sum uses the same max)
+//               P read from tensor memory as the A operand, V as the MN-major B operand straight from its
+//               [key][dim] tile); the score product of tile j + 1 is issued before the output product of tile j, so it
+//               runs while the softmax warps work on tile j
+//   warps 2..9  softmax, two groups of four warps: thread (group, r) owns half of the columns of query row r
+//               (tensor-memory lane r).  It reads them with tcgen05.ld and keeps the running max and sum in float.
+//               Once the row has a max in use, the exponentials of a tile are taken against it in the same pass that
+//               finds the tile's own max; only when that turns out more than 8 above the max in use (a stale max is
+//               exact arithmetic as long as 2^(s - m) stays small; the final division by the sum uses the same max)
+//               is the row of O rescaled and the tile done again from the scores, which stay in tensor memory until
+//               P is handed over.  P = 2^(s - m) goes back to tensor memory as bfloat16 pairs (tcgen05.st), two
+//               buffers, so a tile's P never waits for the output product of the tile before.
 //
 // Exactness: scores are scaled by scale * log2(e) in float after the product, exponentials are base 2 (ex2.approx),
 // the sum and the max are float, P is rounded to bfloat16 once.  The keys a query sees and their order do not depend
