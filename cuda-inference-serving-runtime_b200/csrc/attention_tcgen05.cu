@@ -1,15 +1,17 @@
 // Causal grouped-query attention of prompt portions on the 5th-generation tensor cores, for head sizes 64 and 128
 // (bfloat16 cache).  One CTA per (128-query tile, query head); scores and the output accumulate in tensor memory.
 //
-//   warp 0      producer: the query tile once, then key and value tiles (128 keys at head size 64, 64 at 128) into a
-//               four-stage ring, by
-//               tensor-map copies (cp.async.bulk.tensor.2d, 128-byte swizzle), one box per page and 64 columns
+//   warps 0, 2  producers: warp 0 the query tile once and then the key tiles, warp 2 the value tiles (128 keys each),
+//               into rings of their own (four stages each at head size 64; three key and two value stages at 128),
+//               by tensor-map copies (cp.async.bulk.tensor.2d, 128-byte swizzle), one box per page and 64 columns;
+//               page ids come straight from the block table.  A key tile is free again when its score product is
+//               done, a value tile after the output product, one softmax later
 //   warp 1      one thread issues the products: S = Q K^T (tcgen05.mma kind::f16, M = 128, N = 128, K = 16 steps,
 //               Q and K both K-major) into one of two score buffers in tensor memory, and O += P V (N = head size,
 //               P read from tensor memory as the A operand, V as the MN-major B operand straight from its
 //               [key][dim] tile); the score product of tile j + 1 is issued before the output product of tile j, so it
 //               runs while the softmax warps work on tile j
-//   warps 2..9  softmax, two groups of four warps: thread (group, r) owns half of the columns of query row r
+//   warps 3..10 softmax, two groups of four warps: thread (group, r) owns half of the columns of query row r
 //               (tensor-memory lane r).  It reads them with tcgen05.ld and keeps the running max and sum in float.
 //               Once the row has a max in use, the exponentials of a tile are taken against it in the same pass that
 //               finds the tile's own max; only when that turns out more than 8 above the max in use (a stale max is
@@ -40,22 +42,23 @@ namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int D = HEAD_DIM;
 constexpr int NSUB = D / 64;                  // 64-column sub-tiles of Q, K and V rows
-constexpr int BN = D == 64 ? 128 : 64;        // keys per tile: a tile's keys and values are 32 KB at either head size
+constexpr int BN = 128;                       // keys per tile
 constexpr int SUB_BYTES = 128 * 128;          // one 128-row x 64-column sub-tile (queries, probabilities)
 constexpr int KV_SUB = BN * 128;              // one BN-key x 64-column sub-tile (keys, values)
 constexpr int Q_BYTES = NSUB * SUB_BYTES;
 constexpr int KV_BYTES = NSUB * KV_SUB;       // a K tile, or a V tile
 constexpr int P_COL0 = 384;                   // tensor memory: scores [0, 2 BN), output [256, 256 + D), probabilities from here
 constexpr int P_COLS = BN / 2;                // a tile's probabilities: bfloat16 pairs, two buffers
-#ifndef ATTN_STAGES
-#define ATTN_STAGES 4
-#endif
-constexpr int STAGES = ATTN_STAGES;           // key/value tiles on their way: a copy takes several tiles' worth of time to land
-constexpr size_t SMEM_FIXED = 1024 + Q_BYTES + STAGES * 2 * KV_BYTES + 256 + 4 * 128 * sizeof(float);
+// Key tiles and value tiles have rings of their own: a key tile is free again when its score product is done, a value
+// tile only after the output product, one softmax later.  A tile is 16 KB at head size 64 and 32 KB at 128.
+constexpr int K_STAGES = D == 64 ? 4 : 3;
+constexpr int V_STAGES = D == 64 ? 4 : 2;
+constexpr size_t SMEM_FIXED = 1024 + Q_BYTES + (K_STAGES + V_STAGES) * KV_BYTES + 256 + 4 * 128 * sizeof(float);
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.f;           // the max may lag by this much (base-2 exponent) before O is rescaled
 constexpr int SOFTMAX_THREADS = 256;          // two groups of four warps: each thread has half of a query row's columns
-constexpr int THREADS = 64 + SOFTMAX_THREADS;
+constexpr int FIRST_SOFTMAX_WARP = 3;         // warps 0 to 2: key producer, issuing thread, value producer
+constexpr int THREADS = 32 * FIRST_SOFTMAX_WARP + SOFTMAX_THREADS;
 constexpr int HALF = BN / 2;                  // score columns per softmax thread and tile
 bool g_pdl = false;
 int* g_error = nullptr;
@@ -81,20 +84,22 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* Qs = base;                                   // [NSUB][128 queries][128 B]
-    unsigned char* KVs = Qs + Q_BYTES;                          // [STAGES][K tile | V tile], each [NSUB][BN keys][128 B]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(KVs + STAGES * 2 * KV_BYTES);
+    unsigned char* Kring = Qs + Q_BYTES;                        // [K_STAGES] key tiles, each [NSUB][BN keys][128 B]
+    unsigned char* Vring = Kring + K_STAGES * KV_BYTES;         // [V_STAGES] value tiles, the same layout
+    uint64_t* bars = reinterpret_cast<uint64_t*>(Vring + V_STAGES * KV_BYTES);
     uint64_t* q_full = bars;                                    // the query tile has landed
-    uint64_t* kv_full = bars + 1;                               // [STAGES] a stage's keys and values have landed
-    uint64_t* kv_empty = kv_full + STAGES;                      // [STAGES] the products that read the stage are done
-    uint64_t* s_full = kv_empty + STAGES;                       // [2] a score buffer is complete
+    uint64_t* k_full = bars + 1;                                // [K_STAGES] a key tile has landed
+    uint64_t* k_empty = k_full + K_STAGES;                      // [K_STAGES] the score product that read it is done
+    uint64_t* v_full = k_empty + K_STAGES;                      // [V_STAGES] a value tile has landed
+    uint64_t* v_empty = v_full + V_STAGES;                      // [V_STAGES] the output product that read it is done
+    uint64_t* s_full = v_empty + V_STAGES;                      // [2] a score buffer is complete
     uint64_t* s_empty = s_full + 2;                             // [2] the softmax threads have read it
     uint64_t* p_full = s_empty + 2;                             // P is in shared memory (and O rescaled)
     uint64_t* pv_done = p_full + 1;                             // the output product of a tile is done
-    static_assert(1 + 2 * STAGES + 6 <= 23, "the barriers and the two words behind them fit 192 bytes");
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
+    static_assert(1 + 2 * (K_STAGES + V_STAGES) + 6 <= 31, "the barriers and the two words behind them fit 256 bytes");
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 31);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
-    float* exchange = reinterpret_cast<float*>(bars + 24);      // [2 sets][2 groups][128 rows]: the groups' maxima of a tile, then their sums
-    int* pages = reinterpret_cast<int*>(exchange + 4 * BM);     // block table entries of this tile's key range
+    float* exchange = reinterpret_cast<float*>(bars + 32);      // [2 sets][2 groups][128 rows]: the groups' maxima of a tile, then their sums
 
     pdl_trigger();
     const int tile = blockIdx.x, head = blockIdx.y;
@@ -110,11 +115,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int k_end = qpos0 + rows;                                                       // the last row sees keys up to its own position
     const int k_begin = ((window > 0 ? max(0, qpos0 - window + 1) : 0) / BN) * BN;
     const int n_tiles = (k_end - k_begin + BN - 1) / BN;
-    const int first_page = k_begin / page_size;
-    for (int i = tid; i <= (k_end - 1) / page_size - first_page; i += THREADS) pages[i] = table[first_page + i];
     if (tid == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
+        for (int s = 0; s < K_STAGES; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
+        for (int s = 0; s < V_STAGES; ++s) { mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(s_full + s, 1); mbar_init(s_empty + s, SOFTMAX_THREADS / 32); }
         mbar_init(p_full, SOFTMAX_THREADS / 32);       // one arrival per softmax warp, by its first lane after the warp has met
         mbar_init(pv_done, 1);
@@ -145,27 +149,32 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         return false;
     };
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ producer
-        if (lane == 0) {
+    if (warp == 0 || warp == 2) {
+        // ------------------------------------------------------------ producers: warp 0 the queries and the keys, warp 2 the values
+        const bool values = warp == 2;
+        const int stages = values ? V_STAGES : K_STAGES;
+        uint64_t* full = values ? v_full : k_full;
+        uint64_t* empty = values ? v_empty : k_empty;
+        unsigned char* ring = values ? Vring : Kring;
+        const CUtensorMap* map = values ? &map_v : &map_k;
+        if (!values && lane == 0) {
             mbar_expect_tx(q_full, (uint32_t)Q_BYTES);
             for (int sub = 0; sub < NSUB; ++sub) tma_load_2d(Qs + sub * SUB_BYTES, &map_q, head * D + sub * 64, tok0, q_full);
         }
         const int box_rows = min(page_size, BN), boxes = BN / box_rows;
         for (int j = 0; j < n_tiles; ++j) {
-            const int s = j % STAGES;
+            const int s = j % stages;
             bool ok = true;
-            if (j >= STAGES) ok = wait(kv_empty + s, ((j / STAGES) & 1) ^ 1);
+            if (j >= stages) ok = wait(empty + s, ((j / stages) & 1) ^ 1);
             if (!__all_sync(0xffffffffu, ok)) break;
-            unsigned char* Ks = KVs + s * 2 * KV_BYTES;
-            if (lane == 0) mbar_expect_tx(kv_full + s, (uint32_t)(2 * KV_BYTES));
+            if (lane == 0) mbar_expect_tx(full + s, (uint32_t)KV_BYTES);
             __syncwarp();
-            for (int b = lane; b < 2 * NSUB * boxes; b += 32) {
-                const int i = b % boxes, sub = (b / boxes) % NSUB, is_v = b / (boxes * NSUB);
+            for (int b = lane; b < NSUB * boxes; b += 32) {       // lane b: box b (64-column half, run of box_rows keys)
+                const int i = b % boxes, sub = b / boxes;
                 const int kpos = k_begin + j * BN + i * box_rows;
-                const int page = kpos < k_end ? pages[kpos / page_size - first_page] : -1;
+                const int page = kpos < k_end ? __ldg(table + kpos / page_size) : -1;     // the table is older than the kernel before
                 const int row = page < 0 ? cache_rows : (page * hkv + kvh) * page_size + kpos % page_size;   // beyond the cache: zeros
-                tma_load_2d(Ks + is_v * KV_BYTES + sub * KV_SUB + i * box_rows * 128, is_v ? &map_v : &map_k, sub * 64, row, kv_full + s);
+                tma_load_2d(ring + s * KV_BYTES + sub * KV_SUB + i * box_rows * 128, map, sub * 64, row, full + s);
             }
         }
     } else if (warp == 1) {
@@ -173,8 +182,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc(BN);
             constexpr uint32_t idesc_o = umma_idesc(D) | UMMA_B_MN_MAJOR;
-            auto output_product = [&](int j) {                    // O += P(j) V(j)
-                const unsigned char* Vs = KVs + (j % STAGES) * 2 * KV_BYTES + KV_BYTES;
+            auto output_product = [&](int j) -> bool {            // O += P(j) V(j)
+                if (!wait(v_full + j % V_STAGES, (j / V_STAGES) & 1)) return false;
+                tcgen05_fence_after();
+                const unsigned char* Vs = Vring + (j % V_STAGES) * KV_BYTES;
                 const uint32_t tmem_p = tmem_base + (uint32_t)(P_COL0 + (j & 1) * P_COLS);
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks) {            // 16 keys per step: 8 columns of P, V two 8-row groups down
@@ -182,15 +193,16 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     umma_bf16_ts(tmem_o, tmem_p + 8 * ks, desc_v, idesc_o, (j | ks) != 0);
                 }
                 umma_commit(pv_done);
-                umma_commit(kv_empty + j % STAGES);
+                umma_commit(v_empty + j % V_STAGES);
+                return true;
             };
             bool ok = wait(q_full, 0);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j & 1, ph = (j >> 1) & 1;              // the score buffer and its phase
-                ok = wait(kv_full + j % STAGES, (j / STAGES) & 1) && wait(s_empty + s, ph ^ 1);
+                ok = wait(k_full + j % K_STAGES, (j / K_STAGES) & 1) && wait(s_empty + s, ph ^ 1);
                 if (!ok) break;
                 tcgen05_fence_after();
-                const unsigned char* Ks = KVs + (j % STAGES) * 2 * KV_BYTES;
+                const unsigned char* Ks = Kring + (j % K_STAGES) * KV_BYTES;
 #pragma unroll
                 for (int kd = 0; kd < D / 16; ++kd) {             // 16 of the head's dimensions per step
                     const uint64_t desc_q = umma_desc(Qs + (kd >> 2) * SUB_BYTES) + 2 * (kd & 3);
@@ -198,17 +210,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     umma_bf16(tmem_base + (uint32_t)(s * BN), desc_q, desc_k, idesc_s, kd != 0);
                 }
                 umma_commit(s_full + s);
+                umma_commit(k_empty + j % K_STAGES);              // the key tile is free when these products are done
                 if (j > 0) {
-                    ok = wait(p_full, (j - 1) & 1);
+                    ok = wait(p_full, (j - 1) & 1) && output_product(j - 1);
                     if (!ok) break;
-                    tcgen05_fence_after();
-                    output_product(j - 1);
                 }
             }
-            if (ok && wait(p_full, (n_tiles - 1) & 1)) {
-                tcgen05_fence_after();
-                output_product(n_tiles - 1);
-            }
+            if (ok && wait(p_full, (n_tiles - 1) & 1)) output_product(n_tiles - 1);
         }
     } else {
         // ------------------------------------------------------------ softmax and output
@@ -216,7 +224,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // score tile.  The two threads of a row exchange their maxima through shared memory, so both follow the same
         // max; each keeps the sum of its own half, added at the end.
         const int quarter = warp & 3;                              // the 32 tensor-memory lanes this warp may touch
-        const int group = (warp - 2) >> 2;
+        const int group = (warp - FIRST_SOFTMAX_WARP) >> 2;
         const int row = quarter * 32 + lane;
         const int qpos = qpos0 + row;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
@@ -338,9 +346,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tcgen05_fence_before();
             if (k_begin + j * BN + BN > k_end) {
                 // Value rows beyond the last key were never written, or are left over from another request: they must
-                // not meet the zero probabilities of those keys (0 * NaN).  The stage has landed (S came from it).
-                unsigned char* Vs = KVs + (j % STAGES) * 2 * KV_BYTES + KV_BYTES;
-                for (int e = tid - 64; e < BN * NSUB * 8; e += SOFTMAX_THREADS) {
+                // not meet the zero probabilities of those keys (0 * NaN).  Once the tile has landed they are zeroed.
+                ok = __all_sync(0xffffffffu, wait(v_full + j % V_STAGES, (j / V_STAGES) & 1));
+                if (!ok) return;
+                unsigned char* Vs = Vring + (j % V_STAGES) * KV_BYTES;
+                for (int e = tid - 32 * FIRST_SOFTMAX_WARP; e < BN * NSUB * 8; e += SOFTMAX_THREADS) {
                     const int r = e / (NSUB * 8), c = e - r * (NSUB * 8);
                     if (k_begin + j * BN + r >= k_end)
                         *reinterpret_cast<uint4*>(Vs + (c >> 3) * KV_SUB + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
@@ -421,8 +431,8 @@ CISR_EXPORT int cisr_attn_prefill_tcgen05(const void* q, void* out, int n_tokens
     if (status) return status;
     if ((status = cached_map(&map_k, k_cache, cache_rows, D, box_rows, 64))) return status;
     if ((status = cached_map(&map_v, v_cache, cache_rows, D, box_rows, 64))) return status;
-    const size_t smem = SMEM_FIXED + sizeof(int) * ((size_t)table_width + 4);     // a tile's key range spans at most the table
-    if (smem > 225 * 1024) return -3;
+    const size_t smem = SMEM_FIXED;
+    static_assert(SMEM_FIXED <= 227 * 1024, "a CTA has 227 KB of shared memory");
     static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
