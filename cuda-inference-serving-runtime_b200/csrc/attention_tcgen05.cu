@@ -7,22 +7,23 @@
 //               page ids come straight from the block table.  A key tile is free again when its score product is
 //               done, a value tile after the output product, one softmax later
 //   warp 1      one thread issues the products: S = Q K^T (tcgen05.mma kind::f16, M = 128, N = 128, K = 16 steps,
-//               Q and K both K-major) into one of two score buffers in tensor memory, and O += P V (N = head size,
-//               P read from tensor memory as the A operand, V as the MN-major B operand straight from its
-//               [key][dim] tile); the score product of tile j + 1 is issued before the output product of tile j, so it
-//               runs while the softmax warps work on tile j
-//   warps 3..10 softmax, two groups of four warps: thread (group, r) owns half of the columns of query row r
-//               (tensor-memory lane r).  It reads them with tcgen05.ld and keeps the running max and sum in float.
-//               Once the row has a max in use, the exponentials of a tile are taken against it in the same pass that
-//               finds the tile's own max; only when that turns out more than 8 above the max in use (a stale max is
-//               exact arithmetic as long as 2^(s - m) stays small; the final division by the sum uses the same max)
-//               is the row of O rescaled and the tile done again from the scores, which stay in tensor memory until
-//               P is handed over.  P = 2^(s - m) goes back to tensor memory as bfloat16 pairs (tcgen05.st), two
-//               buffers, so a tile's P never waits for the output product of the tile before.
+//               Q and K both K-major) into one of two score buffers in tensor memory, and, for each half of a
+//               tile's keys, O_g += P_g V (N = head size, P read from tensor memory as the A operand, V as the
+//               MN-major B operand straight from its [key][dim] tile).  The scores run two tiles ahead of the
+//               output products
+//   warps 3..10 softmax, two groups of four warps, each a stream of its own: thread (group g, r) has keys
+//               [64 g, 64 g + 64) of every tile for query row r (tensor-memory lane r), its own running max and sum
+//               in float and its own output accumulator O_g, so one group's exponentials run while the other waits,
+//               loads or stores.  Once a row has a max in use, the exponentials of a tile are taken against it in
+//               the same pass that finds the tile's own max; only when that turns out more than 8 above the max in
+//               use (a stale max is exact arithmetic as long as 2^(s - m) stays small) is the row of O_g rescaled
+//               and the tile done again from the scores.  P = 2^(s - m) goes back to tensor memory as bfloat16
+//               pairs (tcgen05.st) over the first half of the thread's own scores.  At the end the two streams of
+//               a row are merged with their maxima and sums.
 //
 // Exactness: scores are scaled by scale * log2(e) in float after the product, exponentials are base 2 (ex2.approx),
-// the sum and the max are float, P is rounded to bfloat16 once.  The keys a query sees and their order do not depend
-// on the batch: tiles start at multiples of 128 in absolute positions.
+// the sums and the maxima are float, P is rounded to bfloat16 once.  The keys a query sees, their split into the two
+// streams and their order do not depend on the batch: tiles start at multiples of 128 in absolute positions.
 //
 // Every wait on an mbarrier is bounded; a role whose wait ran out raises the CTA's abort flag and the device flag
 // (5), the other roles leave at their next wait, tensor memory is freed, and the host reports the failure.
@@ -47,8 +48,7 @@ constexpr int SUB_BYTES = 128 * 128;          // one 128-row x 64-column sub-til
 constexpr int KV_SUB = BN * 128;              // one BN-key x 64-column sub-tile (keys, values)
 constexpr int Q_BYTES = NSUB * SUB_BYTES;
 constexpr int KV_BYTES = NSUB * KV_SUB;       // a K tile, or a V tile
-constexpr int P_COL0 = 384;                   // tensor memory: scores [0, 2 BN), output [256, 256 + D), probabilities from here
-constexpr int P_COLS = BN / 2;                // a tile's probabilities: bfloat16 pairs, two buffers
+// tensor memory: two score buffers [0, 2 BN), then the two groups' output accumulators [256, 256 + 2 D)
 // Key tiles and value tiles have rings of their own: a key tile is free again when its score product is done, a value
 // tile only after the output product, one softmax later.  A tile is 16 KB at head size 64 and 32 KB at 128.
 constexpr int K_STAGES = D == 64 ? 4 : 3;
@@ -93,10 +93,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint64_t* v_full = k_empty + K_STAGES;                      // [V_STAGES] a value tile has landed
     uint64_t* v_empty = v_full + V_STAGES;                      // [V_STAGES] the output product that read it is done
     uint64_t* s_full = v_empty + V_STAGES;                      // [2] a score buffer is complete
-    uint64_t* s_empty = s_full + 2;                             // [2] the softmax threads have read it
-    uint64_t* p_full = s_empty + 2;                             // P is in shared memory (and O rescaled)
-    uint64_t* pv_done = p_full + 1;                             // the output product of a tile is done
-    static_assert(1 + 2 * (K_STAGES + V_STAGES) + 6 <= 31, "the barriers and the two words behind them fit 256 bytes");
+    // [2 groups][2 score buffers] a group's P of a tile is in tensor memory (and its O rescaled).  One barrier per score
+    // buffer: a group may finish tile j + 1 before the issuing thread has looked at its tile j, and a barrier tells
+    // only the last phase from the one before
+    uint64_t* p_full = s_full + 2;
+    uint64_t* pv_done = p_full + 4;                             // [2] a group's output product of a tile is done
+    static_assert(1 + 2 * (K_STAGES + V_STAGES) + 8 <= 31, "the barriers and the two words behind them fit 256 bytes");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 31);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
     float* exchange = reinterpret_cast<float*>(bars + 32);      // [2 sets][2 groups][128 rows]: the groups' maxima of a tile, then their sums
@@ -119,9 +121,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_init(q_full, 1);
         for (int s = 0; s < K_STAGES; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
         for (int s = 0; s < V_STAGES; ++s) { mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(s_full + s, 1); mbar_init(s_empty + s, SOFTMAX_THREADS / 32); }
-        mbar_init(p_full, SOFTMAX_THREADS / 32);       // one arrival per softmax warp, by its first lane after the warp has met
-        mbar_init(pv_done, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(s_full + s, 1);
+            mbar_init(p_full + 2 * s, SOFTMAX_THREADS / 64);   // one arrival per warp of the group, by its first lane after the warp has met
+            mbar_init(p_full + 2 * s + 1, SOFTMAX_THREADS / 64);
+            mbar_init(pv_done + s, 1);
+        }
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -182,79 +187,78 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc(BN);
             constexpr uint32_t idesc_o = umma_idesc(D) | UMMA_B_MN_MAJOR;
-            auto output_product = [&](int j) -> bool {            // O += P(j) V(j)
-                if (!wait(v_full + j % V_STAGES, (j / V_STAGES) & 1)) return false;
-                tcgen05_fence_after();
-                const unsigned char* Vs = Vring + (j % V_STAGES) * KV_BYTES;
-                const uint32_t tmem_p = tmem_base + (uint32_t)(P_COL0 + (j & 1) * P_COLS);
-#pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {            // 16 keys per step: 8 columns of P, V two 8-row groups down
-                    const uint64_t desc_v = umma_desc_mn_major(Vs + ks * 16 * 128, KV_SUB);
-                    umma_bf16_ts(tmem_o, tmem_p + 8 * ks, desc_v, idesc_o, (j | ks) != 0);
-                }
-                umma_commit(pv_done);
-                umma_commit(v_empty + j % V_STAGES);
-                return true;
-            };
-            bool ok = wait(q_full, 0);
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j & 1, ph = (j >> 1) & 1;              // the score buffer and its phase
-                ok = wait(k_full + j % K_STAGES, (j / K_STAGES) & 1) && wait(s_empty + s, ph ^ 1);
-                if (!ok) break;
+            auto score_product = [&](int j) -> bool {             // S(j) = Q K(j)^T into score buffer j & 1
+                if (!wait(k_full + j % K_STAGES, (j / K_STAGES) & 1)) return false;
                 tcgen05_fence_after();
                 const unsigned char* Ks = Kring + (j % K_STAGES) * KV_BYTES;
 #pragma unroll
                 for (int kd = 0; kd < D / 16; ++kd) {             // 16 of the head's dimensions per step
                     const uint64_t desc_q = umma_desc(Qs + (kd >> 2) * SUB_BYTES) + 2 * (kd & 3);
                     const uint64_t desc_k = umma_desc(Ks + (kd >> 2) * KV_SUB) + 2 * (kd & 3);
-                    umma_bf16(tmem_base + (uint32_t)(s * BN), desc_q, desc_k, idesc_s, kd != 0);
+                    umma_bf16(tmem_base + (uint32_t)((j & 1) * BN), desc_q, desc_k, idesc_s, kd != 0);
                 }
-                umma_commit(s_full + s);
+                umma_commit(s_full + (j & 1));
                 umma_commit(k_empty + j % K_STAGES);              // the key tile is free when these products are done
-                if (j > 0) {
-                    ok = wait(p_full, (j - 1) & 1) && output_product(j - 1);
-                    if (!ok) break;
+                return true;
+            };
+            // O_g += P_g(j) V(j)[keys 64 g ...]: half g of the tile's keys, with the P that group g left over the first
+            // 32 columns of its own scores
+            auto output_product = [&](int j, int g) {
+                const unsigned char* Vs = Vring + (j % V_STAGES) * KV_BYTES;
+                const uint32_t tmem_p = tmem_base + (uint32_t)((j & 1) * BN + g * HALF);
+#pragma unroll
+                for (int ks = 0; ks < HALF / 16; ++ks) {          // 16 keys per step: 8 columns of P, V two 8-row groups down
+                    const uint64_t desc_v = umma_desc_mn_major(Vs + (g * HALF + ks * 16) * 128, KV_SUB);
+                    umma_bf16_ts(tmem_o + (uint32_t)(g * D), tmem_p + 8 * ks, desc_v, idesc_o, (j | ks) != 0);
                 }
+                umma_commit(pv_done + g);
+            };
+            // Both score buffers are filled at the start.  Then, tile by tile: each half's output product as soon as its
+            // P has arrived, and after both the scores of the tile two on, into the buffer that these output products
+            // read P from: products run in the order they are issued, so the buffer is overwritten after it was read.
+            bool ok = wait(q_full, 0) && score_product(0);
+            if (ok && n_tiles > 1) ok = score_product(1);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                ok = wait(v_full + j % V_STAGES, (j / V_STAGES) & 1);
+                for (int g = 0; g < 2 && ok; ++g) {
+                    ok = wait(p_full + 2 * g + (j & 1), (j >> 1) & 1);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    output_product(j, g);
+                }
+                if (!ok) break;
+                umma_commit(v_empty + j % V_STAGES);
+                if (j + 2 < n_tiles) ok = score_product(j + 2);
             }
-            if (ok && wait(p_full, (n_tiles - 1) & 1)) output_product(n_tiles - 1);
         }
     } else {
         // ------------------------------------------------------------ softmax and output
-        // Two groups of four warps; thread (group, r) has columns [64 * group, 64 * group + 64) of query row r of every
-        // score tile.  The two threads of a row exchange their maxima through shared memory, so both follow the same
-        // max; each keeps the sum of its own half, added at the end.
+        // Two groups of four warps, each a stream of its own: thread (group, r) has the keys [64 * group, 64 * group + 64)
+        // of every tile for query row r, with its own running max and sum and its own output accumulator; nothing is
+        // exchanged between the groups until the end, so one group's exponentials run while the other waits or stores.
         const int quarter = warp & 3;                              // the 32 tensor-memory lanes this warp may touch
         const int group = (warp - FIRST_SOFTMAX_WARP) >> 2;
         const int row = quarter * 32 + lane;
         const int qpos = qpos0 + row;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t tmem_own = tmem_o + lane_base + (uint32_t)(group * D);     // this thread's row of its group's accumulator
         const float scale2 = scale * LOG2E;
         auto softmax_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory"); };
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
-        // (Requesting the scores of tile j + 1 while tile j is worked on, into a second set of registers, was slower.)
-        auto request = [&](int j, uint32_t* dst) {
-            const uint32_t addr = tmem_base + lane_base + (uint32_t)((j & 1) * BN + group * HALF);
-#pragma unroll
-            for (int c0 = 0; c0 < HALF; c0 += 32) tmem_load32_nowait(addr + c0, dst + c0);
-        };
         uint32_t raw[HALF];
-        // A warp whose wait ran out keeps walking the tiles (every later wait returns at once) so that the barrier between
-        // the two groups is reached the same number of times by all.
         auto step = [&](int j) {
-            const int s = j & 1;
-            if (ok) ok = __all_sync(0xffffffffu, wait(s_full + s, (j >> 1) & 1));
+            if (ok) ok = __all_sync(0xffffffffu, wait(s_full + (j & 1), (j >> 1) & 1));
+            if (!ok) return;
             const int kt = k_begin + j * BN;                       // the tile's first key
             const int k0 = kt + group * HALF;                     // this thread's first key
             // tiles on the diagonal, at the window's start and at the end of the keys need the per-element mask
             const bool edge = kt + BN - 1 > qpos0 || kt + BN > k_end || (window > 0 && kt <= qpos0 + BM - 1 - window);
             auto masked = [&](int kpos) { return kpos > qpos || kpos >= k_end || (window > 0 && kpos <= qpos - window); };
-            // One pass when the row already has a max in use: the exponentials are taken against it while the tile's own
-            // max is found, and only a tile whose max turns out more than RESCALE_STEP above it is done again (from the
-            // scores, which stay in tensor memory until this tile's P is handed over).  A warp with a row that has no
-            // max yet (the first tile, or only masked keys so far) finds the max first.
+            const uint32_t s_addr = tmem_base + lane_base + (uint32_t)((j & 1) * BN + group * HALF);
             auto fetch = [&]() {
-                request(j, raw);
+#pragma unroll
+                for (int c0 = 0; c0 < HALF; c0 += 32) tmem_load32_nowait(s_addr + c0, raw + c0);
                 tmem_load_wait();
                 if (edge) {
 #pragma unroll
@@ -279,31 +283,21 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 mx_out = fmaxf(mx[0], mx[1]);
                 return (sums[0] + sums[1]) + (sums[2] + sums[3]);
             };
-            float m_tile = -INFINITY, sum = 0.f;
-            bool ahead = false;                                   // the exponentials were taken before the max was known
-            if (ok) {
-                tcgen05_fence_after();
-                fetch();                       // this tile's half row of scores is in registers
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(s_empty + s);
-                ahead = __all_sync(0xffffffffu, m_used != -INFINITY);
-                float mx = -INFINITY;
-                if (ahead) {
-                    sum = exponentials(m_used, mx);
-                } else {
+            // One pass when the row already has a max in use: the exponentials are taken against it while the tile's own
+            // max is found, and only a tile whose max turns out more than RESCALE_STEP above it is done again (from the
+            // scores, which stay in tensor memory until P is written over them).  A warp with a row that has no max
+            // yet (the first tile, or only masked keys so far) finds the max first.
+            tcgen05_fence_after();
+            fetch();
+            const bool ahead = __all_sync(0xffffffffu, m_used != -INFINITY);
+            float mx = -INFINITY, sum = 0.f;
+            if (ahead) {
+                sum = exponentials(m_used, mx);
+            } else {
 #pragma unroll
-                    for (int c = 0; c < HALF; ++c) mx = fmaxf(mx, __uint_as_float(raw[c]));
-                }
-                m_tile = mx * scale2;          // the scale is positive: the max of the raw scores, scaled
+                for (int c = 0; c < HALF; ++c) mx = fmaxf(mx, __uint_as_float(raw[c]));
             }
-            // the two threads of a row exchange their maxima (a read of the partner's half from tensor memory instead
-            // costs a second load round trip, which was slower); every warp reaches this barrier in every iteration
-            float* slot = exchange + (j & 1) * 2 * BM;           // two sets: a thread a tile ahead writes the other one
-            slot[group * BM + row] = m_tile;
-            softmax_sync();
-            m_tile = fmaxf(m_tile, slot[(group ^ 1) * BM + row]);
-            if (!ok) return;
+            const float m_tile = mx * scale2;                     // the scale is positive: the max of the raw scores, scaled
             // the max in use moves only when it lags by more than RESCALE_STEP; the first finite max is taken as it is
             float alpha = 1.f;
             const bool moved = m_tile > m_used + RESCALE_STEP || (m_used == -INFINITY && m_tile > -INFINITY);
@@ -316,74 +310,82 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 float unused;
                 sum = exponentials(m_ref, unused);
             } else if (__any_sync(0xffffffffu, moved)) {          // tensor-memory access is warp-wide: every lane does its row again
-                tcgen05_fence_after();
                 fetch();
                 float unused;
                 sum = exponentials(m_ref, unused);
             }
-            const bool rescale = __any_sync(0xffffffffu, alpha != 1.f);
-            // O is free once the output product of the tile before is done.  P's buffer (one of two) was read by the
-            // product of two tiles back, which the issuing thread sent before this tile's scores: their arrival covers it.
-            if (j > 0 && rescale) ok = __all_sync(0xffffffffu, wait(pv_done, (j - 1) & 1));
-            if (!ok) return;
-            tcgen05_fence_after();
-            if (group == 0 && j > 0 && rescale) {                 // all lanes go, most with alpha 1
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // the group's accumulator may be touched once its output product of the tile before is done; all lanes
+                // go, most with alpha 1
+                ok = __all_sync(0xffffffffu, wait(pv_done + group, (j - 1) & 1));
+                if (!ok) return;
+                tcgen05_fence_after();
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t acc[32];
-                    tmem_load32(tmem_o + lane_base + c0, acc);
+                    tmem_load32(tmem_own + c0, acc);
 #pragma unroll
                     for (int c = 0; c < 32; ++c) acc[c] = __float_as_uint(__uint_as_float(acc[c]) * alpha);
-                    tmem_store32(tmem_o + lane_base + c0, acc);
+                    tmem_store32(tmem_own + c0, acc);
                 }
             }
             l = l * alpha + sum;
-            // the thread's half row of P into tensor memory, where the output product reads it as its A operand
-            const uint32_t p_addr = tmem_base + lane_base + (uint32_t)(P_COL0 + (j & 1) * P_COLS + group * (HALF / 2));
+            // the thread's P goes over the first half of its own scores, where the output product reads it as its A operand
 #pragma unroll
-            for (int c0 = 0; c0 < HALF / 2; c0 += 16) tmem_store16_nowait(p_addr + c0, packed + c0);
+            for (int c0 = 0; c0 < HALF / 2; c0 += 16) tmem_store16_nowait(s_addr + c0, packed + c0);
             tmem_store_wait();
             tcgen05_fence_before();
-            if (k_begin + j * BN + BN > k_end) {
+            if (kt + BN > k_end) {
                 // Value rows beyond the last key were never written, or are left over from another request: they must
-                // not meet the zero probabilities of those keys (0 * NaN).  Once the tile has landed they are zeroed.
+                // not meet the zero probabilities of those keys (0 * NaN).  Once the tile has landed, each group zeroes
+                // those among the rows that its own output product reads.
                 ok = __all_sync(0xffffffffu, wait(v_full + j % V_STAGES, (j / V_STAGES) & 1));
                 if (!ok) return;
                 unsigned char* Vs = Vring + (j % V_STAGES) * KV_BYTES;
-                for (int e = tid - 32 * FIRST_SOFTMAX_WARP; e < BN * NSUB * 8; e += SOFTMAX_THREADS) {
-                    const int r = e / (NSUB * 8), c = e - r * (NSUB * 8);
-                    if (k_begin + j * BN + r >= k_end)
+                for (int e = (warp - FIRST_SOFTMAX_WARP - 4 * group) * 32 + lane; e < HALF * NSUB * 8; e += SOFTMAX_THREADS / 2) {
+                    const int r = group * HALF + e / (NSUB * 8), c = e % (NSUB * 8);
+                    if (kt + r >= k_end)
                         *reinterpret_cast<uint4*>(Vs + (c >> 3) * KV_SUB + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroed rows before the tensor core reads them
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(p_full + 2 * group + (j & 1));
         };
         for (int j = 0; j < n_tiles; ++j) step(j);
-        if (ok) ok = wait(pv_done, (n_tiles - 1) & 1);
+        if (ok) ok = wait(pv_done, (n_tiles - 1) & 1) && wait(pv_done + 1, (n_tiles - 1) & 1);
         const bool all_ok = __all_sync(0xffffffffu, ok);
         if (!all_ok) *(volatile int*)abort_flag = 1;
-        // the row's sum: both halves; each group then writes half of the output columns
-        exchange[group * BM + row] = l;
+        // The two streams of a row meet: with m the larger of their maxima, out = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) /
+        // (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)); each group writes half of the output columns.
+        exchange[group * BM + row] = m_used;
+        exchange[(2 + group) * BM + row] = l;
         softmax_sync();
         if (all_ok && !*(volatile int*)abort_flag) {
             tcgen05_fence_after();
-            const float total = exchange[row] + exchange[BM + row];
+            const float m0 = exchange[row], m1 = exchange[BM + row], m = fmaxf(m0, m1);
+            const float w0 = m0 == -INFINITY ? 0.f : fast_exp2(m0 - m), w1 = m1 == -INFINITY ? 0.f : fast_exp2(m1 - m);
+            const float total = exchange[2 * BM + row] * w0 + exchange[3 * BM + row] * w1;
             const float inv = total > 0.f ? 1.f / total : 0.f;
+            const float f0 = w0 * inv, f1 = w1 * inv;
             bf16* dst = out + ((size_t)(tok0 + row) * hq + head) * D;
 #pragma unroll 1
             for (int c0 = group * (D / 2); c0 < (group + 1) * (D / 2); c0 += 32) {
-                uint32_t acc[32];
-                tmem_load32(tmem_o + lane_base + c0, acc);          // warp-wide, also for rows beyond the portion
+                uint32_t a0[32], a1[32];
+                tmem_load32_nowait(tmem_o + lane_base + c0, a0);            // warp-wide, also for rows beyond the portion
+                tmem_load32_nowait(tmem_o + lane_base + D + c0, a1);
+                tmem_load_wait();
                 if (row < rows) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         uint32_t w[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(acc[8 * q + 2 * e]) * inv,
-                                                                        __uint_as_float(acc[8 * q + 2 * e + 1]) * inv);
+                            const int c = 8 * q + 2 * e;
+                            // a stream without keys for this row weighs nothing, whatever its accumulator holds
+                            const float x0 = (w0 > 0.f ? __uint_as_float(a0[c]) * f0 : 0.f) + (w1 > 0.f ? __uint_as_float(a1[c]) * f1 : 0.f);
+                            const float x1 = (w0 > 0.f ? __uint_as_float(a0[c + 1]) * f0 : 0.f) + (w1 > 0.f ? __uint_as_float(a1[c + 1]) * f1 : 0.f);
+                            __nv_bfloat162 pair = __floats2bfloat162_rn(x0, x1);
                             w[e] = *reinterpret_cast<uint32_t*>(&pair);
                         }
                         *reinterpret_cast<uint4*>(dst + c0 + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
