@@ -530,9 +530,12 @@ def test_skinny_gemm_rope_matches_the_separate_kernels(m, dim, hq, hkv, rot, int
 
 
 @pytest.mark.parametrize("m,n,kk", [(128, 128, 64), (128, 64, 128), (2048, 960, 576), (300, 576, 1536), (130, 49, 72),
-                                    (257, 3072, 576), (129, 100, 8), (1000, 1000, 1000)])
+                                    (257, 3072, 576), (129, 100, 8), (1000, 1000, 1000), (17, 960, 576), (64, 576, 1536),
+                                    (2048, 576, 576), (100, 200, 4096)])
 def test_gemm_tcgen05(m, n, kk):
-    """The tcgen05 + TMA product against a float64 product, at sizes with ragged edges in M, N and K."""
+    """The tcgen05 + TMA product against a float64 product, at sizes with ragged edges in M, N and K; grids of 128 x 256
+    tiles, of 128 x 128 tiles, and of fewer tiles than SMs (deep rings of 128 x 128 and of 128 x 64 tiles); fewer tokens
+    than a tile has rows."""
     k = kernels()
     g = torch.Generator().manual_seed(m + n + kk)
     a = torch.randn(m, kk, generator=g).to(torch.bfloat16)
@@ -544,7 +547,8 @@ def test_gemm_tcgen05(m, n, kk):
     close(out, ref, 2e-6 * kk ** 0.5 * 4, 1e-5, f"tcgen05 gemm {m}x{n}x{kk}")
 
 
-@pytest.mark.parametrize("m,inter,kk", [(128, 64, 64), (300, 176, 64), (2048, 1536, 576), (130, 250, 96), (129, 13, 40)])
+@pytest.mark.parametrize("m,inter,kk", [(128, 64, 64), (300, 176, 64), (2048, 1536, 576), (130, 250, 96), (129, 13, 40),
+                                        (40, 96, 64), (64, 1536, 576), (1024, 4000, 128)])
 def test_gemm_tcgen05_swiglu_epilogue(m, inter, kk):
     k = kernels()
     g = torch.Generator().manual_seed(m + inter)
@@ -558,8 +562,8 @@ def test_gemm_tcgen05_swiglu_epilogue(m, inter, kk):
     close(out, ref, 1e-3, 2 ** -7, "tcgen05 swiglu epilogue")
 
 
-@pytest.mark.parametrize("m", [128, 333])
-@pytest.mark.parametrize("dim,hq,hkv", [(64, 9, 3), (128, 2, 1), (64, 2, 2)])
+@pytest.mark.parametrize("m", [17, 64, 128, 333, 2048])
+@pytest.mark.parametrize("dim,hq,hkv", [(64, 9, 3), (128, 2, 1), (64, 2, 2), (128, 32, 8)])
 def test_gemm_tcgen05_rope_epilogue_matches_the_separate_kernels(m, dim, hq, hkv):
     k = kernels()
     hidden, page, theta = 96, 16, 10000.0
@@ -567,9 +571,10 @@ def test_gemm_tcgen05_rope_epilogue_matches_the_separate_kernels(m, dim, hq, hkv
     w = (0.2 * torch.randn((hq + 2 * hkv) * dim, hidden, generator=g)).to(torch.bfloat16).to(dev())
     hbf = torch.randn(m, hidden, generator=g).to(torch.bfloat16).to(dev())
     positions = torch.arange(m, dtype=torch.int32).to(dev()) % 200
-    token_req = (torch.arange(m) // 200).to(torch.int32).to(dev())               # two requests
-    req_slot = torch.tensor([1, 0], dtype=torch.int32, device=dev())
-    table = torch.arange(32, dtype=torch.int32).reshape(2, 16).to(dev())
+    n_req = -(-m // 200)
+    token_req = (torch.arange(m) // 200).to(torch.int32).to(dev())               # requests of 200 tokens
+    req_slot = torch.arange(n_req - 1, -1, -1, dtype=torch.int32).to(dev())
+    table = torch.arange(16 * n_req, dtype=torch.int32).reshape(n_req, 16).to(dev())
     half = dim // 2
     inv = (theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / dim)).to(dev())
     cos = torch.empty(m, half, device=dev()); sin = torch.empty(m, half, device=dev())
@@ -577,7 +582,7 @@ def test_gemm_tcgen05_rope_epilogue_matches_the_separate_kernels(m, dim, hq, hkv
     results = []
     for fused in (False, True):
         q = torch.zeros(m, hq, dim, dtype=torch.bfloat16, device=dev())
-        kc = torch.zeros(32, hkv, page, dim, dtype=torch.bfloat16, device=dev()); vc = torch.zeros_like(kc)
+        kc = torch.zeros(16 * n_req, hkv, page, dim, dtype=torch.bfloat16, device=dev()); vc = torch.zeros_like(kc)
         if fused:
             k.gemm_tcgen05_rope(hbf, w, dict(cos=cos, sin=sin, q_out=q, k_cache=kc, v_cache=vc, positions=positions, token_req=token_req,
                                              req_slot=req_slot, block_table=table, page_size=page, hq=hq, hkv=hkv, dim=dim))
