@@ -13,7 +13,9 @@ import tiny_models as tm
 
 pytestmark = pytest.mark.gpu
 
-CASES = {"tiny_a": (tm.TINY_A, 11), "tiny_b": (tm.TINY_B, 12), "tiny_c": (tm.TINY_C, 13)}
+# configuration, seed of the weights, their scale (about one over the root of the width: a layer's gain near one)
+CASES = {"tiny_a": (tm.TINY_A, 11, 0.08), "tiny_b": (tm.TINY_B, 12, 0.08), "tiny_c": (tm.TINY_C, 13, 0.08),
+         "tiny_d": (tm.TINY_D, 14, 0.05)}
 LENGTHS = {"a": 150, "b": 70, "c": 33, "d": 200, "e": 90, "f": 3, "g": 129, "h": 64, "i": 47, "j": 111}
 _cache = {}
 
@@ -23,8 +25,8 @@ def setup(case, dtype, tmp_path_factory, sharpen=1.0):
     if key not in _cache:
         from cisr_b200 import Model
 
-        cfg, seed = CASES[case]
-        weights = tm.make_weights(cfg, seed, scale=0.08, bf16_exact=True)
+        cfg, seed, scale = CASES[case]
+        weights = tm.make_weights(cfg, seed, scale=scale, bf16_exact=True)
         if sharpen != 1.0:
             for name in weights:
                 if "q_proj" in name or "k_proj" in name:

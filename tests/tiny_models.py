@@ -67,6 +67,25 @@ TINY_C = {
     "hidden_act": "silu",
 }
 
+# A fourth shape with 64-wide heads, three query heads to a key head: the head geometry for which the engine has its
+# tensor-map decode attention, its tcgen05 prompt attention and the rotation epilogue of the tcgen05 product.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "vocab_size": 173,
+    "hidden_size": 384,
+    "intermediate_size": 272,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 6,
+    "num_key_value_heads": 2,
+    "head_dim": 64,
+    "rms_norm_eps": 2e-5,
+    "rope_theta": 50000.0,
+    "max_position_embeddings": 2048,
+    "tie_word_embeddings": True,
+    "hidden_act": "silu",
+}
+
 
 def tensor_shapes(cfg: dict) -> dict:
     """Name -> shape of every tensor of a Llama checkpoint (runtime/checkpoint.py:45-56)."""
