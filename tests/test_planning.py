@@ -38,3 +38,19 @@ def test_context_buckets_waste_at_most_a_fifth(n):
         assert (b - n) / b < 0.2
     if n > MIN_CONTEXT_BUCKET:
         assert context_bucket_of(n - 1) <= b                          # monotone
+
+
+def test_which_tokens_counts_take_the_tcgen05_product():
+    """The plain product goes to tcgen05 from one 128-row tile on; the product whose epilogue rotates and writes the
+    cache replaces two launches and is taken from 17 tokens on; 16 and fewer belong to the weight-streaming kernels."""
+    import torch
+    from cisr_b200.ops import kernels as k
+
+    w = torch.zeros(192, 64, dtype=torch.bfloat16)
+    for tokens, plain, fused in ((16, False, False), (17, False, True), (127, False, True), (128, True, True), (2048, True, True)):
+        a = torch.zeros(tokens, 64, dtype=torch.bfloat16)
+        assert k.tcgen05_ok(a, w) is plain and k.tcgen05_ok(a, w, fused=True) is fused, tokens
+    assert not k.tcgen05_ok(torch.zeros(256, 64), w)                                   # float32 operands: the library
+    assert not k.tcgen05_ok(torch.zeros(256, 60, dtype=torch.bfloat16), w[:, :60])     # rows that are no multiple of 16 bytes
+    assert k.tcgen05_rope_ok(64, 32, False) and k.tcgen05_rope_ok(128, 64, False)
+    assert not k.tcgen05_rope_ok(64, 16, False) and not k.tcgen05_rope_ok(64, 32, True) and not k.tcgen05_rope_ok(48, 24, False)
