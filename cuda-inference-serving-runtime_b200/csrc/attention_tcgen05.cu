@@ -428,7 +428,7 @@ CISR_EXPORT int cisr_attn_prefill_tcgen05(const void* q, void* out, int n_tokens
     const long long cache_rows = (long long)n_pages * hkv * page_size;
     if (cache_rows <= 0 || cache_rows >= (1ll << 31) || (((uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)q | (uintptr_t)out) & 15)) return -2;
     const int box_rows = page_size < BN ? page_size : BN;
-    const CUtensorMap *map_q, *map_k, *map_v;
+    CUtensorMap map_q, map_k, map_v;
     int status = cached_map(&map_q, q, n_tokens, hq * D, BM, 64);
     if (status) return status;
     if ((status = cached_map(&map_k, k_cache, cache_rows, D, box_rows, 64))) return status;
@@ -441,7 +441,7 @@ CISR_EXPORT int cisr_attn_prefill_tcgen05(const void* q, void* out, int n_tokens
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    return launch_kernel(attn_prefill_tcgen05_kernel, dim3(n_tiles, hq), dim3(THREADS), smem, (cudaStream_t)stream, g_pdl, *map_q,
-                         *map_k, *map_v, (bf16*)out, (int)cache_rows, req_slot, block_table, table_width, tile_req, tile_q0,
+    return launch_kernel(attn_prefill_tcgen05_kernel, dim3(n_tiles, hq), dim3(THREADS), smem, (cudaStream_t)stream, g_pdl, map_q,
+                         map_k, map_v, (bf16*)out, (int)cache_rows, req_slot, block_table, table_width, tile_req, tile_q0,
                          q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, g_error);
 }

@@ -10,7 +10,7 @@
 
 #define CISR_EXPORT extern "C" __attribute__((visibility("default")))
 
-// dtype codes shared with the Python side (ops/library.py)
+// dtype codes shared with the Python side (ops/kernels.py: F32, BF16)
 enum : int { CISR_F32 = 0, CISR_BF16 = 1 };
 
 __device__ __forceinline__ float to_float(float v) { return v; }

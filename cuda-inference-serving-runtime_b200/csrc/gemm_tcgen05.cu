@@ -1,17 +1,21 @@
 // Matrix product on the 5th-generation tensor cores: out[M, N] (float) = a[M, K] * w[N, K]^T, bfloat16
-// operands, float accumulation in tensor memory.  Used for steps with many tokens (prompt portions).
+// operands, float accumulation in tensor memory.  Used for steps with more tokens than the weight-streaming
+// kernels take (prompt portions, large decode batches).
 //
-//   * one CTA per 128 x BN output tile (BN = 128, or 64 for narrow outputs)
+//   * persistent CTAs, each walking output tiles of 128 x BN (BN = 256, 128 or 64, chosen from the number of
+//     tiles: see the launchers), with two accumulators of BN columns in tensor memory so that the epilogue of
+//     one tile runs under the products of the next
 //   * warp 0: one thread issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the A tile
-//     [128 rows x 64 k] and the B tile [BN rows x 64 k] into a STAGES-deep ring of shared memory, each
-//     load completing on the stage's "full" mbarrier
-//   * warp 1: allocates BN columns of tensor memory; one thread issues tcgen05.mma (kind::f16, M = 128,
+//     [128 rows x 64 k] and the B tile [BN rows x 64 k] into a STAGES-deep ring of shared memory (3 to 8
+//     stages), each load completing on the stage's "full" mbarrier
+//   * warp 1: allocates 2 * BN columns of tensor memory; one thread issues tcgen05.mma (kind::f16, M = 128,
 //     N = BN, K = 16, four per 64-wide k block) on shared-memory descriptors and commits each stage to its
-//     "empty" mbarrier, and the whole tile to the "accumulator ready" mbarrier
+//     "empty" mbarrier, and each finished tile to its "accumulator ready" mbarrier
 //   * warps 2..5: read the accumulator with tcgen05.ld (32 lanes x 32 columns per warp and step) and run the
-//     epilogue: PLAIN writes float rows of `out`; SWIGLU (the B tile is 64 gate rows and the 64 up rows of the
-//     same features) writes silu(gate) * up as bfloat16; ROPE (the tile is whole heads of the stacked q/k/v
-//     projection) rotates q and k heads and writes q rows and the k, v cache pages as bfloat16
+//     epilogue: PLAIN writes float rows of `out` (or adds them to it: the residual form); SWIGLU (the B tile is
+//     gate rows and the up rows of the same features) writes silu(gate) * up as bfloat16; ROPE (the tile is
+//     whole heads of the stacked q/k/v projection) rotates q and k heads and writes q rows and the k, v cache
+//     pages as bfloat16
 //
 // Rows and columns beyond M, N or K are zero-filled by TMA on the way in and skipped on the way out, so any
 // M and N work; K must be a multiple of 8 (16-byte rows for the tensor map).  Every wait on an mbarrier
@@ -282,7 +286,7 @@ int* g_error = nullptr;          // device flag, owned by the caller (see cisr_g
 
 template <int BN, int STAGES, int EPI>
 int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k, int tiles_n, cudaStream_t s) {
-    const CUtensorMap *map_a, *map_w;
+    CUtensorMap map_a, map_w;
     int status = cached_map(&map_a, a, m, k, BM);
     if (status) return status;
     if ((status = cached_map(&map_w, w, n, k, EPI == EPI_SWIGLU ? BN / 2 : BN))) return status;
@@ -305,7 +309,7 @@ int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k
     }
     const int tiles_m = (m + BM - 1) / BM, total = tiles_m * tiles_n;
     return launch_kernel(gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(total < slots ? total : slots), dim3(192), S::TOTAL, s, g_pdl,
-                         *map_a, *map_w, ep, m, n, k, tiles_m, tiles_n, g_error);
+                         map_a, map_w, ep, m, n, k, tiles_m, tiles_n, g_error);
 }
 
 // 128 x 256 tiles read a third less from L2 per flop than 128 x 128; worth it once there are enough of them to
@@ -341,6 +345,9 @@ CISR_EXPORT int cisr_gemm_tcgen05_init(int* error_flag) {
 }
 
 CISR_EXPORT void cisr_gemm_tcgen05_set_pdl(int on) { g_pdl = on != 0; }
+
+// How many tensor maps the library remembers before it empties its cache (tests lower it to force evictions).
+CISR_EXPORT void cisr_gemm_tcgen05_set_map_cache_limit(int entries) { g_map_cache_limit = entries < 1 ? 1 : (size_t)entries; }
 
 // Three pipeline stages keep a CTA near 100 KB of shared memory, so two CTAs share an SM and one's epilogue overlaps
 // the other's main loop.

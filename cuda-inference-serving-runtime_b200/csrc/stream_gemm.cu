@@ -395,7 +395,7 @@ int launch(StreamArgs& a, const void* w, cudaStream_t s) {
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const CUtensorMap* map_w;
+    CUtensorMap map_w;
     int status;
     if (EPI == EPI_PLAIN) {
         status = cached_map(&map_w, w, a.n, a.k, a.block_rows, 64);
@@ -423,11 +423,11 @@ int launch(StreamArgs& a, const void* w, cudaStream_t s) {
             }
             if (!status) it = maps.emplace(key, map).first;
         }
-        if (!status) map_w = &it->second;
+        if (!status) map_w = it->second;
     }
     if (status) return status;
     const int grid = a.n_blocks < sms ? a.n_blocks : sms;
-    return launch_kernel(stream_kernel<MT, EPI>, dim3(grid), dim3(THREADS), smem, s, g_pdl, *map_w, a, g_error);
+    return launch_kernel(stream_kernel<MT, EPI>, dim3(grid), dim3(THREADS), smem, s, g_pdl, map_w, a, g_error);
 }
 
 template <int MT>

@@ -113,18 +113,22 @@ struct MapKeyHash {
     }
 };
 std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;     // a map describes geometry only, so it stays right while the address does
+size_t g_map_cache_limit = 4096;                                // entries kept before the cache is emptied
 
-int cached_map(const CUtensorMap** out, const void* base, long long rows, int cols, int box_rows, int box_cols = 64) {
+// The tensor map for (base, shape, box), encoded once and then found again.  The map is COPIED into the caller's
+// storage: a launcher asks for several maps in a row, and a later call may empty the cache, so nothing may keep a
+// pointer into it.
+int cached_map(CUtensorMap* out, const void* base, long long rows, int cols, int box_rows, int box_cols = 64) {
     const MapKey key{base, rows, cols, box_rows, box_cols};
     auto it = g_maps.find(key);
     if (it == g_maps.end()) {
-        if (g_maps.size() > 4096) g_maps.clear();
+        if (g_maps.size() >= g_map_cache_limit) g_maps.clear();
         CUtensorMap map;
         const int status = make_map(&map, base, rows, cols, box_rows, box_cols);
         if (status) return status;
         it = g_maps.emplace(key, map).first;
     }
-    *out = &it->second;
+    *out = it->second;
     return 0;
 }
 }  // namespace

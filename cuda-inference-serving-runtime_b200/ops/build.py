@@ -13,6 +13,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -70,9 +71,29 @@ def _find_build_dir() -> Path:
     raise BuildError("no writable folder for built kernels: tried " + ", ".join(str(c) for c in candidates))
 
 
+_INCLUDE = re.compile(r'^[ \t]*#[ \t]*include[ \t]*"([^"]+)"', re.MULTILINE)
+
+
+def source_closure(source: Path) -> list:
+    """The source and every file under csrc/ it includes, directly or through another file (a .cu file may include
+    headers, a .h, or another .cu file), sorted by name."""
+    seen, todo = {}, [source]
+    while todo:
+        path = todo.pop()
+        if path.name in seen or not path.exists():
+            continue
+        seen[path.name] = path
+        for name in _INCLUDE.findall(path.read_text()):
+            todo.append(CSRC / name)
+    return [seen[name] for name in sorted(seen)]
+
+
 def _digest(source: Path, defines: Mapping[str, object], extra: Sequence[str]) -> str:
+    """Hash of everything a library is made from: its source, every file that source includes, the definitions
+    and the flags.  An edit to any of them gives the library another name, so a stale build is never loaded."""
     h = hashlib.sha256()
-    for path in [source] + sorted(CSRC.glob("*.cuh")):
+    h.update(source.name.encode())
+    for path in source_closure(source):
         h.update(path.name.encode())
         h.update(path.read_bytes())
     h.update(repr(sorted(defines.items())).encode())
