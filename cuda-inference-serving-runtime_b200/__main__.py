@@ -18,7 +18,7 @@ from pathlib import Path
 
 
 def build_parser() -> argparse.ArgumentParser:
-    from .config.llama import preset_names
+    from .config.presets import preset_names
 
     parser = argparse.ArgumentParser(prog="python -m cisr_b200", description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)

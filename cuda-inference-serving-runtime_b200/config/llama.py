@@ -5,16 +5,15 @@ Parity: runtime/model.py:11-35 (fields and checks) and runtime/checkpoint.py:12-
 """
 from __future__ import annotations
 
-import json
 from dataclasses import dataclass
-from pathlib import Path
 from typing import Any, Mapping, Optional, Tuple
 
+from .errors import ConfigError
+from .registry import register_architecture
 from .spec import LayerSpec, ModelSpec, PartSpec, RunEntry
 
-
-class ConfigError(ValueError):
-    """config.json asks for something this engine does not compute."""
+# Head sizes the attention kernels are built for (csrc/attention*.cu are specialised by HEAD_DIM in steps of 16).
+HEAD_DIM_STEP, HEAD_DIM_MAX = 16, 256
 
 
 @dataclass(frozen=True)
@@ -45,6 +44,11 @@ class LlamaConfig:
             raise ConfigError("num_attention_heads must be a multiple of num_key_value_heads")
         if self.head_dim % 2:
             raise ConfigError("rotary position encoding needs an even head_dim")
+        if self.head_dim % HEAD_DIM_STEP or self.head_dim > HEAD_DIM_MAX:
+            # the reference takes any even size up to 256 (runtime/model.py:31-32); the kernels here are specialised
+            # in steps of 16, and a size between the steps is refused before any weight is read
+            raise ConfigError(f"head_dim {self.head_dim} is not supported: the attention kernels take multiples of "
+                              f"{HEAD_DIM_STEP} up to {HEAD_DIM_MAX}")
         if not self.rms_norm_eps > 0 or not self.rope_theta > 0:
             raise ConfigError("rms_norm_eps and rope_theta must be positive")
 
@@ -129,20 +133,4 @@ class LlamaConfig:
         return spec
 
 
-PRESET_DIR = Path(__file__).resolve().parent / "presets"
-
-
-def preset_names() -> list:
-    return sorted(p.stem for p in PRESET_DIR.glob("*.json"))
-
-
-def preset_dict(name: str) -> dict:
-    """config.json dict of a named shape (files under config/presets/)."""
-    path = PRESET_DIR / f"{name}.json"
-    if not path.exists():
-        raise ConfigError(f"unknown preset {name!r}; known: {', '.join(preset_names())}")
-    return json.loads(path.read_text())
-
-
-def preset(name: str) -> LlamaConfig:
-    return LlamaConfig.from_dict(preset_dict(name))
+register_architecture("LlamaForCausalLM", LlamaConfig, model_types=("llama",))

@@ -1,16 +1,17 @@
 """One registry from an architecture's name (config.json `architectures[0]`) to its model.
 
-An entry gives the configuration class (with `from_dict(raw)` and `to_spec()`).
-The model itself is always assembled by `engine.model.build_model` from the spec,
-so adding an architecture means adding a configuration class that emits a spec,
-and any parts the spec names that are not registered yet.
+An entry gives the configuration class (with `from_dict(raw)`, `to_dict()` and `to_spec()`).
+The model itself is always assembled by `engine.model.Model` from the spec, so adding an
+architecture means adding a configuration class that emits a spec, and any parts the spec
+names that are not registered yet.  This module knows no architecture: each one registers
+itself where its configuration class is defined (config/llama.py does so for Llama).
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
 from typing import Any, Dict, Mapping
 
-from .llama import ConfigError, LlamaConfig
+from .errors import ConfigError
 
 
 @dataclass(frozen=True)
@@ -42,5 +43,3 @@ def architecture_for(raw: Mapping[str, Any]) -> Architecture:
     raise ConfigError(f"no registered architecture for architectures={list(names)!r}, model_type={model_type!r}; "
                       f"known: {', '.join(sorted(ARCHITECTURES))}")
 
-
-register_architecture("LlamaForCausalLM", LlamaConfig, model_types=("llama",))

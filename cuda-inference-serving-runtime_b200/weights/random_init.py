@@ -60,7 +60,7 @@ def write_random_model(directory, config, seed: int = 0, store_dtype: str = "bfl
     from safetensors.torch import save_file
 
     from ..config import architecture_for
-    from ..config.llama import preset_dict
+    from ..config.presets import preset_dict
     from ..engine.model import Model, resolve_dtype
 
     raw = preset_dict(config) if isinstance(config, str) else (dict(config) if isinstance(config, dict) else config.to_dict())

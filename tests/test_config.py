@@ -5,7 +5,7 @@ import pytest
 
 import tiny_models as tm
 from cisr_b200.config import ARCHITECTURES, ModelSpec, RunEntry, architecture_for, register_architecture
-from cisr_b200.config.llama import ConfigError, LlamaConfig, preset, preset_dict, preset_names
+from cisr_b200.config import ConfigError, LlamaConfig, preset, preset_dict, preset_names
 
 
 def test_every_field_comes_from_config_json():
