@@ -620,6 +620,9 @@ __device__ __forceinline__ void stamp(int i) {
 
 // cluster: CTAs per cluster along the key ranges (1: none).  n_parts = n_splits / cluster partial sums per query head
 // remain; with one, the first CTA writes the finished rows to `out`, otherwise partial sums for the merge kernel.
+// per_cta (only without clusters): consecutive key ranges one CTA walks, blockIdx.z * per_cta onwards.  Each range is
+// still summed on its own (a fresh running softmax, its own partial sum), so the result is the same to the last bit
+// however the ranges are dealt out to CTAs; a large batch gets fewer, longer CTAs that way.
 __global__ void __launch_bounds__(DEC_THREADS, 3)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_cache,
@@ -627,11 +630,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const int* __restrict__ block_table, int table_width, const int* __restrict__ dec_req,
                        const int* __restrict__ q_start, const int* __restrict__ ctx_len, float* __restrict__ partial,
                        float* __restrict__ stats, int hq, int hkv, int page_size, float scale, int window, int split_size,
-                       int cluster, int n_parts, int row0, int* __restrict__ error) {
+                       int cluster, int n_parts, int per_cta, int row0, int* __restrict__ error) {
     CISR_TRACE_SCOPE(TRACE_ATTN_DECODE_TMA);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024-byte aligned
-    float* merge = reinterpret_cast<float*>(ring);                   // reused after the loop: [4][16][D + 2]
+    float* merge = reinterpret_cast<float*>(ring);                   // reused after a range's loop: [4][16][D + 2]
     bf16* Qs = reinterpret_cast<bf16*>(ring + 4 * (size_t)TMA_TILE_BYTES);         // [16][LDS]
     uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * LDS);     // [4]: a warp's tile has landed
     int* failed = reinterpret_cast<int*>(full + 4);
@@ -642,48 +645,64 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int group = hq / hkv;
     const int rows = min(16, group - row0);
     int* pages = reinterpret_cast<int*>(gathered + (cluster > 1 ? (size_t)cluster * rows * ((D + cluster - 1) / cluster + 2) : 0));   // block table entries of the key range
-    const int slot = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int slot = blockIdx.x, kvh = blockIdx.y;
     const int req = dec_req[slot];
     const int tok = q_start[req];
     const int ctx = ctx_len[req];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int* table = block_table + (size_t)req_slot[req] * table_width;
-
-    int lo = split * split_size;                                     // a multiple of TK (checked by the launcher)
-    const int hi = min(lo + split_size, ctx);
-    if (window > 0) lo = max(lo, ctx - window);
     const size_t part_base = ((size_t)slot * hq + (size_t)kvh * group + row0) * n_parts;
-    const bool empty = lo >= hi;              // nothing in this range (the same for every thread)
+    unsigned char* stage = ring + (size_t)warp * TMA_TILE_BYTES;     // this warp's stage and its barrier
+    uint64_t* bar = full + warp;
+    const int box_rows = min(page_size, TK), boxes = TK / box_rows;
+    const float scale2 = scale * LOG2E;
+    const unsigned char* Ks = stage;
+    unsigned char* Vs = stage + NSUB * SUB_BYTES;
+
+    if (tid == 0) {
+        *failed = 0;
+        for (int w = 0; w < 4; ++w) mbar_init(full + w, 1);
+        mbar_init_fence();
+    }
+    float o[ND][4];
+    float m_run[2], l_run[2];
+    uint32_t qf[KD][4];
+    bool waited = false;          // on the kernel before this one (once per CTA)
+    bool have_q = false;          // the query fragments are in registers (once per CTA)
+    unsigned uses = 0;            // tiles this warp has received so far: the parity of its barrier
+    bool empty = true;
+    int split = blockIdx.z * per_cta, lo = 0, hi = 0;
+
+    for (int walked = 0; walked < per_cta && split < n_parts * cluster; ++walked, ++split) {
+    lo = split * split_size;                                         // a multiple of TK (checked by the launcher)
+    hi = min(lo + split_size, ctx);
+    if (window > 0) lo = max(lo, ctx - window);
+    empty = lo >= hi;                         // nothing in this range (the same for every thread)
     if (empty && cluster == 1) {              // the merge skips a zero denominator
-        pdl_wait();
+        if (!waited) { pdl_wait(); waited = true; }
         for (int g = tid; g < rows; g += DEC_THREADS) {
             const size_t p = part_base + (size_t)g * n_parts + split;
             stats[2 * p] = -INFINITY; stats[2 * p + 1] = 0.f;
         }
-        return;
+        continue;
     }
-    float o[ND][4];
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
 #pragma unroll
     for (int i = 0; i < ND; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-    if (tid == 0) *failed = 0;
 
     if (!empty) {
     const int base = lo & ~(TK - 1);          // tiles start on multiples of TK keys, so a tile is whole pages (or part of one)
     const int n_tiles = (hi - base + TK - 1) / TK;
     const int first_page = base / page_size;
-    for (int i = tid; i <= (hi - 1) / page_size - first_page; i += DEC_THREADS) pages[i] = table[first_page + i];
-    if (tid == 0) {
-        for (int w = 0; w < 4; ++w) mbar_init(full + w, 1);
-        mbar_init_fence();
-    }
+    // the range before is written out: its page list and the merge area (ordinary stores into what tensor-map copies
+    // fill next) are free once every thread is here
+    if (walked) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
+    for (int i = tid; i <= (hi - 1) / page_size - first_page; i += DEC_THREADS) pages[i] = table[first_page + i];
+    __syncthreads();                          // (also: the barriers are initialised)
     STAMP(1);
 
     // Tile t into this warp's stage: lane b fetches box b (K or V, 64-column half, run of box_rows keys).
-    unsigned char* stage = ring + (size_t)warp * TMA_TILE_BYTES;
-    uint64_t* bar = full + warp;
-    const int box_rows = min(page_size, TK), boxes = TK / box_rows;
     auto fetch = [&](int t) {
         if (lane == 0) mbar_expect_tx(bar, (uint32_t)TMA_TILE_BYTES);
         __syncwarp();
@@ -701,9 +720,21 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int newest = hi == ctx ? n_tiles - 1 : -1;
     if (warp < n_tiles) fetch(warp);
     STAMP(2);
-    pdl_wait();
-    CISR_TRACE_WAITED();
+    if (!waited) {
+        pdl_wait();
+        CISR_TRACE_WAITED();
+        waited = true;
+    }
     STAMP(3);
+    const bool load_q = !have_q;
+    if (load_q) {
+        for (int c = tid; c < 16 * CHUNKS; c += DEC_THREADS) {
+            const int r = c / CHUNKS, ch = c - r * CHUNKS;
+            const bool ok = r < rows;
+            cp_async16(Qs + r * LDS + ch * 8, q + ((size_t)tok * hq + kvh * group + row0 + (ok ? r : 0)) * D + ch * 8, ok);
+        }
+        cp_async_commit();
+    }
     uint4 newest_k = make_uint4(0, 0, 0, 0), newest_v = newest_k;
     if (warp == newest && lane < NSUB * 8) {
         const int pos = ctx - 1, page = pages[pos / page_size - first_page];
@@ -713,30 +744,25 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             newest_v = __ldcg(reinterpret_cast<const uint4*>(v_cache + at));
         }
     }
-    for (int c = tid; c < 16 * CHUNKS; c += DEC_THREADS) {
-        const int r = c / CHUNKS, ch = c - r * CHUNKS;
-        const bool ok = r < rows;
-        cp_async16(Qs + r * LDS + ch * 8, q + ((size_t)tok * hq + kvh * group + row0 + (ok ? r : 0)) * D + ch * 8, ok);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();                                                 // the query rows are in shared memory
-    STAMP(4);
-
-    uint32_t qf[KD][4];
+    if (load_q) {
+        cp_async_wait<0>();
+        __syncthreads();                                             // the query rows are in shared memory
+        STAMP(4);
 #pragma unroll
-    for (int kk = 0; kk < KD; ++kk)
-        ldmatrix_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
-    const float scale2 = scale * LOG2E;
-    const unsigned char* Ks = stage;
-    unsigned char* Vs = stage + NSUB * SUB_BYTES;
+        for (int kk = 0; kk < KD; ++kk)
+            ldmatrix_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
+        have_q = true;
+    }
 
+    bool lost = false;
     for (int t = warp, it = 0; t < n_tiles; t += 4, ++it) {
-        if (!__all_sync(0xffffffffu, mbar_wait(bar, it & 1))) {      // the lanes agree on whether the wait ran out
+        if (!__all_sync(0xffffffffu, mbar_wait(bar, uses & 1))) {    // the lanes agree on whether the wait ran out
             if (lane == 0) { atomicExch(error, 3); *failed = 1; }
-            mbar_wait(bar, it & 1);      // one more bounded chance for the copy to land before the stage is given up
+            mbar_wait(bar, uses & 1);    // one more bounded chance for the copy to land before the stage is given up
+            lost = true;
             break;
         }
+        ++uses;
         if (it == 0) STAMP(5);
         const int k0 = base + t * TK;
         if (it == 0 && t == newest) {             // the newest key's row over the stale one the early copy brought
@@ -823,8 +849,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         __syncwarp();                                                // every lane has read the stage
         if (t + 4 < n_tiles) fetch(t + 4);
     }
-    } else {
+    (void)lost;
+    } else if (!waited) {
         pdl_wait();
+        waited = true;
     }
     __syncthreads();          // every warp is done with its stage: the stages become the merge area
     STAMP(6);
@@ -832,8 +860,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (*failed) return;  // a copy never arrived; the host reads the error flag
         decode_finish(merge, o, m_run, l_run, partial, stats, part_base, rows, n_parts, split, tid);
         STAMP(7);
-        return;
+        continue;
     }
+    break;                    // with clusters a CTA has one range: the exchange below
+    }
+    if (cluster == 1) return;
 
     // All-to-all over the cluster: CTA r finishes output columns [r * cols, (r + 1) * cols) of every query row, so each
     // CTA sends every other CTA that slice of its rows (and the rows' max and denominator).  A CTA without keys, or
@@ -1006,7 +1037,7 @@ CISR_EXPORT int cisr_attn_decode_tma_ok(int page_size, int split_size) {
 }
 
 #if HEAD_DIM % 64 == 0
-namespace { int* g_error = nullptr; bool g_clusters = false; int g_last_launches = 0; }
+namespace { int* g_error = nullptr; bool g_clusters = false; int g_last_launches = 0; int g_ranges_per_cta = 0; }
 
 // `error_flag`: one zeroed int in device memory that a kernel sets when a wait on a copy ran out.
 CISR_EXPORT int cisr_attn_tma_init(int* error_flag) {
@@ -1029,7 +1060,7 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
     const long long cache_rows = (long long)n_pages * hkv * page_size;
     if (cache_rows <= 0 || cache_rows >= (1ll << 31) || (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15)) return -2;
     const int box_rows = page_size < TK ? page_size : TK;
-    const CUtensorMap *map_k, *map_v;
+    CUtensorMap map_k, map_v;
     int status = cached_map(&map_k, k_cache, cache_rows, D, box_rows, 64);
     if (status) return status;
     if ((status = cached_map(&map_v, v_cache, cache_rows, D, box_rows, 64))) return status;
@@ -1071,14 +1102,24 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
         break;
     }
     const int n_parts = n_splits / cluster;
+    // Without clusters a CTA may walk several consecutive ranges (each still summed on its own, so the result does not
+    // change): as many as it takes to bring the grid down to about three CTAs per SM, in powers of two.
+    int per_cta = 1;
+    if (cluster == 1) {
+        static int sms = 0;
+        if (!sms) { int device = 0; cudaGetDevice(&device); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device); }
+        if (g_ranges_per_cta > 0) per_cta = g_ranges_per_cta;
+        else while (per_cta < n_splits && (long long)n_dec * hkv * ((n_splits + per_cta - 1) / per_cta) > 3ll * sms) per_cta *= 2;
+        if (per_cta > n_splits) per_cta = n_splits;
+    }
     cudaStream_t s = (cudaStream_t)stream;
     g_last_launches = (group + 15) / 16 + ((n_parts == 1 && cluster > 1) ? 0 : 1);
     for (int row0 = 0; row0 < group; row0 += 16) {
-        status = launch_kernel_cluster(attn_decode_tma_kernel, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), smem, s, g_pdl, cluster,
-                                       *map_k, *map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
+        status = launch_kernel_cluster(attn_decode_tma_kernel, dim3(n_dec, hkv, (n_splits + per_cta - 1) / per_cta), dim3(DEC_THREADS), smem, s,
+                                       g_pdl, cluster, map_k, map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                        (int)cache_rows, req_slot, block_table, table_width,
                                        dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale, window, split_size,
-                                       cluster, n_parts, row0, g_error);
+                                       cluster, n_parts, per_cta, row0, g_error);
         if (status) return status;
     }
     if (n_parts == 1 && cluster > 1) return 0;
@@ -1092,6 +1133,10 @@ CISR_EXPORT int cisr_attn_trace_read(void* host, int bytes) { return (int)cudaMe
 
 // Kernels launched by the last cisr_attn_decode_tma call (the merge kernel is left out when one cluster covers all ranges).
 CISR_EXPORT int cisr_attn_decode_tma_launches() { return g_last_launches; }
+
+// Key ranges one CTA walks when no clusters are used: 0 lets the launcher choose (about three CTAs per SM), n > 0 fixes
+// it (tests compare 1, 2 and more: the output must be the same to the last bit).
+CISR_EXPORT void cisr_attn_set_ranges_per_cta(int n) { g_ranges_per_cta = n < 0 ? 0 : n; }
 
 // 0 turns the clusters off (every key range then writes its partial sum and the merge kernel runs).
 CISR_EXPORT void cisr_attn_set_clusters(int on) { g_clusters = on != 0; }

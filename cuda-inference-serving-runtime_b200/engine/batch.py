@@ -17,12 +17,6 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..ops import kernels
-
-CTA_TARGET = 444           # three CTAs per SM on a 148-SM part: what the decode split aims to fill
-SPLIT_QUANTUM = 64         # key ranges of the split are multiples of this
-SPLIT_MIN = 256            # a CTA's four warps each take tiles of up to 64 keys: a shorter range leaves warps idle
-CLUSTER_MAX = 16           # key ranges of one request and head that one thread-block cluster can merge
 
 
 @dataclass
@@ -42,10 +36,40 @@ class HostBatch:
     ctx_len: List[int]                # length of each request after this step
     n_tokens: int
     logit_rows: List[int]
+    # When set: a bound on the ctx_len of every request that brings a single token, which also holds for later steps
+    # run with this step's launch plans (a captured graph is replayed with other lengths, up to its context bucket).
+    # None or 0: the plans serve this step alone and may use the lengths themselves.
+    ctx_bound: Optional[int] = None
+
+
+@dataclass
+class StepPlan:
+    """What a part derives on the host from a step's shape before the step runs: int32 lists its kernels read on the
+    device (tile lists and the like) and plain numbers for its launches (grid sizes).  A plan may depend on the
+    portion lengths `q_len` and their order, and on the lengths of single-token requests only through an upper bound
+    (`ctx_bound` when set, else their largest `ctx_len`); never on token values or on the lengths of longer portions,
+    so that steps of the same shape share it and a captured step stays right when replayed."""
+    arrays: Dict[str, np.ndarray] = field(default_factory=dict)
+    info: Dict[str, int] = field(default_factory=dict)
+
+
+class PlanViews:
+    """A `StepPlan` once its lists are on the device: `views[name]` are int32 device tensors, `info` the numbers."""
+
+    def __init__(self, views: Dict[str, torch.Tensor], info: Dict[str, int]):
+        self.views, self.info = views, info
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        return self.views[name]
 
 
 class StepContext:
-    """Device-side view of one step, handed to every part."""
+    """Device-side view of one step, handed to every part.
+
+    It holds only what every mixer needs: the tokens, their positions and requests, per request its slot, first row,
+    portion length and length after the step, and the rows whose logits are wanted.  Launch plans of single parts
+    (`plan_for`) and values parts share within a step (`shared`: rotary tables) hang beside it under the parts' keys.
+    """
 
     def __init__(self, device, host: HostBatch):
         self.device = device
@@ -53,36 +77,33 @@ class StepContext:
         self.n_tokens = host.n_tokens
         self.n_requests = len(host.keys)
         self.shared: Dict[object, object] = {}   # values parts share within a step (rotary tables, ...)
+        self.plans: Dict[object, PlanViews] = {}  # launch plans by the parts' plan keys
         self.token_ids = self.positions = self.token_req = None
         self.req_slot = self.q_start = self.q_len = self.ctx_len = None
-        self.tile_req = self.tile_q0 = self.dec_req = None
-        self.wide_req = self.wide_q0 = None      # the same portions cut into tiles of kernels.WIDE_TILE queries
-        self.n_tiles = self.n_wide = self.n_decode = 0
         self.logit_rows = None
-        self.max_decode_ctx = 0
-        self.fixed_splits: Optional[Tuple[int, int]] = None
 
-    def decode_splits(self, kv_heads: int) -> Tuple[int, int]:
-        """(keys per range, number of ranges) for the split decode attention of this step.
+    def plan_for(self, part) -> PlanViews:
+        """The launch plan of `part` for this step.  The engine packs the plans of a model's parts into the step's one
+        metadata copy; a part run outside that (a test of one part) gets its plan made and sent here."""
+        key = part.plan_key()
+        views = self.plans.get(key)
+        if views is None:
+            plan = part.step_plan(self.host)
+            views = PlanViews({name: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(self.device)
+                               for name, a in plan.arrays.items()}, dict(plan.info))
+            self.plans[key] = views
+        return views
 
-        Ranges start at multiples of the range size in absolute positions, so which keys
-        fall together does not depend on the batch; the range size is chosen to give the
-        device about three CTAs per SM, and up to 16 ranges are merged inside one thread-block cluster.
-        """
-        if self.fixed_splits is not None:
-            return self.fixed_splits
-        return plan_decode_splits(self.n_decode, kv_heads, self.max_decode_ctx)
 
-
-def plan_decode_splits(n_decode: int, kv_heads: int, max_ctx: int) -> Tuple[int, int]:
-    ctas = max(1, n_decode * kv_heads)
-    wanted = max(1, CTA_TARGET // ctas)          # rounded down: one wave of CTAs, not a wave and a bit
-    size = -(-max(1, max_ctx) // wanted)
-    size = max(SPLIT_MIN, -(-size // SPLIT_QUANTUM) * SPLIT_QUANTUM)
-    n_splits = max(1, -(-max_ctx // size))
-    if n_splits > CLUSTER_MAX:       # whole clusters: the ranges beyond the context are empty
-        n_splits = -(-n_splits // CLUSTER_MAX) * CLUSTER_MAX
-    return size, n_splits
+def unique_planners(parts) -> list:
+    """The parts that make launch plans, one per plan key (thirty attention layers of one geometry share one plan)."""
+    seen, out = set(), []
+    for part in parts:
+        key = part.plan_key() if hasattr(part, "plan_key") else None
+        if key is not None and key not in seen:
+            seen.add(key)
+            out.append(part)
+    return out
 
 
 class PinnedRing:
@@ -119,46 +140,46 @@ class StaticMeta:
     same shape always has the same layout; the caller applies what does not fit before packing.
     """
 
-    def __init__(self, device, ints: int, update_capacity: int, max_decode_ctx: int):
+    def __init__(self, device, ints: int, update_capacity: int, ctx_bound: int):
         self.pinned = torch.zeros(ints, dtype=torch.int32, pin_memory=True)
         self.dev = torch.zeros(ints, dtype=torch.int32, device=device)
         self.update_capacity = update_capacity
-        self.max_decode_ctx = max_decode_ctx        # an upper bound (the bucket), so the decode split plan is fixed
+        self.ctx_bound = ctx_bound                  # the context bucket: launch plans made for it stay right at replay
+        self.sent: Optional[torch.cuda.Event] = None   # the last copy out of `pinned`
+
+    def wait_until_sent(self) -> None:
+        """The pinned buffer is about to be rewritten: the copy of the step before must have left it."""
+        if self.sent is not None:
+            self.sent.synchronize()
+
+    def mark_sent(self) -> None:
+        if self.sent is None:
+            self.sent = torch.cuda.Event()
+        self.sent.record()
 
 
 def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarray, positions: np.ndarray,
                   token_req: np.ndarray, table_updates: Sequence[Tuple[np.ndarray, np.ndarray]],
-                  extra: Optional[Dict[str, np.ndarray]] = None, static: Optional[StaticMeta] = None):
+                  extra: Optional[Dict[str, np.ndarray]] = None, static: Optional[StaticMeta] = None,
+                  planners: Sequence = ()):
     """Pack the step's metadata, send it in one copy, and return (context, update views, extra views).
 
+    `planners`: parts whose launch plans (`part.step_plan(host)`) travel in the same copy.
     With `static`, the metadata goes into that shape's fixed buffers instead of fresh ones."""
-    q_len = np.asarray(host.q_len, dtype=np.int32)
-    tile = kernels.PREFILL_TILE
-    tile_req: List[int] = []
-    tile_q0: List[int] = []
-    wide_req: List[int] = []
-    wide_q0: List[int] = []
-    dec_req: List[int] = []
-    max_decode_ctx = 0
-    for r, n in enumerate(host.q_len):
-        if n == 1:
-            dec_req.append(r)
-            max_decode_ctx = max(max_decode_ctx, host.ctx_len[r])
-        else:
-            for q0 in reversed(range(0, n, tile)):     # a portion's last tile has the longest key loop: launch it first
-                tile_req.append(r)
-                tile_q0.append(q0)
-            for q0 in reversed(range(0, n, kernels.WIDE_TILE)):
-                wide_req.append(r)
-                wide_q0.append(q0)
+    if static is not None:
+        host.ctx_bound = static.ctx_bound
     segments: List[Tuple[str, np.ndarray]] = [
         ("token_ids", token_ids), ("positions", positions), ("token_req", token_req),
         ("req_slot", np.asarray(host.slots, dtype=np.int32)), ("q_start", np.asarray(host.q_start, dtype=np.int32)),
-        ("q_len", q_len), ("ctx_len", np.asarray(host.ctx_len, dtype=np.int32)),
-        ("tile_req", np.asarray(tile_req, dtype=np.int32)), ("tile_q0", np.asarray(tile_q0, dtype=np.int32)),
-        ("wide_req", np.asarray(wide_req, dtype=np.int32)), ("wide_q0", np.asarray(wide_q0, dtype=np.int32)),
-        ("dec_req", np.asarray(dec_req, dtype=np.int32)), ("logit_rows", np.asarray(host.logit_rows, dtype=np.int32)),
+        ("q_len", np.asarray(host.q_len, dtype=np.int32)), ("ctx_len", np.asarray(host.ctx_len, dtype=np.int32)),
+        ("logit_rows", np.asarray(host.logit_rows, dtype=np.int32)),
     ]
+    plans = []
+    for i, part in enumerate(planners):
+        plan = part.step_plan(host)
+        plans.append((part.plan_key(), i, plan))
+        for name, arr in plan.arrays.items():
+            segments.append((f"plan{i}.{name}", np.ascontiguousarray(arr, dtype=np.int32).reshape(-1)))
     for g, (idx, val) in enumerate(table_updates):
         if static is not None:
             padded_idx = np.full(static.update_capacity, -1, dtype=np.int32)
@@ -179,6 +200,7 @@ def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarr
     if static is not None:
         if total > static.pinned.numel():
             raise ValueError("the step's metadata does not fit the buffers of its shape")
+        static.wait_until_sent()
         pinned, dev = static.pinned, static.dev
     else:
         pinned, ring_index = ring.take(total)
@@ -190,6 +212,8 @@ def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarr
     dev[:total].copy_(pinned[:total], non_blocking=True)
     if static is None:
         ring.sent(ring_index)
+    else:
+        static.mark_sent()
 
     def view(name: str) -> torch.Tensor:
         start, size = offsets[name]
@@ -198,11 +222,9 @@ def build_context(device, ring: PinnedRing, host: HostBatch, token_ids: np.ndarr
     ctx = StepContext(device, host)
     ctx.token_ids, ctx.positions, ctx.token_req = view("token_ids"), view("positions"), view("token_req")
     ctx.req_slot, ctx.q_start, ctx.q_len, ctx.ctx_len = view("req_slot"), view("q_start"), view("q_len"), view("ctx_len")
-    ctx.tile_req, ctx.tile_q0, ctx.dec_req = view("tile_req"), view("tile_q0"), view("dec_req")
-    ctx.wide_req, ctx.wide_q0 = view("wide_req"), view("wide_q0")
-    ctx.n_tiles, ctx.n_wide, ctx.n_decode = len(tile_req), len(wide_req), len(dec_req)
     ctx.logit_rows = view("logit_rows")
-    ctx.max_decode_ctx = max_decode_ctx if static is None else max(static.max_decode_ctx, max_decode_ctx)
+    for key, i, plan in plans:
+        ctx.plans[key] = PlanViews({name: view(f"plan{i}.{name}") for name in plan.arrays}, dict(plan.info))
     updates = [(view(f"upd_idx{g}"), view(f"upd_val{g}")) for g in range(len(table_updates))]
     extras = {name: view(name) for name in (extra or {})}
     return ctx, updates, extras

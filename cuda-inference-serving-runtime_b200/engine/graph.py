@@ -28,7 +28,7 @@ import torch
 
 from ..ops import kernels
 from ..sampling import sample_tokens
-from .batch import HostBatch, StepContext, StepEntry
+from .batch import HostBatch, PlanViews, StepContext, StepEntry
 
 MIN_CONTEXT_BUCKET = 256
 RING_SLOTS = 4
@@ -78,11 +78,19 @@ class DecodeGraph:
         cache = stepper.cache
         device = stepper.model.device
         self.n_updates = 2 * rows
-        names = ["token_ids", "positions", "token_req", "req_slot", "q_start", "q_len", "ctx_len", "dec_req", "logit_rows",
+        names = ["token_ids", "positions", "token_req", "req_slot", "q_start", "q_len", "ctx_len", "logit_rows",
                  "temperature", "counter", "live"]
         sizes = {n: rows for n in names}
         sizes["seed"] = 2 * rows
         names.append("seed")
+        # the parts' launch plans for `rows` single tokens with contexts up to the bucket: fixed for the graph's life
+        self.plan_host = HostBatch([None] * rows, [cache.null_slot] * rows, list(range(rows)), [1] * rows, [ctx_bucket] * rows,
+                                   rows, list(range(rows)), ctx_bound=ctx_bucket)
+        self.plans = [(part.plan_key(), i, part.step_plan(self.plan_host)) for i, part in enumerate(stepper.planners)]
+        for _, i, plan in self.plans:
+            for name, arr in plan.arrays.items():
+                sizes[f"plan{i}.{name}"] = max(1, int(np.asarray(arr).size))
+                names.append(f"plan{i}.{name}")
         for g in cache.page_groups:
             for kind in ("upd_idx", "upd_val"):
                 sizes[f"{kind}{g.index}"] = self.n_updates
@@ -96,9 +104,12 @@ class DecodeGraph:
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)
         arange = np.arange(rows, dtype=np.int32)
-        for n in ("token_req", "q_start", "dec_req", "logit_rows"):
+        for n in ("token_req", "q_start", "logit_rows"):
             self.h(n)[:] = arange
         self.h("q_len")[:] = 1
+        for _, i, plan in self.plans:
+            for name, arr in plan.arrays.items():
+                self.h(f"plan{i}.{name}")[:np.asarray(arr).size] = np.asarray(arr, dtype=np.int32).reshape(-1)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.tokens = torch.zeros(rows, dtype=torch.int32, device=device)
@@ -111,7 +122,9 @@ class DecodeGraph:
         # written while the copy of the step before may still be on its way
         self.upd_start = min((self.offsets[f"upd_idx{g.index}"][0] for g in cache.page_groups), default=total)
         self.upd_host = [torch.full((total - self.upd_start,), -1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.upd_sent: List[Optional[torch.cuda.Event]] = [None, None]
         self.upd_turn = 0
+        self.sent: Optional[torch.cuda.Event] = None      # the last copy out of `host`
         self.replays = 0
         self.launches = {"own": 0, "library": 0}
 
@@ -127,6 +140,8 @@ class DecodeGraph:
         """Write one step's contents into the pinned buffer (rows beyond the live ones become padding)."""
         n, rows = len(slots), self.rows
         null = self.stepper.cache.null_slot
+        if self.sent is not None:
+            self.sent.synchronize()      # the copy of the step before must have left the pinned buffer
         self.h("token_ids")[:n] = tokens; self.h("token_ids")[n:] = 0
         self.h("positions")[:n] = positions; self.h("positions")[n:] = 0
         self.h("req_slot")[:n] = slots; self.h("req_slot")[n:] = null
@@ -143,6 +158,9 @@ class DecodeGraph:
 
     def upload(self) -> None:
         self.dev.copy_(self.host, non_blocking=True)
+        if self.sent is None:
+            self.sent = torch.cuda.Event()
+        self.sent.record()
 
     def upload_updates(self, updates) -> None:
         """Send this step's block-table update lists (the rest of the buffer holds what the device fed back to itself)."""
@@ -150,6 +168,8 @@ class DecodeGraph:
             return
         self.upd_turn ^= 1
         staging = self.upd_host[self.upd_turn]
+        if self.upd_sent[self.upd_turn] is not None:
+            self.upd_sent[self.upd_turn].synchronize()     # two copies ago: long done unless the host ran far ahead
         flat = staging.numpy()
         for g, (idx, val) in zip(self.stepper.cache.page_groups, updates):
             a, size = self.offsets[f"upd_idx{g.index}"]
@@ -158,21 +178,22 @@ class DecodeGraph:
             flat[a - self.upd_start:a - self.upd_start + idx.size] = idx
             flat[b - self.upd_start:b - self.upd_start + idx.size] = val
         self.dev[self.upd_start:].copy_(staging, non_blocking=True)
+        if self.upd_sent[self.upd_turn] is None:
+            self.upd_sent[self.upd_turn] = torch.cuda.Event()
+        self.upd_sent[self.upd_turn].record()
 
     def _run(self, advance: bool) -> None:
         stepper = self.stepper
         cache, model = stepper.cache, stepper.model
         for g in cache.page_groups:
             kernels.table_update(g.device_table, self.d(f"upd_idx{g.index}"), self.d(f"upd_val{g.index}"))
-        host = HostBatch([None] * self.rows, [cache.null_slot] * self.rows, list(range(self.rows)), [1] * self.rows,
-                         [0] * self.rows, self.rows, list(range(self.rows)))
-        ctx = StepContext(model.device, host)
+        ctx = StepContext(model.device, self.plan_host)
         ctx.token_ids, ctx.positions, ctx.token_req = self.d("token_ids"), self.d("positions"), self.d("token_req")
         ctx.req_slot, ctx.q_start, ctx.q_len, ctx.ctx_len = self.d("req_slot"), self.d("q_start"), self.d("q_len"), self.d("ctx_len")
-        ctx.tile_req = ctx.tile_q0 = ctx.wide_req = ctx.wide_q0 = self.d("dec_req")[:0]
-        ctx.dec_req, ctx.n_tiles, ctx.n_decode = self.d("dec_req"), 0, self.rows
         ctx.logit_rows = self.d("logit_rows")
-        ctx.max_decode_ctx = self.ctx_bucket
+        for key, i, plan in self.plans:
+            ctx.plans[key] = PlanViews({name: self.d(f"plan{i}.{name}")[:np.asarray(arr).size] for name, arr in plan.arrays.items()},
+                                       dict(plan.info))
         self.logits = model.forward(ctx, cache)
         sample_tokens(self.logits, self.d("temperature").view(torch.float32), self.d("seed").view(torch.int64),
                       self.d("counter"), out=self.tokens)
@@ -218,7 +239,12 @@ class ShapeGraph:
         tokens = sum(q_lens)
         self.stepper = stepper
         capacity = tokens // max(1, cache.page_size) + 2 * len(q_lens) + 8
-        ints = 4 * tokens + 8 * len(q_lens) + 4 * (tokens // 64 + len(q_lens) + 4) + n_rows * 8 + 2 * capacity * max(1, len(cache.page_groups)) + 256
+        # room for the parts' launch plans: their sizes depend on the shape only, so one trial run measures them
+        starts = [sum(q_lens[:i]) for i in range(len(q_lens))]
+        trial = HostBatch([None] * len(q_lens), [0] * len(q_lens), starts, list(q_lens), [max(ctx_bucket, n) for n in q_lens], tokens,
+                          [], ctx_bound=ctx_bucket)
+        plan_ints = sum(_align(int(np.asarray(a).size)) for part in stepper.planners for a in part.step_plan(trial).arrays.values())
+        ints = 4 * tokens + 8 * len(q_lens) + plan_ints + n_rows * 8 + 2 * capacity * max(1, len(cache.page_groups)) + 256
         self.static = StaticMeta(stepper.model.device, ints, capacity, ctx_bucket)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None

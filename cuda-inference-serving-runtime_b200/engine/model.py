@@ -89,6 +89,12 @@ class Model:
         jobs.append(("sampling.cu", {}, ()))
         return jobs
 
+    def planners(self) -> list:
+        """The parts whose launch plans travel with every step's metadata, one per plan key."""
+        from .batch import unique_planners
+
+        return unique_planners(part for _, part in self._named_parts())
+
     def compile_kernels(self) -> None:
         """Build, in parallel, exactly the kernel libraries this model launches."""
         kernel_build.compile_many(self.kernel_jobs())
@@ -143,7 +149,7 @@ class Model:
 
         `config` is a preset name, a config.json dict, or a configuration object.
         """
-        from ..config.llama import preset_dict
+        from ..config.presets import preset_dict
         from ..weights import random_tensors
 
         raw = preset_dict(config) if isinstance(config, str) else (config if isinstance(config, dict) else config.to_dict())

@@ -35,6 +35,7 @@ from .batch import StepEntry
 
 POLICIES = ("serial", "chunked", "decode_first")
 RESERVE_MODES = ("full", "lazy")
+ENDED = ("finished", "cancelled")
 
 
 @dataclass
@@ -57,6 +58,10 @@ class Request:
 
     def tokens(self) -> list:
         return self.prompt + self.generated
+
+    def life_tokens(self) -> int:
+        """Tokens the request holds in the cache at most: its prompt and all it generates but the last token."""
+        return len(self.prompt) + max(0, self.max_new_tokens - 1)
 
     def eos_ids(self) -> tuple:
         if self.eos_token_id is None:
@@ -113,89 +118,107 @@ class Engine:
     def _page_size(self) -> int:
         return self.stepper.cache.page_size
 
+    def _pools(self):
+        return [g.pool for g in self.stepper.cache.page_groups]
+
     def _pool_pages(self) -> int:
-        groups = self.stepper.cache.page_groups
-        return min(g.pool.n_pages for g in groups) if groups else 1 << 30
+        return min((pool.n_pages for pool in self._pools()), default=1 << 30)
 
     def _free_pages(self) -> int:
-        groups = self.stepper.cache.page_groups
-        return min(g.pool.n_free for g in groups) if groups else 1 << 30
+        return min((pool.n_free for pool in self._pools()), default=1 << 30)
 
     def _resident_pages(self) -> int:
-        groups = self.stepper.cache.page_groups
-        return max(g.pool.n_used for g in groups) if groups else 0
+        return max((pool.n_used for pool in self._pools()), default=0)
+
+    def _pages_for(self, tokens: int) -> int:
+        return math.ceil(tokens / self._page_size)
 
     def _life_pages(self, r: Request) -> int:
-        # the last token chosen is never fed back, so it needs no place in the cache
-        return math.ceil((len(r.prompt) + max(0, r.max_new_tokens - 1)) / self._page_size)
+        """Pages of a request's whole life.  The last token chosen is never fed back, so it needs no place in the cache
+        (runtime/engine.py:46-47)."""
+        return self._pages_for(r.life_tokens())
 
     # ---------------------------------------------------------------- requests
-    def submit(self, request: Request) -> None:
-        r = request
+    def _problems(self, r: Request) -> List[str]:
+        """Everything that is wrong with a request, all at once (the checks of runtime/engine.py:40-48, one more for
+        the temperature)."""
+        found = []
         if r.key in self.requests:
-            raise ValueError("duplicate request ID")
+            found.append(f"duplicate request ID {r.key!r}")
         if not r.prompt or r.max_new_tokens < 0 or r.arrival_s < 0:
-            raise ValueError("invalid request")
+            found.append("invalid request (it needs a prompt, max_new_tokens >= 0 and arrival_s >= 0)")
         if r.status != "waiting" or r.cursor or r.generated:
-            raise ValueError("request already used")
-        if any(t < 0 or t >= self.vocab_size for t in r.prompt):
-            raise ValueError("invalid prompt token")
+            found.append("request already used")
+        bad = [t for t in r.prompt if not 0 <= t < self.vocab_size]
+        if bad:
+            found.append(f"invalid prompt token {bad[0]} (vocabulary of {self.vocab_size})")
         if r.temperature < 0:
-            raise ValueError("temperature must not be negative")
-        if len(r.prompt) + max(0, r.max_new_tokens - 1) > self.max_positions:
-            raise ValueError("request exceeds context limit")
-        if self._life_pages(r) > self._pool_pages():
-            raise ValueError("request cannot fit in page pool")
-        r.submitted_at = self.start + r.arrival_s
-        self.requests[r.key] = r
-        self.waiting.append(r)
+            found.append("temperature must not be negative")
+        if r.life_tokens() > self.max_positions:
+            found.append(f"request exceeds context limit of {self.max_positions}")
+        elif self._life_pages(r) > self._pool_pages():
+            found.append(f"request cannot fit in page pool ({self._life_pages(r)} pages wanted, {self._pool_pages()} exist)")
+        return found
 
-    def _finish(self, r: Request, status: str = "finished") -> None:
-        if r in self.active:
-            self.stepper.release(r.key)   # pages go back at once; later steps follow on the same stream
-            self.reserved.pop(r.key, None)
+    def submit(self, request: Request) -> None:
+        problems = self._problems(request)
+        if problems:
+            raise ValueError("; ".join(problems))
+        request.submitted_at = self.start + request.arrival_s
+        self.requests[request.key] = request
+        self.waiting.append(request)
+
+    def _retire(self, r: Request, status: str) -> None:
+        """The request is over.  Its pages go back at once: later steps follow on the same stream, behind any step of
+        its own that is still in flight (the reference synchronises the device first, runtime/model.py:78-80)."""
+        if r.key in self.reserved:
+            self.stepper.release(r.key)
+            del self.reserved[r.key]
             self.active.remove(r)
         r.status = status
         r.finished_at = time.perf_counter()
 
+    def _finish(self, r: Request) -> None:
+        self._retire(r, "finished")
+
     def cancel(self, key) -> None:
+        """Stop a request wherever it is: in the queue, running, or with a step of its own still in flight (whose token
+        is then dropped when it is read)."""
         r = self.requests[key]
-        if r.status in ("finished", "cancelled"):
+        if r.status in ENDED:
             return
-        if r in self.waiting:
+        if r.status == "waiting":
             self.waiting.remove(r)
-        self._finish(r, "cancelled")
+        self._retire(r, "cancelled")
+
+    def _entry_price(self, r: Request) -> int:
+        """Pages a request must find to be admitted: its whole life under "full" (then it can never lack one later,
+        runtime/engine.py:65-76), what it holds tokens for now under "lazy"."""
+        return self._life_pages(r) if self.reserve == "full" else self._pages_for(len(r.tokens()))
 
     def _admit(self) -> None:
-        if self.reserve == "full":
-            available = self._pool_pages() - sum(self.reserved.values())
-        else:
-            available = self._free_pages()
-        # scan the whole queue: a large request does not block smaller ones behind it
-        for r in list(self.waiting):
+        budget = self._pool_pages() - sum(self.reserved.values()) if self.reserve == "full" else self._free_pages()
+        now = time.perf_counter()
+        # every waiting request is looked at, so a large one does not hold up smaller ones behind it
+        for r in [w for w in self.waiting if w.submitted_at <= now]:
             if len(self.active) >= self.max_active:
-                break
-            if time.perf_counter() < r.submitted_at:
-                continue
-            if self.reserve == "full":
-                pages = self._life_pages(r)
-            else:
-                pages = math.ceil(len(r.tokens()) / self._page_size)
-            if pages > available:
+                return
+            price = self._entry_price(r)
+            if price > budget:
                 continue
             self.waiting.remove(r)
             if r.max_new_tokens == 0:
-                self._finish(r)
+                self._finish(r)           # nothing to generate: it never touches the cache
                 continue
             self.stepper.create(r.key)
-            self.reserved[r.key] = pages
-            available -= pages
+            self.reserved[r.key] = price
+            budget -= price
             r.status = "prefill"
             self.active.append(r)
 
     def _preempt(self, r: Request) -> None:
         self.stepper.release(r.key)
-        self.reserved.pop(r.key, None)
+        del self.reserved[r.key]
         self.active.remove(r)
         r.cursor = 0
         r.status = "waiting"
@@ -203,21 +226,28 @@ class Engine:
         self.waiting.appendleft(r)
 
     # ---------------------------------------------------------------- one step
-    def _plan(self) -> List[Tuple[Request, int]]:
-        """(request, number of its next tokens) for this step, within the token budget."""
-        order = self.active[self.rotation:] + self.active[:self.rotation]
-        self.rotation = (self.rotation + 1) % max(1, len(self.active))
+    def _turn_order(self) -> List[Request]:
+        """Who is served first this step: the running requests, starting one further along each step so that none
+        starves when the budget is smaller than the batch; under decode_first the decoding ones move to the front,
+        otherwise keeping that order (runtime/engine.py:83-85)."""
+        first = self.rotation % max(1, len(self.active))
+        self.rotation = (first + 1) % max(1, len(self.active))
+        order = self.active[first:] + self.active[:first]
         if self.policy == "decode_first":
-            order.sort(key=lambda r: r.status != "decode")
-        remaining = self.token_budget
+            order = [r for r in order if r.status == "decode"] + [r for r in order if r.status != "decode"]
+        return order
+
+    def _plan(self) -> List[Tuple[Request, int]]:
+        """(request, number of its next tokens) for this step, within the token budget: one token for a decoding
+        request, for the others as much of the prompt as the chunk limit and the rest of the budget allow."""
+        left = self.token_budget
         plan = []
-        for r in order:
-            if remaining <= 0:
+        for r in self._turn_order():
+            if left <= 0:
                 break
-            pending = len(r.prompt) + len(r.generated) - r.cursor
-            n = 1 if r.status == "decode" else min(pending, self.prefill_chunk, remaining)
+            n = 1 if r.status == "decode" else min(len(r.tokens()) - r.cursor, self.prefill_chunk, left)
             plan.append((r, n))
-            remaining -= n
+            left -= n
         return plan
 
     def _staged(self, tokens):
@@ -331,10 +361,16 @@ class Engine:
                 "seed": np.asarray([r.seed for r in choosing], dtype=np.int64),
                 "counter": np.asarray([len(r.generated) for r in choosing], dtype=np.int32)}
 
+    def _sleep_until_an_arrival(self) -> None:
+        """Nothing runs and everything queued is still to arrive: wait a little (at most 10 ms, so a new submit is seen)."""
+        if self.active or not self.waiting:
+            return
+        wait = min(r.submitted_at for r in self.waiting) - time.perf_counter()
+        if wait > 0:
+            time.sleep(min(wait, 0.01))
+
     def run(self) -> List[Request]:
+        """Tick until every request has ended; the requests in the order they were submitted."""
         while self.tick():
-            if not self.active and self.waiting:
-                delay = min(r.submitted_at for r in self.waiting) - time.perf_counter()
-                if delay > 0:
-                    time.sleep(min(delay, 0.01))
+            self._sleep_until_an_arrival()
         return list(self.requests.values())

@@ -50,12 +50,12 @@ def run_page_copies(cache: CacheManager, device) -> None:
 
 
 def prepare_step(cache: CacheManager, ring: PinnedRing, device, entries: Sequence[StepEntry], vocab_size: int,
-                 extra: Optional[Dict[str, np.ndarray]] = None, shape_graphs=None):
+                 extra: Optional[Dict[str, np.ndarray]] = None, shape_graphs=None, planners: Sequence = ()):
     """Validate a batch, reserve its pages (all or nothing), send its metadata and bring the device's block
     tables up to date.  Returns (context, device views of `extra`, graph or None).  Lengths advance in `commit_step`.
 
     With `shape_graphs`, a step whose shape has a captured graph gets its metadata into that graph's buffers and
-    leaves the table updates to the graph."""
+    leaves the table updates to the graph.  `planners`: the parts whose launch plans are packed into the same copy."""
     validate_entries(cache, entries, vocab_size)
     keys = [e.key for e in entries]
     cache.reserve([(e.key, len(e.tokens)) for e in entries])   # raises before any change
@@ -86,7 +86,8 @@ def prepare_step(cache: CacheManager, ring: PinnedRing, device, entries: Sequenc
         updates.append((idx, val))
     ctx, update_views, extras = build_context(
         device, ring, host, np.asarray(token_ids, dtype=np.int32), np.asarray(positions, dtype=np.int32),
-        np.asarray(token_req, dtype=np.int32), updates, extra, static=graph.static if graph is not None else None)
+        np.asarray(token_req, dtype=np.int32), updates, extra, static=graph.static if graph is not None else None,
+        planners=planners)
     if graph is None:
         for g, (idx, val) in zip(cache.page_groups, update_views):
             if idx.numel():
@@ -124,6 +125,7 @@ class Stepper:
         self.max_slots = max_slots
         self.cache: CacheManager = model.make_cache(n_pages, page_size, max_slots)
         self.ring = PinnedRing()
+        self.planners = model.planners()
         self.last_context: Optional[StepContext] = None
         self.last_extras: Dict[str, torch.Tensor] = {}
         self.last_tokens: Optional[torch.Tensor] = None     # tokens a graph step sampled itself
@@ -159,7 +161,7 @@ class Stepper:
         if self.graphs is not None and entries and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return self._graph_step(entries, extra)
         ctx, extras, graph = prepare_step(self.cache, self.ring, self.model.device, entries, self.model.spec.vocab_size,
-                                          extra, shape_graphs=self.graphs)
+                                          extra, shape_graphs=self.graphs, planners=self.planners)
         if graph is not None:
             logits = graph.run(ctx, ctx.update_views)
         else:

@@ -230,6 +230,15 @@ def set_clusters(on: bool) -> None:
             lib.cisr_attn_set_clusters(int(on))
 
 
+def set_decode_ranges_per_cta(n: int) -> None:
+    """How many consecutive key ranges one CTA of the tensor-map decode attention walks: 0 lets the launcher choose (it
+    aims at about three CTAs per SM), n > 0 fixes it.  Each range is summed on its own whatever the choice, so the output
+    is the same to the last bit; tests use this to check exactly that."""
+    for lib in _attention_libs.values():
+        if lib._tensor_maps:
+            lib.cisr_attn_set_ranges_per_cta(int(n))
+
+
 def _error_flag() -> torch.Tensor:
     """One int on the device that a kernel sets when one of its bounded waits ran out."""
     flag = _error_state.get("flag")
@@ -693,3 +702,87 @@ def raise_if_kernel_gave_up() -> None:
     flag = _error_state.get("flag")
     if flag is not None:
         raise_for_code(int(flag.item()))
+
+
+# ------------------------------------------------------------------ per-launch timing, for measurement only
+_timing = {"records": None}
+
+
+class timed_launches:
+    """Inside this context every kernel function of this module is bracketed by two CUDA events on the current stream;
+    `records` collects (function name, shape description, begin event, end event).  Used by bench.py for the
+    per-kernel figures (launches run one after the other, outside graphs, so these are isolated kernel times); the
+    engine never turns it on.  Read the times with `summary()` after a synchronisation."""
+
+    def __enter__(self):
+        self.records = []
+        _timing["records"] = self.records
+        return self
+
+    def __exit__(self, *exc):
+        _timing["records"] = None
+        return False
+
+    def summary(self) -> dict:
+        """(name, shape) -> {"launches", "us"}: total device time between the two events of each launch."""
+        torch.cuda.synchronize()
+        out = {}
+        for name, shape, begin, end in self.records:
+            entry = out.setdefault((name, shape), {"launches": 0, "us": 0.0})
+            entry["launches"] += 1
+            entry["us"] += begin.elapsed_time(end) * 1e3
+        return out
+
+
+def _describe_gemm(a, w, *rest, **kw):
+    return (int(a.shape[0]), int(w.shape[0]), int(w.shape[1]))
+
+
+_DESCRIBE = {
+    "embedding": lambda table, ids, out: (int(out.shape[0]), int(out.shape[1])),
+    "add_rmsnorm": lambda x, delta, weight, eps, out, rows=None, write_back=True: (int(out.shape[0]), int(out.shape[1]), delta is not None),
+    "swiglu": lambda gate_up, out: (int(out.shape[0]), int(out.shape[1])),
+    "rotary_tables": lambda positions, inv_freq, cos, sin: (int(cos.shape[0]), int(cos.shape[1])),
+    "rope_store": lambda proj, *rest, **kw: (int(proj.shape[0]), int(proj.shape[1])),
+    "page_copy": lambda *a, **kw: (),
+    "table_update": lambda *a, **kw: (),
+    "attn_prefill_wide": lambda q, out, k_cache, *rest, **kw: (int(q.shape[0]), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2])),
+    "attn_prefill": lambda q, out, k_cache, *rest, **kw: (int(q.shape[0]), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2])),
+    "attn_decode": lambda q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, *rest, **kw:
+        (int(n_dec), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2])),
+    "sample": lambda logits, *rest, **kw: (int(logits.shape[0]), int(logits.shape[1])),
+    "decode_advance": lambda *a, **kw: (),
+    "gemm_library": _describe_gemm,
+    "gemm_tcgen05": _describe_gemm,
+    "gemm_tcgen05_swiglu": _describe_gemm,
+    "gemm_tcgen05_rope": _describe_gemm,
+    "skinny_gemm": lambda w, tokens, **kw: (int(tokens), int(w.shape[0]), int(w.shape[1]), int(kw.get("epilogue", EPI_PLAIN)),
+                                            kw.get("act") is None),
+}
+
+
+def _instrument() -> None:
+    import functools
+
+    def wrap(name, describe):
+        fn = globals()[name]
+
+        @functools.wraps(fn)
+        def launched(*args, **kwargs):
+            records = _timing["records"]
+            if records is None:
+                return fn(*args, **kwargs)
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            result = fn(*args, **kwargs)
+            end.record()
+            records.append((name, describe(*args, **kwargs), begin, end))
+            return result
+
+        globals()[name] = launched
+
+    for name, describe in _DESCRIBE.items():
+        wrap(name, describe)
+
+
+_instrument()

@@ -9,12 +9,20 @@ from __future__ import annotations
 
 from typing import Dict
 
+import numpy as np
 import torch
 
 from ..config.spec import CacheUse
 from ..ops import kernels
 from .base import MIXERS, POSITIONS, Mixer, TensorNeed, build_part, register
 from .linear import as_tensor, linear, norm_fusable
+
+
+# Keys per range of the split decode attention.  Ranges are [i * DECODE_RANGE, (i + 1) * DECODE_RANGE) in absolute
+# positions whatever else is in the batch, so the order in which a request's keys are summed depends only on its own
+# length: 256 keys are one tile for each of a CTA's four warps at head size 64, two at head size 128.
+DECODE_RANGE = 256
+CLUSTER_MAX = 16           # key ranges of one request and head that one thread-block cluster can merge
 
 
 @register(MIXERS, "gqa_attention")
@@ -59,6 +67,39 @@ class GQAAttention(Mixer):
     def cache_use(self) -> CacheUse:
         return CacheUse("pages", kv_heads=self.hkv, head_dim=self.dim, window=self.window)
 
+    # ---------------------------------------------------------------- the launch plan of a step
+    def plan_key(self):
+        return ("gqa_attention", kernels.PREFILL_TILE, kernels.WIDE_TILE, DECODE_RANGE)
+
+    def step_plan(self, host):
+        """Which CTAs the attention kernels launch for a step: portions of more than one token are cut into query
+        tiles (request, first query), once per tile size of the two prompt kernels, a portion's last tile first (it
+        has the longest key loop); single tokens are listed for the split kernel, whose number of key ranges comes
+        from the longest context among them (or from the bound a captured graph was made for)."""
+        from ..engine.batch import StepPlan
+
+        tile_req, tile_q0, wide_req, wide_q0, dec_req = [], [], [], [], []
+        longest = 0
+        for r, n in enumerate(host.q_len):
+            if n == 1:
+                dec_req.append(r)
+                longest = max(longest, host.ctx_len[r])
+            else:
+                for q0 in reversed(range(0, n, kernels.PREFILL_TILE)):
+                    tile_req.append(r)
+                    tile_q0.append(q0)
+                for q0 in reversed(range(0, n, kernels.WIDE_TILE)):
+                    wide_req.append(r)
+                    wide_q0.append(q0)
+        if dec_req and host.ctx_bound:
+            longest = max(longest, host.ctx_bound)
+        as_i32 = lambda values: np.asarray(values, dtype=np.int32)
+        return StepPlan(
+            arrays={"tile_req": as_i32(tile_req), "tile_q0": as_i32(tile_q0), "wide_req": as_i32(wide_req),
+                    "wide_q0": as_i32(wide_q0), "dec_req": as_i32(dec_req)},
+            info={"n_tiles": len(tile_req), "n_wide": len(wide_req), "n_decode": len(dec_req),
+                  "n_splits": decode_ranges(longest)})
+
     def forward(self, h, ctx, cache):
         tokens = ctx.n_tokens
         hq, hkv, dim = self.hq, self.hkv, self.dim
@@ -98,17 +139,29 @@ class GQAAttention(Mixer):
                                cache.k if cache.write else None, cache.v if cache.write else None,
                                ctx.token_req, ctx.positions, ctx.req_slot, cache.block_table, cache.page_size, hq, hkv, dim)
         out = torch.empty((tokens, hq, dim), dtype=self.dtype, device=device)
-        if ctx.n_tiles and kernels.attn_prefill_wide_ok(q, cache.k, cache.page_size):
-            kernels.attn_prefill_wide(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, ctx.wide_req, ctx.wide_q0,
+        plan = ctx.plan_for(self)
+        if plan.info["n_tiles"] and kernels.attn_prefill_wide_ok(q, cache.k, cache.page_size):
+            kernels.attn_prefill_wide(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, plan["wide_req"], plan["wide_q0"],
                                       ctx.q_start, ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, self.scale, self.window)
-        elif ctx.n_tiles:
-            kernels.attn_prefill(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, ctx.tile_req, ctx.tile_q0, ctx.q_start,
-                                 ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, self.scale, self.window)
-        if ctx.n_decode:
-            split_size, n_splits = ctx.decode_splits(hkv)
-            partial = torch.empty((ctx.n_decode, hq, n_splits, dim), dtype=torch.float32, device=device)
-            stats = torch.empty((ctx.n_decode, hq, n_splits, 2), dtype=torch.float32, device=device)
-            kernels.attn_decode(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, ctx.dec_req, ctx.n_decode, ctx.q_start,
+        elif plan.info["n_tiles"]:
+            kernels.attn_prefill(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, plan["tile_req"], plan["tile_q0"],
+                                 ctx.q_start, ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, self.scale, self.window)
+        n_decode = plan.info["n_decode"]
+        if n_decode:
+            n_splits = plan.info["n_splits"]
+            partial = torch.empty((n_decode, hq, n_splits, dim), dtype=torch.float32, device=device)
+            stats = torch.empty((n_decode, hq, n_splits, 2), dtype=torch.float32, device=device)
+            kernels.attn_decode(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, plan["dec_req"], n_decode, ctx.q_start,
                                 ctx.ctx_len, partial, stats, hq, hkv, cache.page_size, self.scale, self.window,
-                                split_size, n_splits)
+                                DECODE_RANGE, n_splits)
         return linear(out.view(tokens, hq * dim), self.o)
+
+
+def decode_ranges(longest_context: int) -> int:
+    """How many key ranges of DECODE_RANGE the split kernel is launched with, per request and key head, for contexts
+    up to `longest_context`.  Ranges beyond a request's own length are empty and change nothing in its sum, so the
+    count may be any bound; beyond CLUSTER_MAX it is rounded up to whole clusters for the cluster merge."""
+    n = max(1, -(-longest_context // DECODE_RANGE))
+    if n > CLUSTER_MAX:
+        n = -(-n // CLUSTER_MAX) * CLUSTER_MAX
+    return n

@@ -48,6 +48,16 @@ class Part:
         """Build jobs (source, defines, extra flags) of the kernel libraries this part launches."""
         return []
 
+    def plan_key(self) -> Optional[tuple]:
+        """None: the part needs nothing but the step context.  Otherwise a hashable key naming the launch plan it
+        derives from a step's shape (`step_plan`); parts with equal keys share one plan per step, which the engine
+        sends to the device inside the step's one metadata copy (`ctx.plan_for(part)` reads it)."""
+        return None
+
+    def step_plan(self, host):
+        """The `engine.batch.StepPlan` for a step described by `host` (`engine.batch.HostBatch`)."""
+        raise NotImplementedError
+
 
 class PendingNorm:
     """The input of a mixer or feed-forward that has not been normed yet: norm(x + pending).

@@ -487,12 +487,63 @@ def test_skinny_gemm_swiglu_and_residual_output(m, inter, kk, kind):
     close(act, ref, 2e-2, 2e-2, "skinny swiglu")
 
 
+def plain_rotated_projection(hbf, w, positions, token_req, req_slot, table, page, n_pages, hq, hkv, dim, rot, interleaved, theta):
+    """What the fused q/k/v kernels must leave behind, in float64 from the bfloat16-rounded inputs: q [m, hq, dim] and the
+    key and value caches [pages, hkv, page, dim] (zero where nothing is written).  Whole-head split-half rotation is
+    plain_llama.rotary (runtime/reference.py:9-15); a partial or interleaved rotation, which the reference does not
+    have, is the same turn of pair (i, i + rot/2) or (2i, 2i + 1) of the first `rot` coordinates."""
+    import plain_llama as pl
+    proj = hbf.double().cpu() @ w.double().cpu().T
+    m = proj.shape[0]
+    pos = positions.cpu().long()
+    q = proj[:, :hq * dim].reshape(m, hq, dim)
+    kk = proj[:, hq * dim:(hq + hkv) * dim].reshape(m, hkv, dim)
+    vv = proj[:, (hq + hkv) * dim:].reshape(m, hkv, dim)
+
+    def turn(x):
+        if rot == dim and not interleaved:
+            return pl.rotary(x, pos, theta)
+        half = rot // 2
+        inv = theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / rot)
+        angle = pos.double()[:, None] * inv[None, :]
+        c, s_ = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        out = x.clone()
+        if interleaved:
+            a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+            out[..., 0:rot:2], out[..., 1:rot:2] = a * c - b * s_, b * c + a * s_
+        else:
+            a, b = x[..., :half], x[..., half:rot]
+            out[..., :half], out[..., half:rot] = a * c - b * s_, b * c + a * s_
+        return out
+
+    q, kk = turn(q), turn(kk)
+    kc = torch.zeros(n_pages, hkv, page, dim, dtype=torch.float64); vc = torch.zeros_like(kc)
+    slots, tab = req_slot.cpu().long(), table.cpu().long()
+    for t in range(m):
+        row = tab[slots[token_req[t].item()]]
+        pg, off = row[pos[t] // page].item(), (pos[t] % page).item()
+        kc[pg, :, off], vc[pg, :, off] = kk[t], vv[t]
+    return q, kc, vc
+
+
+def check_rotated_projection(results, reference):
+    """results[0]: the separate kernels, results[1]: the fused kernel; both against the float64 reference (a bfloat16
+    result is within half a unit in the last place of its value plus the product's rounding), then against each other."""
+    for i, what in enumerate(("q", "k cache", "v cache")):
+        for got, path in ((results[1][i], "fused"), (results[0][i], "separate")):
+            assert float(got.abs().sum()) > 0
+            torch.testing.assert_close(got.double(), reference[i], atol=2e-2, rtol=2e-2, msg=lambda s: f"{path} {what} against float64: {s}")
+            assert torch.equal(got == 0, reference[i] == 0) or what == "q", f"{path} {what}: other cache places were written"
+        torch.testing.assert_close(results[1][i], results[0][i], atol=2e-2, rtol=2e-2, msg=lambda s: f"{what}, fused against separate: {s}")
+
+
 @pytest.mark.parametrize("m", [1, 8, 11, 30])
 @pytest.mark.parametrize("dim,hq,hkv,rot,interleaved", [(64, 9, 3, 64, False), (16, 2, 2, 16, False), (48, 5, 1, 32, True), (128, 2, 1, 128, False),
                                                         (96, 3, 1, 96, True), (32, 4, 2, 32, False)])
 @pytest.mark.parametrize("kind", ["latency", "stream"])
-def test_skinny_gemm_rope_matches_the_separate_kernels(m, dim, hq, hkv, rot, interleaved, kind):
-    """Fused norm + q/k/v product + rotation + cache write against product -> rope_store on the same inputs."""
+def test_skinny_gemm_rope_matches_plain_and_the_separate_kernels(m, dim, hq, hkv, rot, interleaved, kind):
+    """Fused q/k/v product + rotation + cache write against the float64 plain rotation of the float64 product, and
+    against product -> rope_store on the same inputs."""
     k = kernels()
     if kind == "stream" and (m > k.STREAM_MAX_TOKENS or dim % 32 or rot != dim):
         pytest.skip("the streaming kernel takes up to 16 tokens, head sizes in steps of 32 and whole-head rotation")
@@ -523,10 +574,8 @@ def test_skinny_gemm_rope_matches_the_separate_kernels(m, dim, hq, hkv, rot, int
             k.rope_store(proj, hq * dim, (hq + hkv) * dim, cos, sin, half, interleaved, q, kc, vc, token_req, positions, req_slot,
                          table, page, hq, hkv, dim)
         results.append((q.float().cpu(), kc.float().cpu(), vc.float().cpu()))
-    for a, b, what in zip(results[0], results[1], ("q", "k cache", "v cache")):
-        assert float(b.abs().sum()) > 0
-        torch.testing.assert_close(b, a, atol=2e-2, rtol=2e-2, msg=lambda s: f"{what}: {s}")
-        assert torch.equal(b == 0, a == 0) or what == "q"                          # the same cache places were written
+    check_rotated_projection(results, plain_rotated_projection(hbf, w, positions, token_req, req_slot, table, page, 36, hq, hkv, dim,
+                                                               rot, interleaved, theta))
 
 
 @pytest.mark.parametrize("m,n,kk", [(128, 128, 64), (128, 64, 128), (2048, 960, 576), (300, 576, 1536), (130, 49, 72),
@@ -548,12 +597,14 @@ def test_gemm_tcgen05(m, n, kk):
 
 
 @pytest.mark.parametrize("m,inter,kk", [(128, 64, 64), (300, 176, 64), (2048, 1536, 576), (130, 250, 96), (129, 13, 40),
-                                        (40, 96, 64), (64, 1536, 576), (1024, 4000, 128)])
+                                        (40, 96, 64), (64, 1536, 576), (1024, 4000, 128), (17, 1536, 576), (33, 250, 96),
+                                        (100, 8192, 2048), (64, 14336, 4096)])
 def test_gemm_tcgen05_swiglu_epilogue(m, inter, kk):
     k = kernels()
     g = torch.Generator().manual_seed(m + inter)
     a = torch.randn(m, kk, generator=g).to(torch.bfloat16)
-    w = (0.2 * torch.randn(2 * inter, kk, generator=g)).to(torch.bfloat16)
+    # a scale of 0.2 up to K = 576; beyond, the scale that keeps gate and up values at the size they have at K = 576
+    w = (0.2 * min(1.0, math.sqrt(576 / kk)) * torch.randn(2 * inter, kk, generator=g)).to(torch.bfloat16)
     out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=dev())
     k.gemm_tcgen05_swiglu(a.to(dev()), w.to(dev()), out)
     k.raise_if_kernel_gave_up()
@@ -564,7 +615,9 @@ def test_gemm_tcgen05_swiglu_epilogue(m, inter, kk):
 
 @pytest.mark.parametrize("m", [17, 64, 128, 333, 2048])
 @pytest.mark.parametrize("dim,hq,hkv", [(64, 9, 3), (128, 2, 1), (64, 2, 2), (128, 32, 8)])
-def test_gemm_tcgen05_rope_epilogue_matches_the_separate_kernels(m, dim, hq, hkv):
+def test_gemm_tcgen05_rope_epilogue_matches_plain_and_the_separate_kernels(m, dim, hq, hkv):
+    """The tcgen05 q/k/v product with rotation and cache write as its epilogue against float64 (plain_llama.rotary of the
+    float64 product), and against the library product followed by the rotate kernel."""
     k = kernels()
     hidden, page, theta = 96, 16, 10000.0
     g = torch.Generator().manual_seed(m + dim)
@@ -593,7 +646,72 @@ def test_gemm_tcgen05_rope_epilogue_matches_the_separate_kernels(m, dim, hq, hkv
             k.rope_store(proj, hq * dim, (hq + hkv) * dim, cos, sin, half, False, q, kc, vc, token_req, positions, req_slot, table,
                          page, hq, hkv, dim)
         results.append((q.float().cpu(), kc.float().cpu(), vc.float().cpu()))
-    for a, b, what in zip(results[0], results[1], ("q", "k cache", "v cache")):
-        assert float(b.abs().sum()) > 0
-        torch.testing.assert_close(b, a, atol=2e-2, rtol=2e-2, msg=lambda s: f"{what}: {s}")
-        assert torch.equal(b == 0, a == 0) or what == "q"
+    check_rotated_projection(results, plain_rotated_projection(hbf, w, positions, token_req, req_slot, table, page, 16 * n_req, hq, hkv,
+                                                               dim, dim, False, theta))
+
+
+def test_tensor_maps_of_one_launch_survive_an_eviction_between_them():
+    """The library remembers tensor maps by (address, shape) and empties that cache when it is full.  A launch asks for
+    two maps in a row (activations, then weights); with room for one entry only, the second request evicts the first
+    while the launch still needs it.  The launch must use its own copies: the products stay right."""
+    k = kernels()
+    lib = k._tcgen05()
+    lib.cisr_gemm_tcgen05_set_map_cache_limit(1)
+    try:
+        g = torch.Generator().manual_seed(5)
+        for m, n, kk in ((200, 300, 128), (130, 64, 256), (200, 300, 128)):
+            a = torch.randn(m, kk, generator=g).to(torch.bfloat16)
+            w = torch.randn(n, kk, generator=g).to(torch.bfloat16)
+            out = torch.full((m, n), float("nan"), device=dev())
+            k.gemm_tcgen05(a.to(dev()), w.to(dev()), out)
+            k.raise_if_kernel_gave_up()
+            close(out, a.double() @ w.double().T, 2e-6 * kk ** 0.5 * 4, 1e-5, f"tcgen05 gemm {m}x{n}x{kk} with a one-entry map cache")
+    finally:
+        lib.cisr_gemm_tcgen05_set_map_cache_limit(4096)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_decode_attention_of_a_request_does_not_depend_on_its_neighbours(dtype):
+    """Key ranges are cut at fixed absolute positions and empty ranges add exactly nothing, so a request's output is the
+    same to the last bit alone, beside short requests, and beside a much longer one (which brings more ranges)."""
+    k = kernels()
+    from cisr_b200.parts.attention import DECODE_RANGE, decode_ranges
+    d, hq, hkv, page = 64, 6, 2, 16
+    lens = [700, 40, 3000, 257]
+    i32 = lambda a: torch.as_tensor(np.asarray(list(a), dtype=np.int32), device=dev())
+    g = torch.Generator().manual_seed(9)
+    n_pages = sum(-(-n // page) for n in lens)
+    kc = torch.randn(n_pages, hkv, page, d, generator=g).to(dtype).to(dev()); vc = torch.randn(n_pages, hkv, page, d, generator=g).to(dtype).to(dev())
+    width = max(-(-n // page) for n in lens)
+    table = np.full((len(lens), width), -1, dtype=np.int32)
+    at = 0
+    for r, n in enumerate(lens):
+        need = -(-n // page)
+        table[r, :need] = np.arange(at, at + need); at += need
+    q_all = (2 * torch.randn(len(lens), hq, d, generator=g)).to(dtype).to(dev())
+
+    def run(rows):
+        n = len(rows)
+        q = q_all[rows].contiguous()
+        out = torch.full_like(q, float("nan"))
+        n_splits = decode_ranges(max(lens[r] for r in rows))
+        partial = torch.full((n, hq, n_splits, d), float("nan"), device=dev()); stats = torch.full((n, hq, n_splits, 2), float("nan"), device=dev())
+        k.attn_decode(q, out, kc, vc, i32(rows), i32(table), i32(range(n)), n, i32(range(n)), i32([lens[r] for r in rows]), partial, stats,
+                      hq, hkv, page, d ** -0.5, None, DECODE_RANGE, n_splits)
+        return out
+
+    alone = run([0])
+    assert torch.isfinite(alone).all()
+    if dtype == torch.bfloat16:
+        # the tensor-map kernel deals several ranges to one CTA when the batch is large; each range is still summed on its
+        # own, so however they are dealt out the output is the same to the last bit
+        everyone = run([0, 1, 2, 3])
+        for per_cta in (1, 2, 3, 8, 64):
+            k.set_decode_ranges_per_cta(per_cta)
+            try:
+                assert torch.equal(run([0, 1, 2, 3]), everyone), per_cta
+            finally:
+                k.set_decode_ranges_per_cta(0)
+    assert torch.equal(run([1, 0])[1], alone[0])                 # beside a short request
+    assert torch.equal(run([0, 2, 3, 1])[0], alone[0])           # beside a long one: twelve ranges instead of three
+    assert torch.equal(run([3, 2])[0], run([3])[0])              # 257 keys: the second range holds one key
