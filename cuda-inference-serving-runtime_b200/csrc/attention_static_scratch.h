@@ -20,6 +20,9 @@
 //  * The call allocates nothing: no cudaMalloc, no cudaFree, no allocating library routine.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
 //    device current) and remembers it for that device.  Make this first call before any stream capture.
+//    The remembered addresses are filled in without a lock: two host threads that make the first call on
+//    one device at the same moment both look the address up and both store the same value, which is
+//    harmless; nothing else about the entry point is shared between host threads but the array itself.
 //  * Sizes whose partial sums do not fit are refused: the call returns CISR_STATIC_TOO_LARGE and, if
 //    `message` is given, writes a sentence there that names the need and the limit.
 //        need = n_dec * hq * n_splits * (head_dim + 2) floats  <=  CISR_STATIC_SCRATCH_BYTES / 4

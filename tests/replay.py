@@ -199,3 +199,28 @@ def compare(got: Dict[Tuple[str, int], np.ndarray], requests: Dict[str, List[int
             if not rel < RRMS16:
                 raise AssertionError(f"bfloat16 logits differ for request {rid} at position {pos}: relative RMS error "
                                      f"{rel:.4f} >= {RRMS16}")
+
+
+def check_generated_tokens(cfg: dict, weights: dict, prompts: Dict[str, List[int]], generated: Dict[str, List[int]],
+                           first_logits: Dict[str, np.ndarray]) -> int:
+    """Greedy bfloat16 generation against the plain implementation, without asking for luck.
+
+    `first_logits[k]`: the engine's logits at the last prompt position of request k, which must be within the bfloat16
+    bound of the plain ones.  Then every generated token must be the plain choice for the sequence generated so far
+    wherever the plain margin between the two best logits is wider than that bound lets a logit move (a relative RMS
+    error of RRMS16 over a row moves single logits by a few times RRMS16 * rms(row)).  Returns how many tokens had
+    such a margin and were checked."""
+    tw = tiny_models.torch_weights(weights)
+    reference = {k: plain_llama.forward(cfg, tw, p).numpy() for k, p in prompts.items()}
+    compare({(k, len(prompts[k]) - 1): row for k, row in first_logits.items()}, prompts, reference, "bfloat16")
+    checked = 0
+    for k, p in prompts.items():
+        seq = list(p)
+        for n, token in enumerate(generated[k]):
+            logits = reference[k][-1] if n == 0 else plain_llama.forward(cfg, tw, seq)[-1].numpy()
+            best = np.sort(logits)[-2:]
+            if best[1] - best[0] > 8 * RRMS16 * float(np.sqrt(np.mean(logits ** 2))):
+                assert token == int(np.argmax(logits)), f"request {k}: generated token {n} is {token}, the plain choice is {int(np.argmax(logits))}"
+                checked += 1
+            seq.append(token)          # follow the engine's own sequence
+    return checked

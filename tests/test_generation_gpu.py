@@ -90,22 +90,61 @@ def test_temperature_sampling_is_reproducible_and_independent_of_batching(tiny):
             seq.append(token)
 
 
-def test_bfloat16_generation_runs_and_mostly_agrees(tiny):
-    from cisr_b200 import Engine, Model, Request
+def test_bfloat16_generation_stays_within_the_logits_bound(tiny):
+    """bfloat16 through the entry point: a request's first token is chosen from logits that must lie within the replay
+    tests' bfloat16 bound of the plain ones, so it must be the plain choice wherever the plain margin between the best
+    two logits is wider than that bound allows the logits to move; and from there on every token must again be the plain
+    choice for the sequence generated so far, under the same condition."""
+    from cisr_b200 import Engine, Model, Request, StepEntry, Stepper
 
     cfg, weights, path = tiny["a"]
-    prompts = {f"r{n}": tm.random_tokens(cfg, n, n) for n in (5, 23)}
-    engine = Engine.for_model(Model.from_pretrained(path, dtype="bfloat16"), pages=16)
+    model = Model.from_pretrained(path, dtype="bfloat16")
+    prompts = {f"r{n}": tm.random_tokens(cfg, n, n) for n in (5, 23, 40)}
+    engine = Engine.for_model(model, pages=16)
     for k, p in prompts.items():
         engine.submit(Request(k, p, max_new_tokens=8))
     got = {r.key: r.generated for r in engine.run()}
-    # the first token of each request comes from logits that differ from the plain ones only by bfloat16 rounding
+    stepper = Stepper(model, n_pages=16, page_size=16, max_slots=4)
+    first = {}
     for k, p in prompts.items():
-        logits = pl.forward(cfg, tm.torch_weights(weights), p)[-1]
-        top2 = torch.topk(logits, 2).values
-        if (top2[0] - top2[1]).item() > 0.05 * logits.abs().max().item():
-            assert got[k][0] == int(torch.argmax(logits))
-        assert len(got[k]) == 8 and all(0 <= t < cfg["vocab_size"] for t in got[k])
+        stepper.create(k)
+        first[k] = stepper.step([StepEntry(k, p, [len(p) - 1])]).cpu().numpy()[0]
+    assert all(len(got[k]) == 8 and all(0 <= t < cfg["vocab_size"] for t in got[k]) for k in prompts)
+    assert replay.check_generated_tokens(cfg, weights, prompts, got, first) >= 12, "too few tokens had a clear plain choice"
+
+
+def tiny_tokenizer(folder, words):
+    """A word-level tokenizer.json: token id = index in `words`; written with the tokenizers package as a checkpoint's would be."""
+    from tokenizers import Tokenizer
+    from tokenizers.models import WordLevel
+    from tokenizers.pre_tokenizers import Whitespace
+
+    tok = Tokenizer(WordLevel({w: i for i, w in enumerate(words)}, unk_token=words[0]))
+    tok.pre_tokenizer = Whitespace()
+    tok.save(str(folder / "tokenizer.json"))
+
+
+def test_command_line_with_a_checkpoint_and_its_tokenizer(tiny, tmp_path):
+    """--checkpoint DIR --prompt TEXT: the prompt goes through DIR/tokenizer.json, the generated ids come back as text
+    (runtime/__main__.py:29-32,47), and the ids are the plain implementation's greedy choice for the encoded prompt."""
+    import shutil
+
+    cfg, weights, path = tiny["a"]
+    folder = tmp_path / "checkpoint"
+    shutil.copytree(path, folder)
+    words = ["<unk>"] + [f"w{i}" for i in range(1, cfg["vocab_size"])]
+    tiny_tokenizer(folder, words)
+    prompt_ids = [7, 200, 31, 7]
+    cmd = [sys.executable, "-m", "cisr_b200", "--dtype", "float32", "--checkpoint", str(folder), "--prompt",
+           " ".join(words[i] for i in prompt_ids), "--max-new-tokens", "5", "--pages", "8"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=str(replay.ROOT), timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    out = json.loads(proc.stdout)
+    assert out["weights"] == "pretrained-local"
+    request = out["requests"][0]
+    expected = pl.generate_greedy(cfg, tm.torch_weights(weights), prompt_ids, 5, eos=cfg["eos_token_id"])
+    assert request["generated"] == expected
+    assert request["text"] is not None and request["text"].split() == [words[t] for t in expected]
 
 
 def test_command_line_prints_the_reference_fields(tiny, tmp_path):

@@ -4,9 +4,10 @@ Some users of the kernels cannot call cudaMalloc: plugin or callback code inside
 code held to a memory budget fixed at start-up, and bindings that have no tensor library to ask
 for scratch.  For them the library keeps the scratch of the split decode attention in a static device
 array.  This test calls the exported C symbol directly, as such a caller would, and checks its output
-against the engine's own entry point (caller-owned scratch) on two calls in a row that share the
-array, then checks that an oversized call is refused with a message.  It is collected last, so a run
-that stops at the first failure has already run every other test.
+against the plain float64 attention (tests/plain_llama.py) and against the engine's own entry point
+(caller-owned scratch) on calls in a row that share the array, then checks that an oversized call is
+refused with a message.  It is collected last, so a run that stops at the first failure has already
+run every other test.
 """
 import ctypes
 
@@ -56,6 +57,23 @@ def run_static(lib, c, split_size, n_splits, message=None):
     return status, out
 
 
+def run_plain(c):
+    """plain_llama.causal_attention in float64 on the stored (rounded) inputs: each request's keys and values gathered
+    from its pages in order, its one query as the last row of a sequence whose earlier queries do not matter."""
+    import plain_llama as pl
+    q, kc, vc = c["q"].double().cpu(), c["k"].double().cpu(), c["v"].double().cpu()
+    table, page = c["table"].cpu().numpy(), c["page_size"]
+    out = torch.zeros_like(q)
+    for r, n in enumerate(c["ctx"].cpu().tolist()):
+        pages = [int(table[r, t // page]) for t in range(n)]
+        keys = torch.stack([kc[pg, :, t % page] for t, pg in enumerate(pages)])        # [n, hkv, D]
+        values = torch.stack([vc[pg, :, t % page] for t, pg in enumerate(pages)])
+        queries = torch.zeros(n, c["hq"], HEAD_DIM, dtype=torch.float64)
+        queries[-1] = q[r]
+        out[r] = pl.causal_attention(queries, keys, values)[-1]
+    return out
+
+
 def run_engine(c, split_size, n_splits):
     from cisr_b200.ops import kernels
     out = torch.full_like(c["q"], float("nan"))
@@ -67,7 +85,7 @@ def run_engine(c, split_size, n_splits):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_static_scratch_entry_point_matches_the_engine_entry_point_twice_in_a_row(dtype):
+def test_static_scratch_entry_point_matches_plain_and_the_engine_entry_point_on_calls_in_a_row(dtype):
     lib = load(dtype)
     first = make_case(1, n_dec=5, hq=9, hkv=3, contexts=[700, 64, 1, 333, 129], page_size=16, dtype=dtype)
     second = make_case(2, n_dec=3, hq=4, hkv=4, contexts=[90, 17, 250], page_size=8, dtype=dtype)
@@ -78,7 +96,10 @@ def test_static_scratch_entry_point_matches_the_engine_entry_point_twice_in_a_ro
         want = run_engine(case, split_size, n_splits)
         torch.cuda.synchronize()
         assert torch.isfinite(got).all()
-        # the same kernels on the same inputs: float32 to rounding, bfloat16 to the last stored bit
+        # against float64 on the same stored inputs, at the bounds of the attention kernel tests (test_kernels_gpu.py)
+        torch.testing.assert_close(got.double().cpu(), run_plain(case), atol=3e-6 if dtype == torch.float32 else 2e-2,
+                                   rtol=1e-5 if dtype == torch.float32 else 2e-2)
+        # and against the engine's entry point: float32 to rounding, bfloat16 to the last stored bit
         torch.testing.assert_close(got.float(), want.float(), atol=3e-6 if dtype == torch.float32 else 2e-2,
                                    rtol=1e-5 if dtype == torch.float32 else 2e-2)
 
