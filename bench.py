@@ -398,6 +398,9 @@ def kernel_rooflines(model, raw: dict, batch: int, context: int, seed: int, dtyp
             entries = [StepEntry("p", ids, [PREFILL_TOKENS - 1])]
             cache_tokens, causal = 0, PREFILL_TOKENS
         torch.cuda.synchronize()
+        # The device first idles for some tens of milliseconds, so that the host has queued the whole step before its
+        # first kernel starts: the events then bracket kernels that run back to back, not the host's launch pace.
+        torch.cuda._sleep(int(0.06 * 1.9e9))
         with kernels.timed_launches() as timed:
             logits = stepper.step(entries)
             if phase == "decode":

@@ -405,7 +405,7 @@ __device__ __forceinline__ void decode_slab(const Tile& tile, const uint32_t (&q
 // Each warp's result into the merge area: merge[warp][row][0..D) = unnormalised output, [D] = running max (base 2),
 // [D+1] = denominator.  `merge` is [4][16][D + 2] floats of shared memory that no warp still reads as a tile.
 __device__ __forceinline__ void warps_to_merge_area(float* merge, const float (&o)[ND][4], const float (&m_run)[2],
-                                                    const float (&l_run)[2], int warp, int lane, int rows) {
+                                                    const float (&l_run)[2], int warp, int lane, int rows, int stride = 16) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         float l = l_run[h];
@@ -413,7 +413,7 @@ __device__ __forceinline__ void warps_to_merge_area(float* merge, const float (&
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int row = (lane >> 2) + 8 * h;
         if (row >= rows) continue;                // a padding row of the 16-row tile: nobody reads it
-        float* dst = merge + ((size_t)warp * 16 + row) * (D + 2);
+        float* dst = merge + ((size_t)warp * stride + row) * (D + 2);
 #pragma unroll
         for (int i = 0; i < ND; ++i) {
             dst[i * 8 + 2 * (lane & 3)] = o[i][2 * h];
@@ -424,15 +424,15 @@ __device__ __forceinline__ void warps_to_merge_area(float* merge, const float (&
 }
 // Element d of query row g of the CTA: the four warps' results merged by log-sum-exp, in a fixed order.
 // Returns the numerator; m (base 2) and den are the row's running max and denominator.
-__device__ __forceinline__ float merged_element(const float* merge, int g, int d, float& m, float& den) {
+__device__ __forceinline__ float merged_element(const float* merge, int g, int d, float& m, float& den, int stride = 16) {
     m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, merge[((size_t)w * 16 + g) * (D + 2) + D]);
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, merge[((size_t)w * stride + g) * (D + 2) + D]);
     float num = 0.f;
     den = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-        const float* src = merge + ((size_t)w * 16 + g) * (D + 2);
+        const float* src = merge + ((size_t)w * stride + g) * (D + 2);
         const float wgt = src[D] == -INFINITY ? 0.f : exp2f(src[D] - m);
         num = fmaf(wgt, src[d], num);
         den = fmaf(wgt, src[D + 1], den);
@@ -442,13 +442,13 @@ __device__ __forceinline__ float merged_element(const float* merge, int g, int d
 // The CTA's result written as its key range's partial sum (the merge kernel works in natural logarithms).
 __device__ __forceinline__ void decode_finish(float* merge, const float (&o)[ND][4], const float (&m_run)[2], const float (&l_run)[2],
                                               float* __restrict__ partial, float* __restrict__ stats, size_t part_base,
-                                              int rows, int n_splits, int split, int tid) {
-    warps_to_merge_area(merge, o, m_run, l_run, tid >> 5, tid & 31, rows);
+                                              int rows, int n_splits, int split, int tid, int stride = 16) {
+    warps_to_merge_area(merge, o, m_run, l_run, tid >> 5, tid & 31, rows, stride);
     __syncthreads();
     for (int e = tid; e < rows * D; e += DEC_THREADS) {
         const int g = e / D, d = e - g * D;
         float m, den;
-        const float num = merged_element(merge, g, d, m, den);
+        const float num = merged_element(merge, g, d, m, den, stride);
         const size_t p = part_base + (size_t)g * n_splits + split;
         partial[p * D + d] = num;
         if (d == 0) { stats[2 * p] = m * LN2; stats[2 * p + 1] = den; }
@@ -644,7 +644,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     pdl_trigger();
     const int group = hq / hkv;
     const int rows = min(16, group - row0);
-    int* pages = reinterpret_cast<int*>(gathered + (cluster > 1 ? (size_t)cluster * rows * ((D + cluster - 1) / cluster + 2) : 0));   // block table entries of the key range
+    int* pages = reinterpret_cast<int*>(gathered + (cluster > 1 ? (size_t)cluster * rows * ((D + cluster - 1) / cluster + 2) : 0));   // block table entries of the CTA's key ranges
     const int slot = blockIdx.x, kvh = blockIdx.y;
     const int req = dec_req[slot];
     const int tok = q_start[req];
@@ -658,22 +658,50 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const float scale2 = scale * LOG2E;
     const unsigned char* Ks = stage;
     unsigned char* Vs = stage + NSUB * SUB_BYTES;
+    // A CTA that walks several ranges keeps the merge area apart from the stages ([4][rows][D + 2] floats behind the page
+    // list), so that the next range's first tiles are on their way while this range is merged and written out.
+    const int first_split = blockIdx.z * per_cta;
+    const int last_split = min(first_split + per_cta, n_parts * cluster);
+    const bool walking = per_cta > 1;
+    const int span_lo = first_split * split_size, span_hi = min(last_split * split_size, ctx);
+    const int span_first_page = span_lo / page_size;
+    const int span_pages = span_lo < span_hi ? (span_hi - 1) / page_size - span_first_page + 1 : 0;
+    const int merge_stride = walking ? rows : 16;
+    if (walking) merge = reinterpret_cast<float*>(pages + ((per_cta * split_size / page_size + 8 + 3) & ~3));
 
+    for (int i = tid; i < span_pages; i += DEC_THREADS) pages[i] = table[span_first_page + i];
     if (tid == 0) {
         *failed = 0;
         for (int w = 0; w < 4; ++w) mbar_init(full + w, 1);
         mbar_init_fence();
     }
+    __syncthreads();                          // the page list and the barriers are ready
+    STAMP(1);
     float o[ND][4];
     float m_run[2], l_run[2];
     uint32_t qf[KD][4];
     bool waited = false;          // on the kernel before this one (once per CTA)
     bool have_q = false;          // the query fragments are in registers (once per CTA)
+    bool fetched = false;         // this warp's first tile of the coming range is already requested
     unsigned uses = 0;            // tiles this warp has received so far: the parity of its barrier
     bool empty = true;
-    int split = blockIdx.z * per_cta, lo = 0, hi = 0;
+    int split = first_split, lo = 0, hi = 0;
 
-    for (int walked = 0; walked < per_cta && split < n_parts * cluster; ++walked, ++split) {
+    // Tile t of the range that starts at `base` into this warp's stage: lane b fetches box b (K or V, 64-column half,
+    // run of box_rows keys).
+    auto fetch = [&](int base, int hi, int t) {
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)TMA_TILE_BYTES);
+        __syncwarp();
+        for (int b = lane; b < 2 * NSUB * boxes; b += 32) {
+            const int i = b % boxes, sub = (b / boxes) % NSUB, is_v = b / (boxes * NSUB);
+            const int kpos = base + t * TK + i * box_rows;
+            const int page = kpos < hi ? pages[kpos / page_size - span_first_page] : -1;
+            const int row = page < 0 ? cache_rows : (page * hkv + kvh) * page_size + kpos % page_size;
+            tma_load_2d(stage + (is_v * NSUB + sub) * SUB_BYTES + i * box_rows * 128, is_v ? &map_v : &map_k, sub * 64, row, bar);
+        }
+    };
+
+    for (; split < last_split; ++split) {
     lo = split * split_size;                                         // a multiple of TK (checked by the launcher)
     hi = min(lo + split_size, ctx);
     if (window > 0) lo = max(lo, ctx - window);
@@ -693,32 +721,14 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     if (!empty) {
     const int base = lo & ~(TK - 1);          // tiles start on multiples of TK keys, so a tile is whole pages (or part of one)
     const int n_tiles = (hi - base + TK - 1) / TK;
-    const int first_page = base / page_size;
-    // the range before is written out: its page list and the merge area (ordinary stores into what tensor-map copies
-    // fill next) are free once every thread is here
-    if (walked) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-    for (int i = tid; i <= (hi - 1) / page_size - first_page; i += DEC_THREADS) pages[i] = table[first_page + i];
-    __syncthreads();                          // (also: the barriers are initialised)
-    STAMP(1);
+    const int first_page = span_first_page;   // the page list starts at the CTA's first range
 
-    // Tile t into this warp's stage: lane b fetches box b (K or V, 64-column half, run of box_rows keys).
-    auto fetch = [&](int t) {
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)TMA_TILE_BYTES);
-        __syncwarp();
-        for (int b = lane; b < 2 * NSUB * boxes; b += 32) {
-            const int i = b % boxes, sub = (b / boxes) % NSUB, is_v = b / (boxes * NSUB);
-            const int kpos = base + t * TK + i * box_rows;
-            const int page = kpos < hi ? pages[kpos / page_size - first_page] : -1;
-            const int row = page < 0 ? cache_rows : (page * hkv + kvh) * page_size + kpos % page_size;
-            tma_load_2d(stage + (is_v * NSUB + sub) * SUB_BYTES + i * box_rows * 128, is_v ? &map_v : &map_k, sub * 64, row, bar);
-        }
-    };
     // Older keys do not come from the kernel before this one, only the newest (position ctx - 1) does.  Every warp's
-    // first tile is requested now; in the tile that holds the newest key that one row arrives stale and is fetched
-    // again, by ordinary loads, once the kernel before has finished.
+    // first tile is requested now (unless the range before already did); in the tile that holds the newest key that
+    // one row arrives stale if this is before the wait below, and is fetched again, by ordinary loads, after it.
     const int newest = hi == ctx ? n_tiles - 1 : -1;
-    if (warp < n_tiles) fetch(warp);
+    if (!fetched && warp < n_tiles) fetch(base, hi, warp);
+    fetched = false;
     STAMP(2);
     if (!waited) {
         pdl_wait();
@@ -847,18 +857,29 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
         }
         __syncwarp();                                                // every lane has read the stage
-        if (t + 4 < n_tiles) fetch(t + 4);
+        if (t + 4 < n_tiles) fetch(base, hi, t + 4);
+    }
+    if (walking && split + 1 < last_split) {
+        // this warp's stage is free: request its first tile of the next range before this range is merged and written
+        int nlo = (split + 1) * split_size;
+        const int nhi = min(nlo + split_size, ctx);
+        if (window > 0) nlo = max(nlo, ctx - window);
+        if (nlo < nhi) {
+            const int nbase = nlo & ~(TK - 1);
+            if (warp < (nhi - nbase + TK - 1) / TK) fetch(nbase, nhi, warp);
+            fetched = true;
+        }
     }
     (void)lost;
     } else if (!waited) {
         pdl_wait();
         waited = true;
     }
-    __syncthreads();          // every warp is done with its stage: the stages become the merge area
+    __syncthreads();          // every warp is done with its stage (the stages become the merge area), or with the merge area of the range before
     STAMP(6);
     if (cluster == 1) {
         if (*failed) return;  // a copy never arrived; the host reads the error flag
-        decode_finish(merge, o, m_run, l_run, partial, stats, part_base, rows, n_parts, split, tid);
+        decode_finish(merge, o, m_run, l_run, partial, stats, part_base, rows, n_parts, split, tid, merge_stride);
         STAMP(7);
         continue;
     }
@@ -1002,7 +1023,9 @@ CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, 
                                  const int* req_slot, const int* block_table, int table_width, const int* dec_req,
                                  int n_dec, const int* q_start, const int* ctx_len, float* partial, float* stats, int hq,
                                  int hkv, int page_size, float scale, int window, int split_size, int n_splits,
-                                 void* stream) {
+                                 int merge, void* stream) {
+    // merge == 0: the ranges' partial sums and statistics are left in `partial` and `stats` for the caller's own merge
+    // (merge_proj.cu merges them in the prologue of the output projection); `out` is then not written.
     if (n_dec <= 0) return 0;
     if (hq % hkv || split_size <= 0 || n_splits <= 0) return -2;
     const size_t smem = DEC_SMEM + sizeof(int) * ((size_t)split_size / page_size + 4);   // + the range's block table entries
@@ -1022,6 +1045,7 @@ CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, 
                                    window, split_size, n_splits, row0);
         if (status) return status;
     }
+    if (!merge) return 0;
     return launch_kernel(attn_merge_kernel, dim3(n_dec, hq), dim3(D <= 64 ? 64 : 128), sizeof(float) * 2 * (size_t)n_splits, s, g_pdl,
                          (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_splits);
 }
@@ -1053,9 +1077,10 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
                                      const int* req_slot, const int* block_table, int table_width, const int* dec_req,
                                      int n_dec, const int* q_start, const int* ctx_len, float* partial, float* stats,
                                      int hq, int hkv, int page_size, float scale, int window, int split_size,
-                                     int n_splits, void* stream) {
+                                     int n_splits, int merge, void* stream) {
     if (n_dec <= 0) return 0;
     if (!g_encode || !g_error) return -13;
+    if (!merge && g_clusters) return -2;      // the caller's own merge needs every range's partial sum
     if (hq % hkv || n_splits <= 0 || !cisr_attn_decode_tma_ok(page_size, split_size)) return -2;
     const long long cache_rows = (long long)n_pages * hkv * page_size;
     if (cache_rows <= 0 || cache_rows >= (1ll << 31) || (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15)) return -2;
@@ -1103,7 +1128,8 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
     }
     const int n_parts = n_splits / cluster;
     // Without clusters a CTA may walk several consecutive ranges (each still summed on its own, so the result does not
-    // change): as many as it takes to bring the grid down to about three CTAs per SM, in powers of two.
+    // change): as many as it takes to bring the grid down to about three CTAs per SM, in powers of two.  Such a CTA
+    // holds the page entries of all its ranges and a merge area of its own ([4][rows][D + 2] floats).
     int per_cta = 1;
     if (cluster == 1) {
         static int sms = 0;
@@ -1111,9 +1137,15 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
         if (g_ranges_per_cta > 0) per_cta = g_ranges_per_cta;
         else while (per_cta < n_splits && (long long)n_dec * hkv * ((n_splits + per_cta - 1) / per_cta) > 3ll * sms) per_cta *= 2;
         if (per_cta > n_splits) per_cta = n_splits;
+        while (per_cta > 1) {
+            const size_t need = TMA_SMEM_FIXED + sizeof(int) * (((size_t)per_cta * split_size / page_size + 8 + 3) & ~(size_t)3) +
+                                sizeof(float) * 4 * (size_t)rows_max * (D + 2);
+            if (need <= SMEM_CAP) { smem = need; break; }
+            per_cta /= 2;                     // tiny pages and very many ranges: fewer ranges per CTA
+        }
     }
     cudaStream_t s = (cudaStream_t)stream;
-    g_last_launches = (group + 15) / 16 + ((n_parts == 1 && cluster > 1) ? 0 : 1);
+    g_last_launches = (group + 15) / 16 + (((n_parts == 1 && cluster > 1) || !merge) ? 0 : 1);
     for (int row0 = 0; row0 < group; row0 += 16) {
         status = launch_kernel_cluster(attn_decode_tma_kernel, dim3(n_dec, hkv, (n_splits + per_cta - 1) / per_cta), dim3(DEC_THREADS), smem, s,
                                        g_pdl, cluster, map_k, map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
@@ -1122,7 +1154,7 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
                                        cluster, n_parts, per_cta, row0, g_error);
         if (status) return status;
     }
-    if (n_parts == 1 && cluster > 1) return 0;
+    if ((n_parts == 1 && cluster > 1) || !merge) return 0;
     return launch_kernel(attn_merge_kernel, dim3(n_dec, hq), dim3(D <= 64 ? 64 : 128), sizeof(float) * 2 * (size_t)n_parts, s, g_pdl,
                          (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_parts);
 }

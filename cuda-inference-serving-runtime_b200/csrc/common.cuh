@@ -60,7 +60,8 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 enum : int {
     TRACE_EMBEDDING = 1, TRACE_ADD_RMSNORM, TRACE_SWIGLU, TRACE_ROTARY_TABLE, TRACE_ROPE_STORE, TRACE_PAGE_COPY, TRACE_TABLE_UPDATE,
     TRACE_ATTN_PREFILL, TRACE_ATTN_DECODE_GATHER, TRACE_ATTN_DECODE_TMA, TRACE_ATTN_MERGE, TRACE_SAMPLE, TRACE_DECODE_ADVANCE,
-    TRACE_SKINNY_PLAIN, TRACE_SKINNY_SWIGLU, TRACE_SKINNY_ROPE, TRACE_GEMM_TCGEN05, TRACE_ATTN_SIMT, TRACE_STREAM_GEMM
+    TRACE_SKINNY_PLAIN, TRACE_SKINNY_SWIGLU, TRACE_SKINNY_ROPE, TRACE_GEMM_TCGEN05, TRACE_ATTN_SIMT, TRACE_STREAM_GEMM,
+    TRACE_MERGE_PROJ
 };
 #ifdef CISR_TRACE
 struct TraceRecord { unsigned long long entered, waited, left, marks[4]; int kernel, block, sm, pad; };

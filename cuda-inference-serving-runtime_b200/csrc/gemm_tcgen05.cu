@@ -32,6 +32,7 @@ constexpr int BK = 64, UMMA_K = 16;     // BM = 128 (tcgen05.cuh)
 
 struct Epilogue {                       // what the epilogue variants need beyond the accumulator
     float* out_f32; bf16* out_bf16; int inter;
+    int accumulate;                     // PLAIN: out += product (the residual stream, in place) instead of out = product
     const float* cos_t; const float* sin_t; bf16* q_out; bf16* k_cache; bf16* v_cache; const int* positions;
     const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size; int hq; int hkv; int dim;
 };
@@ -74,14 +75,24 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, uint32_t lane_
             if (row < m) {
                 float* dst = ep.out_f32 + (size_t)row * n + n0 + c;
                 if (n0 + c + 32 <= n && (n & 3) == 0) {
+                    if (ep.accumulate) {
+                        // The add is done where the element lives (a reduction in L2), so the epilogue does not wait for
+                        // a load: every element belongs to this thread alone, and one float add in round-to-nearest is
+                        // the same sum wherever it is made.
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                                          __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        for (int j = 0; j < 32; j += 4)
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(__uint_as_float(v[j])),
+                                         "f"(__uint_as_float(v[j + 1])), "f"(__uint_as_float(v[j + 2])), "f"(__uint_as_float(v[j + 3])) : "memory");
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                              __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                    }
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        if (n0 + c + j < n) dst[j] = __uint_as_float(v[j]);
+                        if (n0 + c + j < n) dst[j] = ep.accumulate ? dst[j] + __uint_as_float(v[j]) : __uint_as_float(v[j]);
                 }
             }
         }
@@ -351,12 +362,14 @@ CISR_EXPORT void cisr_gemm_tcgen05_set_map_cache_limit(int entries) { g_map_cach
 
 // Three pipeline stages keep a CTA near 100 KB of shared memory, so two CTAs share an SM and one's epilogue overlaps
 // the other's main loop.
-CISR_EXPORT int cisr_gemm_tcgen05(const void* a, const void* w, float* out, int m, int n, int k, void* stream) {
+// accumulate != 0: out += a w^T (each output element is read, added to in float and written by the one thread that
+// owns it: what the residual add of a layer does, without a pass of its own).
+CISR_EXPORT int cisr_gemm_tcgen05(const void* a, const void* w, float* out, int m, int n, int k, int accumulate, void* stream) {
     if (m <= 0 || n <= 0) return 0;
     if (!g_encode || !g_error) return -13;
     if (!operands_ok(a, w, k) || ((uintptr_t)out & 15)) return -2;
     Epilogue ep = {};
-    ep.out_f32 = out;
+    ep.out_f32 = out; ep.accumulate = accumulate != 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (n <= 64) return launch<64, 8, EPI_PLAIN>(a, w, ep, m, n, k, (n + 63) / 64, s);
     if (wide_tiles(m, (n + 255) / 256)) return launch<256, 4, EPI_PLAIN>(a, w, ep, m, n, k, (n + 255) / 256, s);

@@ -325,8 +325,11 @@ def attn_prefill(q, out, k_cache, v_cache, req_slot, block_table, tile_req, tile
 
 
 def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, q_start, ctx_len, partial, stats, hq, hkv,
-                page_size, scale, window, split_size, n_splits, kind: str = "auto", staging: str = "auto") -> None:
+                page_size, scale, window, split_size, n_splits, kind: str = "auto", staging: str = "auto", merge: bool = True) -> None:
     """Attention of single new tokens, split over key ranges of `split_size`, merged into out.
+
+    `merge=False` (tensor-core kernels only) leaves the ranges' partial sums in `partial` and `stats` and does not write
+    `out`: the caller merges them itself (`merge_out_proj`).
 
     `staging` picks how the tensor-core kernel brings key and value tiles in: "tensor_map" (one bulk copy per
     page), "gather" (a 16-byte copy per thread), or "auto": tensor maps where the head size (a multiple of 64), the
@@ -340,7 +343,12 @@ def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec,
         raise KernelError("attn_decode: scratch for partial sums is too small")
     lib = attention_library(dim, k_cache.dtype, kind)
     tail = [_p(req_slot), _p(block_table), block_table.shape[1], _p(dec_req), n_dec, _p(q_start), _p(ctx_len), _p(partial),
-            _p(stats), hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), split_size, n_splits, _stream()]
+            _p(stats), hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), split_size, n_splits]
+    if lib._tensor_core:
+        tail.append(int(merge))
+    elif not merge:
+        raise KernelError("attn_decode: only the tensor-core kernels leave the merge to the caller")
+    tail.append(_stream())
     if staging not in ("auto", "tensor_map", "gather"):
         raise KernelError(f"unknown staging {staging!r}")
     tensor_maps = (lib._tensor_maps and lib.cisr_attn_decode_tma_ok(page_size, split_size) and k_cache.is_contiguous()
@@ -352,7 +360,52 @@ def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec,
         status = lib.cisr_attn_decode_tma(_p(q), _p(out), _p(k_cache), _p(v_cache), k_cache.shape[0], *tail)
         _check(status, "attn_decode", own=lib.cisr_attn_decode_tma_launches() if status == 0 else 0)
     else:
-        _check(lib.cisr_attn_decode(_p(q), _p(out), _p(k_cache), _p(v_cache), *tail), "attn_decode", own=-(-(hq // hkv) // 16) + 1)
+        _check(lib.cisr_attn_decode(_p(q), _p(out), _p(k_cache), _p(v_cache), *tail), "attn_decode",
+               own=-(-(hq // hkv) // 16) + (1 if merge else 0))
+
+
+# ------------------------------------------------------------------ merge of the key ranges + output projection (decode steps)
+_merge_proj_state = {}
+
+
+def _merge_proj():
+    lib = _merge_proj_state.get("lib")
+    if lib is None:
+        lib = load_library("merge_proj.cu")
+        lib.cisr_merge_proj.restype = ctypes.c_int
+        lib.cisr_merge_proj_heads_per_cta.restype = ctypes.c_int
+        lib.cisr_merge_proj_set_pdl(int(_pdl_state["on"]))
+        _merge_proj_state["lib"] = lib
+    return lib
+
+
+def merge_proj_jobs():
+    return [("merge_proj.cu", {}, ())]
+
+
+MERGE_PROJ_MAX_BYTES = 8 << 20     # larger output projections are bandwidth-bound: the streaming product serves them, and the merge kernel is small beside it
+
+
+def merge_out_proj_ok(n_dec: int, hq: int, dim: int, w: torch.Tensor) -> bool:
+    """Whether `merge_out_proj` takes the shape: bfloat16 weights [N, hq * dim] of a latency-bound size, at most 16 tokens,
+    head slices of at most 256 columns in at most 16 CTAs; and thread-block clusters in the attention kernel off."""
+    return (w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] == hq * dim and w.numel() * 2 < MERGE_PROJ_MAX_BYTES
+            and not _cluster_state["on"] and os.environ.get("CISR_MERGE_PROJ", "1") != "0"
+            and _merge_proj().cisr_merge_proj_heads_per_cta(n_dec, hq, dim, w.shape[1]) > 0)
+
+
+def merge_out_proj(partial: torch.Tensor, stats: torch.Tensor, n_splits: int, dec_req: torch.Tensor, q_start: torch.Tensor,
+                   n_dec: int, hq: int, dim: int, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[row of request i] (float [tokens, N]) = (log-sum-exp merge of request i's key ranges, rounded to bfloat16) @ w^T:
+    the merge kernel and the output projection of a decode step in one launch of a thread-block cluster."""
+    _need(partial, torch.float32, "partial"); _need(stats, torch.float32, "stats"); _need(w, torch.bfloat16, "w", 2)
+    _need(out, torch.float32, "out", 2); _need(dec_req, torch.int32, "dec_req", 1); _need(q_start, torch.int32, "q_start", 1)
+    if partial.numel() < n_dec * hq * n_splits * dim or stats.numel() < n_dec * hq * n_splits * 2 or out.shape[1] != w.shape[0]:
+        raise KernelError("merge_out_proj: shapes disagree")
+    status = _merge_proj().cisr_merge_proj(_p(partial), _p(stats), n_splits, _p(dec_req), _p(q_start), n_dec, hq, dim, _p(w),
+                                           w.shape[0], w.shape[1], _p(out), _stream())
+    _check(status, "merge_out_proj")
+    return out
 
 
 # ------------------------------------------------------------------ sampling
@@ -452,7 +505,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------ weight-streaming products for few tokens
-SKINNY_MAX_TOKENS = 16           # above this the library product is faster than streaming the weights per 16 features
+SKINNY_MAX_TOKENS = int(os.environ.get("CISR_SKINNY_MAX_TOKENS", "16"))   # most tokens the latency kernels are chosen for (they take up to 64)
 SKINNY_NORM_MAX_TOKENS = 16      # beyond this the norm runs once as its own kernel instead of in every CTA
 EPI_PLAIN, EPI_SWIGLU, EPI_ROPE = 0, 1, 2
 
@@ -473,6 +526,8 @@ def set_pdl(on: bool) -> None:
         _stream_state["lib"].cisr_stream_set_pdl(int(on))
     for lib in _attention_tcgen05_libs.values():
         lib.cisr_attn_tcgen05_set_pdl(int(on))
+    if "lib" in _merge_proj_state:
+        _merge_proj_state["lib"].cisr_merge_proj_set_pdl(int(on))
     _elementwise().cisr_elementwise_set_pdl(int(on))
     _sampling().cisr_sampling_set_pdl(int(on))
     if "lib" in _tcgen05_state:
@@ -629,14 +684,15 @@ def tcgen05_ok(a: torch.Tensor, w: torch.Tensor, fused: bool = False) -> bool:
             and a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[M, N] (float) = a[M, K] @ w[N, K]^T on tcgen05 tensor cores fed by TMA (bfloat16 operands)."""
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+    """out[M, N] (float) = a[M, K] @ w[N, K]^T on tcgen05 tensor cores fed by TMA (bfloat16 operands); with
+    `accumulate`, out += the product (the residual add as the product's epilogue)."""
     _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 2); _need(out, torch.float32, "out", 2)
     m, k = a.shape
     n = w.shape[0]
     if w.shape[1] != k or out.shape != (m, n):
         raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
-    _check(_tcgen05().cisr_gemm_tcgen05(_p(a), _p(w), _p(out), m, n, k, _stream()), "gemm_tcgen05")
+    _check(_tcgen05().cisr_gemm_tcgen05(_p(a), _p(w), _p(out), m, n, k, int(accumulate), _stream()), "gemm_tcgen05")
     return out
 
 
@@ -749,7 +805,9 @@ _DESCRIBE = {
     "attn_prefill_wide": lambda q, out, k_cache, *rest, **kw: (int(q.shape[0]), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2])),
     "attn_prefill": lambda q, out, k_cache, *rest, **kw: (int(q.shape[0]), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2])),
     "attn_decode": lambda q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, *rest, **kw:
-        (int(n_dec), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2])),
+        (int(n_dec), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2]), bool(kw.get("merge", True))),
+    "merge_out_proj": lambda partial, stats, n_splits, dec_req, q_start, n_dec, hq, dim, w, out:
+        (int(n_dec), int(w.shape[0]), int(w.shape[1]), int(n_splits)),
     "sample": lambda logits, *rest, **kw: (int(logits.shape[0]), int(logits.shape[1])),
     "decode_advance": lambda *a, **kw: (),
     "gemm_library": _describe_gemm,

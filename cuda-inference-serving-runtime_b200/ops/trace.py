@@ -19,7 +19,7 @@ from . import build
 KERNEL_NAMES = {
     1: "embedding", 2: "add_rmsnorm", 3: "swiglu", 4: "rotary_table", 5: "rope_store", 6: "page_copy", 7: "table_update",
     8: "attn_prefill", 9: "attn_decode (gather)", 10: "attn_decode (tensor maps)", 11: "attn_merge", 12: "sample",
-    13: "decode_advance", 14: "skinny plain", 15: "skinny swiglu", 16: "skinny rope", 17: "gemm_tcgen05", 18: "attention (CUDA cores)", 19: "stream_gemm",
+    13: "decode_advance", 14: "skinny plain", 15: "skinny swiglu", 16: "skinny rope", 17: "gemm_tcgen05", 18: "attention (CUDA cores)", 19: "stream_gemm", 20: "merge + output projection",
 }
 RECORD = np.dtype([("entered", "<u8"), ("waited", "<u8"), ("left", "<u8"), ("marks", "<u8", (4,)), ("kernel", "<i4"),
                    ("block", "<i4"), ("sm", "<i4"), ("pad", "<i4")])

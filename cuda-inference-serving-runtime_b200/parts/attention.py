@@ -15,7 +15,7 @@ import torch
 from ..config.spec import CacheUse
 from ..ops import kernels
 from .base import MIXERS, POSITIONS, Mixer, TensorNeed, build_part, register
-from .linear import as_tensor, linear, norm_fusable
+from .linear import as_tensor, linear, linear_to_stream, norm_fusable
 
 
 # Keys per range of the split decode attention.  Ranges are [i * DECODE_RANGE, (i + 1) * DECODE_RANGE) in absolute
@@ -62,7 +62,7 @@ class GQAAttention(Mixer):
     def kernel_jobs(self):
         return ([("elementwise.cu", {}, ()), kernels.attention_jobs(self.dim, self.dtype)]
                 + kernels.attention_tcgen05_jobs(self.dim, self.dtype) + kernels.gemm_jobs(self.dtype) + self.position.kernel_jobs()
-                + (kernels.skinny_jobs() if self.dtype == torch.bfloat16 else []))
+                + (kernels.skinny_jobs() + kernels.merge_proj_jobs() if self.dtype == torch.bfloat16 else []))
 
     def cache_use(self) -> CacheUse:
         return CacheUse("pages", kv_heads=self.hkv, head_dim=self.dim, window=self.window)
@@ -101,6 +101,7 @@ class GQAAttention(Mixer):
                   "n_splits": decode_ranges(longest)})
 
     def forward(self, h, ctx, cache):
+        h0 = h                    # as it came: the pending norm, through which the output may go straight into the stream
         tokens = ctx.n_tokens
         hq, hkv, dim = self.hq, self.hkv, self.dim
         device = ctx.device
@@ -151,10 +152,17 @@ class GQAAttention(Mixer):
             n_splits = plan.info["n_splits"]
             partial = torch.empty((n_decode, hq, n_splits, dim), dtype=torch.float32, device=device)
             stats = torch.empty((n_decode, hq, n_splits, 2), dtype=torch.float32, device=device)
+            # a step of single tokens only, with a small output projection: the merge of the key ranges is the prologue
+            # of that projection (one launch of a thread-block cluster instead of the merge kernel and the product)
+            fused = (n_decode == tokens and self.dtype == torch.bfloat16 and dim <= kernels.TENSOR_CORE_MAX_HEAD_DIM
+                     and kernels.merge_out_proj_ok(n_decode, hq, dim, self.o))
             kernels.attn_decode(q, out, cache.k, cache.v, ctx.req_slot, cache.block_table, plan["dec_req"], n_decode, ctx.q_start,
                                 ctx.ctx_len, partial, stats, hq, hkv, cache.page_size, self.scale, self.window,
-                                DECODE_RANGE, n_splits)
-        return linear(out.view(tokens, hq * dim), self.o)
+                                DECODE_RANGE, n_splits, merge=not fused)
+            if fused:
+                projected = torch.empty((tokens, self.hidden), dtype=torch.float32, device=device)
+                return kernels.merge_out_proj(partial, stats, n_splits, plan["dec_req"], ctx.q_start, n_decode, hq, dim, self.o, projected)
+        return linear_to_stream(out.view(tokens, hq * dim), self.o, h0)
 
 
 def decode_ranges(longest_context: int) -> int:

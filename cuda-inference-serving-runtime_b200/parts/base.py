@@ -72,6 +72,7 @@ class PendingNorm:
         self.stream, self.norm, self.dtype = stream, norm, dtype
         self.x = stream.x
         self.delta = stream.pending
+        self.resolved = False      # the norm has run (here or inside a product): stream.x is the sum, nothing is pending
 
     def fusable(self) -> bool:
         return getattr(self.norm, "fusable_into_product", False)
@@ -92,9 +93,12 @@ class PendingNorm:
         self.stream.take_pending()
         if x_out is not None:
             self.stream.x = x_out
+        self.resolved = True
 
     def materialize(self) -> torch.Tensor:
-        return self.norm.forward(self.stream.x, self.stream.take_pending(), self.dtype)
+        out = self.norm.forward(self.stream.x, self.stream.take_pending(), self.dtype)
+        self.resolved = True
+        return out
 
     def materialize_once(self) -> torch.Tensor:
         """`materialize`, remembered: a part may ask for the normed tensor more than once while choosing its kernels."""
@@ -135,7 +139,8 @@ class Mixer(Part):
         return CacheUse("none")
 
     def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
-        """h [tokens, hidden] in the compute dtype -> float [tokens, hidden] to add to the residual stream."""
+        """h [tokens, hidden] in the compute dtype -> float [tokens, hidden] to add to the residual stream (a part that
+        took a `PendingNorm` may instead add its output to `h.stream.x` itself and return None)."""
         raise NotImplementedError
 
 

@@ -11,7 +11,7 @@ import torch
 
 from ..ops import kernels
 from .base import FEED_FORWARDS, FeedForward, TensorNeed, register
-from .linear import as_tensor, linear, norm_fusable
+from .linear import as_tensor, linear, linear_to_stream, norm_fusable
 
 
 @register(FEED_FORWARDS, "swiglu")
@@ -41,6 +41,7 @@ class SwiGLU(FeedForward):
                 + (kernels.skinny_jobs() if self.dtype == torch.bfloat16 else []))
 
     def forward(self, h, ctx):
+        h0 = h
         tokens = h.x.shape[0] if not isinstance(h, torch.Tensor) else h.shape[0]
         device = h.x.device if not isinstance(h, torch.Tensor) else h.device
         act = torch.empty((tokens, self.inter), dtype=self.dtype, device=device)
@@ -59,4 +60,4 @@ class SwiGLU(FeedForward):
                 kernels.gemm_tcgen05_swiglu(hn, self.gate_up, act)      # many tokens: SwiGLU is the product's epilogue
             else:
                 kernels.swiglu(linear(hn, self.gate_up), act)
-        return linear(act, self.down)
+        return linear_to_stream(act, self.down, h0)

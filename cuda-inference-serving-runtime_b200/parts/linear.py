@@ -36,3 +36,19 @@ def norm_fusable(h, tokens: int, w: torch.Tensor) -> bool:
 def as_tensor(h) -> torch.Tensor:
     from .base import PendingNorm
     return h.materialize_once() if isinstance(h, PendingNorm) else h
+
+
+def linear_to_stream(a: torch.Tensor, w: torch.Tensor, h):
+    """The last product of a sub-block, whose result the block adds to the residual stream: returns the float
+    product for the block to add, or None after adding it to the stream in place.
+
+    In place needs the stream's current tensor, which a part has when its input came as a `PendingNorm` that is
+    resolved by now (the norm has run, so `h.stream.x` already holds x + the output before), and a product kernel
+    with the add as its epilogue (the tcgen05 product).  The sum is the same single float add per element that the
+    next norm would otherwise make, so the logits do not change with the path."""
+    from .base import PendingNorm
+    if (isinstance(h, PendingNorm) and h.resolved and h.stream.pending is None and kernels.tcgen05_ok(a, w)
+            and h.stream.x.dtype == torch.float32 and h.stream.x.shape == (a.shape[0], w.shape[0]) and h.stream.x.is_contiguous()):
+        kernels.gemm_tcgen05(a, w, h.stream.x, accumulate=True)
+        return None
+    return linear(a, w)

@@ -11,12 +11,25 @@ rests on the reference's code, not only on a reading of its formulas.
 Weights are a dict of torch tensors under Hugging Face Llama names with [out, in]
 linear layout (runtime/model.py:1-5, runtime/checkpoint.py:45-56).  `dtype` selects
 the arithmetic: float64 (default, the tightest oracle) or float32.
+
+`storage` (None or torch.bfloat16) restates the reference's 16-bit modes (runtime/model.py:3-4,
+docs/RUNTIME.md:16-19: activations between kernels and the cache are stored in 16 bits, every sum is
+taken in 32): with it, the values that the engine's bfloat16 path keeps in bfloat16 (the norm's output,
+the rotated queries and keys, the values, the attention output, the SwiGLU output) are rounded to that
+type where they are produced and the arithmetic goes on in `dtype`; the residual stream and the logits
+are not rounded.  Against this twin a bfloat16 engine differs only by what is left: the order of its
+sums and the rounding of the attention probabilities.
 """
 from __future__ import annotations
 
 import math
 
 import torch
+
+
+def stored(x: torch.Tensor, storage) -> torch.Tensor:
+    """x as it reads back after being stored in `storage` (None: unchanged)."""
+    return x if storage is None else x.to(storage).to(x.dtype)
 
 
 def embed(table: torch.Tensor, tokens) -> torch.Tensor:
@@ -69,48 +82,48 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: 
     return torch.einsum("hts,shd->thd", p, vv)
 
 
-def swiglu_mlp(h: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor) -> torch.Tensor:
+def swiglu_mlp(h: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor, storage=None) -> torch.Tensor:
     """down(silu(gate(h)) * up(h)), silu(g) = g / (1 + exp(-g)) (runtime/model.py:117-119, kernels/execution.cu:7-10)."""
     gate = h @ gate_w.T
-    return (gate / (1 + torch.exp(-gate)) * (h @ up_w.T)) @ down_w.T
+    return stored(gate / (1 + torch.exp(-gate)) * (h @ up_w.T), storage) @ down_w.T
 
 
-def attention_block(h, w, prefix, positions, cfg, window=None):
+def attention_block(h, w, prefix, positions, cfg, window=None, storage=None):
     """q/k/v projections, rotation of q and k, attention, output projection (runtime/model.py:110-115)."""
     hq, hkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
     d = cfg.get("head_dim") or cfg["hidden_size"] // hq
     q = (h @ w[prefix + "self_attn.q_proj.weight"].T).reshape(-1, hq, d)
     k = (h @ w[prefix + "self_attn.k_proj.weight"].T).reshape(-1, hkv, d)
-    v = (h @ w[prefix + "self_attn.v_proj.weight"].T).reshape(-1, hkv, d)
-    q = rotary(q, positions, cfg["rope_theta"])
-    k = rotary(k, positions, cfg["rope_theta"])
-    out = causal_attention(q, k, v, window).reshape(-1, hq * d)
+    v = stored((h @ w[prefix + "self_attn.v_proj.weight"].T).reshape(-1, hkv, d), storage)
+    q = stored(rotary(q, positions, cfg["rope_theta"]), storage)
+    k = stored(rotary(k, positions, cfg["rope_theta"]), storage)       # keys are cached rotated
+    out = stored(causal_attention(q, k, v, window).reshape(-1, hq * d), storage)
     return out @ w[prefix + "self_attn.o_proj.weight"].T
 
 
-def decoder_layer(x, w, layer, positions, cfg):
+def decoder_layer(x, w, layer, positions, cfg, storage=None):
     """Pre-norm residual block (runtime/model.py:109-119)."""
     p = f"model.layers.{layer}."
     eps = cfg["rms_norm_eps"]
-    h = rms_norm(x, w[p + "input_layernorm.weight"], eps)
-    x = x + attention_block(h, w, p, positions, cfg)
-    h = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
-    return x + swiglu_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    h = stored(rms_norm(x, w[p + "input_layernorm.weight"], eps), storage)
+    x = x + attention_block(h, w, p, positions, cfg, storage=storage)
+    h = stored(rms_norm(x, w[p + "post_attention_layernorm.weight"], eps), storage)
+    return x + swiglu_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"], storage)
 
 
-def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64) -> torch.Tensor:
+def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, storage=None) -> torch.Tensor:
     """Logits [T, V] at every position of one whole sequence (runtime/model.py:105-120).
 
     `cfg` is the config.json dict.  A tied head uses the embedding table
-    (runtime/checkpoint.py:38-39).
+    (runtime/checkpoint.py:38-39).  `storage`: see the head of this file.
     """
     w = {k: v.to(dtype) for k, v in weights.items()}
     positions = torch.arange(len(tokens))
     x = embed(w["model.embed_tokens.weight"], tokens)
     for layer in range(cfg["num_hidden_layers"]):
-        x = decoder_layer(x, w, layer, positions, cfg)
+        x = decoder_layer(x, w, layer, positions, cfg, storage)
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
-    return rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]) @ head.T
+    return stored(rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]), storage) @ head.T
 
 
 def greedy(logits: torch.Tensor) -> int:

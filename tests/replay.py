@@ -16,8 +16,8 @@ import tiny_models
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def plain_logits(cfg: dict, weights: dict, tokens: Sequence[int], dtype=torch.float64) -> np.ndarray:
-    return plain_llama.forward(cfg, tiny_models.torch_weights(weights), list(tokens), dtype).to(torch.float64).numpy()
+def plain_logits(cfg: dict, weights: dict, tokens: Sequence[int], dtype=torch.float64, storage=None) -> np.ndarray:
+    return plain_llama.forward(cfg, tiny_models.torch_weights(weights), list(tokens), dtype, storage).to(torch.float64).numpy()
 
 
 # ------------------------------------------------------------------ traces
@@ -178,9 +178,15 @@ ATOL32, RTOL32 = 1.5e-5, 1.5e-5
 RRMS16 = 0.03
 
 
+def relative_rms(row: np.ndarray, ref: np.ndarray) -> float:
+    return float(np.sqrt(np.mean((row.astype(np.float64) - ref) ** 2) / max(np.mean(ref ** 2), 1e-30)))
+
+
 def compare(got: Dict[Tuple[str, int], np.ndarray], requests: Dict[str, List[int]], reference: Dict[str, np.ndarray],
-            dtype: str, scale: float = 1.0) -> None:
+            dtype: str, scale: float = 1.0, rrms: float = None) -> None:
+    """`rrms`: another bound than RRMS16 for the bfloat16 rows (a test that uses one says why)."""
     assert got, "nothing was compared"
+    rrms = RRMS16 if rrms is None else rrms
     worst = 0.0
     for (rid, pos), row in sorted(got.items()):
         ref = reference[rid][pos]
@@ -194,11 +200,11 @@ def compare(got: Dict[Tuple[str, int], np.ndarray], requests: Dict[str, List[int
                 raise AssertionError(f"float32 logits differ for request {rid} at position {pos}, vocab index {i}: "
                                      f"got {row[i]!r}, plain {ref[i]!r}, |diff| {err[i]:.3e} (first wrong place in order)")
         else:
-            rel = float(np.sqrt(np.mean((row.astype(np.float64) - ref) ** 2) / max(np.mean(ref ** 2), 1e-30)))
+            rel = relative_rms(row, ref)
             worst = max(worst, rel)
-            if not rel < RRMS16:
+            if not rel < rrms:
                 raise AssertionError(f"bfloat16 logits differ for request {rid} at position {pos}: relative RMS error "
-                                     f"{rel:.4f} >= {RRMS16}")
+                                     f"{rel:.4f} >= {rrms}")
 
 
 def check_generated_tokens(cfg: dict, weights: dict, prompts: Dict[str, List[int]], generated: Dict[str, List[int]],

@@ -596,6 +596,23 @@ def test_gemm_tcgen05(m, n, kk):
     close(out, ref, 2e-6 * kk ** 0.5 * 4, 1e-5, f"tcgen05 gemm {m}x{n}x{kk}")
 
 
+@pytest.mark.parametrize("m,n,kk", [(2048, 576, 576), (300, 576, 1536), (130, 49, 72), (17, 960, 576), (1000, 1000, 1000)])
+def test_gemm_tcgen05_adds_into_the_residual_stream(m, n, kk):
+    """out += a w^T as the product's epilogue: every element is the one float sum of what was there and the product."""
+    k = kernels()
+    g = torch.Generator().manual_seed(m * n + kk)
+    a = torch.randn(m, kk, generator=g).to(torch.bfloat16)
+    w = torch.randn(n, kk, generator=g).to(torch.bfloat16)
+    x = (10 * torch.randn(m, n, generator=g)).float()
+    product = torch.empty((m, n), device=dev())
+    k.gemm_tcgen05(a.to(dev()), w.to(dev()), product)
+    out = x.clone().to(dev())
+    k.gemm_tcgen05(a.to(dev()), w.to(dev()), out, accumulate=True)
+    k.raise_if_kernel_gave_up()
+    assert torch.equal(out.cpu(), x + product.cpu())             # the same bits as adding the product afterwards
+    close(out, x.double() + a.double() @ w.double().T, 2e-6 * kk ** 0.5 * 4 + 1e-5, 1e-5, f"tcgen05 gemm + residual {m}x{n}x{kk}")
+
+
 @pytest.mark.parametrize("m,inter,kk", [(128, 64, 64), (300, 176, 64), (2048, 1536, 576), (130, 250, 96), (129, 13, 40),
                                         (40, 96, 64), (64, 1536, 576), (1024, 4000, 128), (17, 1536, 576), (33, 250, 96),
                                         (100, 8192, 2048), (64, 14336, 4096)])
@@ -715,3 +732,46 @@ def test_decode_attention_of_a_request_does_not_depend_on_its_neighbours(dtype):
     assert torch.equal(run([1, 0])[1], alone[0])                 # beside a short request
     assert torch.equal(run([0, 2, 3, 1])[0], alone[0])           # beside a long one: twelve ranges instead of three
     assert torch.equal(run([3, 2])[0], run([3])[0])              # 257 keys: the second range holds one key
+
+
+@pytest.mark.parametrize("d,hq,hkv,n_out", [(64, 9, 3, 576), (64, 32, 8, 200), (48, 5, 1, 240), (16, 2, 2, 64), (128, 4, 2, 96), (32, 16, 16, 130)])
+@pytest.mark.parametrize("n_dec", [1, 8, 11, 16])
+def test_merge_and_output_projection_in_one_launch(d, hq, hkv, n_out, n_dec):
+    """The cluster kernel that merges the key ranges and projects (merge_proj.cu) against the merge kernel followed by
+    a float64 product: the merged rows must be the merge kernel's bfloat16 values exactly (a single differing bit in one
+    of them would be a hundred times the bound), and the K-slices must add up to the whole product."""
+    k = kernels()
+    from cisr_b200.parts.attention import DECODE_RANGE, decode_ranges
+    page = 16
+    i32 = lambda a: torch.as_tensor(np.asarray(list(a), dtype=np.int32), device=dev())
+    g = torch.Generator().manual_seed(d * hq + n_dec)
+    lens = [int(x) for x in torch.randint(1, 1500, (n_dec,), generator=g)]
+    lens[0] = 1400
+    n_pages = sum(-(-n // page) for n in lens)
+    kc = torch.randn(n_pages, hkv, page, d, generator=g).to(torch.bfloat16).to(dev())
+    vc = torch.randn(n_pages, hkv, page, d, generator=g).to(torch.bfloat16).to(dev())
+    table = np.full((n_dec, max(-(-n // page) for n in lens)), -1, dtype=np.int32)
+    at = 0
+    for r, n in enumerate(lens):
+        need = -(-n // page)
+        table[r, :need] = np.arange(at, at + need); at += need
+    q = (2 * torch.randn(n_dec, hq, d, generator=g)).to(torch.bfloat16).to(dev())
+    w = (torch.randn(n_out, hq * d, generator=g) / (hq * d) ** 0.5).to(torch.bfloat16).to(dev())
+    rows = torch.randperm(n_dec, generator=g).tolist()            # request i's token sits in row rows[i] of the step
+    q_rows = torch.empty_like(q); q_rows[rows] = q
+    n_splits = decode_ranges(max(lens))
+    if not k.merge_out_proj_ok(n_dec, hq, d, w):
+        pytest.skip("not a shape for the cluster kernel")
+    outs = {}
+    for merge in (True, False):
+        out = torch.full_like(q, float("nan"))
+        partial = torch.full((n_dec, hq, n_splits, d), float("nan"), device=dev()); stats = torch.full((n_dec, hq, n_splits, 2), float("nan"), device=dev())
+        k.attn_decode(q_rows, out, kc, vc, i32(range(n_dec)), i32(table), i32(range(n_dec)), n_dec, i32(rows), i32(lens), partial, stats,
+                      hq, hkv, page, d ** -0.5, None, DECODE_RANGE, n_splits, merge=merge)
+        outs[merge] = (out, partial, stats)
+    merged = outs[True][0]                                          # bfloat16 rows [token row, hq, d] from the merge kernel
+    assert torch.isnan(outs[False][0].float()).all()                # without the merge kernel `out` is not written
+    projected = torch.full((n_dec, n_out), float("nan"), device=dev())
+    k.merge_out_proj(outs[False][1], outs[False][2], n_splits, i32(range(n_dec)), i32(rows), n_dec, hq, d, w, projected)
+    ref = merged.double().reshape(n_dec, hq * d) @ w.double().T
+    close(projected, ref, 2e-6 * float(ref.abs().max()) + 1e-6, 1e-5, "merge + output projection")

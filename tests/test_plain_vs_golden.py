@@ -62,3 +62,25 @@ def test_greedy_takes_the_lowest_index_on_ties_and_inverse_cdf_walks_the_distrib
     assert pl.greedy(torch.tensor([1.0, 3.0, 3.0, 2.0])) == 1
     logits = torch.log(torch.tensor([0.1, 0.2, 0.3, 0.4]))
     assert [pl.sample_inverse_cdf(logits, 1.0, u) for u in (0.0, 0.09, 0.11, 0.59, 0.61, 0.999)] == [0, 0, 1, 2, 3, 3]
+
+
+def test_bfloat16_storage_twin_shows_what_a_model_does_to_rounding():
+    """plain_llama with `storage=bfloat16` rounds what a 16-bit mode stores (runtime/model.py:3-4) and keeps float64
+    arithmetic.  Its distance from the exact run is what the storage format alone costs a given model, with no engine
+    involved.  For the 384-wide tiny configuration that is small at a weight scale of one over the root of the width and
+    beyond the replay tests' bound at 0.08, where every matrix has a gain of 1.6: which is why that configuration is
+    tested at 0.05 (tests/test_replay_gpu.py)."""
+    import numpy as np
+    import replay
+    import tiny_models as tm
+
+    tokens = tm.random_tokens(tm.TINY_D, 200, 103)               # request "d" of the replay tests
+    worst = {}
+    for scale in (0.05, 0.08):
+        weights = tm.make_weights(tm.TINY_D, 14, scale=scale, bf16_exact=True)
+        exact = replay.plain_logits(tm.TINY_D, weights, tokens)
+        twin = replay.plain_logits(tm.TINY_D, weights, tokens, storage=torch.bfloat16)
+        worst[scale] = max(replay.relative_rms(twin[p], exact[p]) for p in range(len(tokens)))
+        assert not np.array_equal(twin, exact)
+    assert worst[0.05] < 0.5 * replay.RRMS16
+    assert worst[0.08] > replay.RRMS16

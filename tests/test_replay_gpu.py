@@ -13,7 +13,12 @@ import tiny_models as tm
 
 pytestmark = pytest.mark.gpu
 
-# configuration, seed of the weights, their scale (about one over the root of the width: a layer's gain near one)
+# configuration, seed of the weights, their scale (about one over the root of the width: a layer's gain near one).
+# tiny_d is 384 wide, so its scale is 0.05.  At 0.08 its matrices have a gain of 1.6 and the model amplifies the rounding
+# of values stored in bfloat16 beyond the bound of tests/replay.py by itself: plain_llama with bfloat16 storage and
+# float64 arithmetic, with no engine involved, is then up to 0.033 away from its exact self (request d, position 115),
+# and the engine measures 0.032 at that same row whichever kernels serve it (tensor-map, mma.sync or CUDA-core
+# attention; tcgen05, weight-streaming or library products).  test_plain_vs_golden.py holds that fact as a test.
 CASES = {"tiny_a": (tm.TINY_A, 11, 0.08), "tiny_b": (tm.TINY_B, 12, 0.08), "tiny_c": (tm.TINY_C, 13, 0.08),
          "tiny_d": (tm.TINY_D, 14, 0.05)}
 LENGTHS = {"a": 150, "b": 70, "c": 33, "d": 200, "e": 90, "f": 3, "g": 129, "h": 64, "i": 47, "j": 111}
