@@ -405,7 +405,7 @@ __device__ __forceinline__ void decode_slab(const Tile& tile, const uint32_t (&q
 // Each warp's result into the merge area: merge[warp][row][0..D) = unnormalised output, [D] = running max (base 2),
 // [D+1] = denominator.  `merge` is [4][16][D + 2] floats of shared memory that no warp still reads as a tile.
 __device__ __forceinline__ void warps_to_merge_area(float* merge, const float (&o)[ND][4], const float (&m_run)[2],
-                                                    const float (&l_run)[2], int warp, int lane, int rows, int stride = 16) {
+                                                    const float (&l_run)[2], int warp, int lane, int rows) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         float l = l_run[h];
@@ -413,7 +413,7 @@ __device__ __forceinline__ void warps_to_merge_area(float* merge, const float (&
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int row = (lane >> 2) + 8 * h;
         if (row >= rows) continue;                // a padding row of the 16-row tile: nobody reads it
-        float* dst = merge + ((size_t)warp * stride + row) * (D + 2);
+        float* dst = merge + ((size_t)warp * 16 + row) * (D + 2);
 #pragma unroll
         for (int i = 0; i < ND; ++i) {
             dst[i * 8 + 2 * (lane & 3)] = o[i][2 * h];
@@ -424,15 +424,15 @@ __device__ __forceinline__ void warps_to_merge_area(float* merge, const float (&
 }
 // Element d of query row g of the CTA: the four warps' results merged by log-sum-exp, in a fixed order.
 // Returns the numerator; m (base 2) and den are the row's running max and denominator.
-__device__ __forceinline__ float merged_element(const float* merge, int g, int d, float& m, float& den, int stride = 16) {
+__device__ __forceinline__ float merged_element(const float* merge, int g, int d, float& m, float& den) {
     m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, merge[((size_t)w * stride + g) * (D + 2) + D]);
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, merge[((size_t)w * 16 + g) * (D + 2) + D]);
     float num = 0.f;
     den = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-        const float* src = merge + ((size_t)w * stride + g) * (D + 2);
+        const float* src = merge + ((size_t)w * 16 + g) * (D + 2);
         const float wgt = src[D] == -INFINITY ? 0.f : exp2f(src[D] - m);
         num = fmaf(wgt, src[d], num);
         den = fmaf(wgt, src[D + 1], den);
@@ -442,13 +442,13 @@ __device__ __forceinline__ float merged_element(const float* merge, int g, int d
 // The CTA's result written as its key range's partial sum (the merge kernel works in natural logarithms).
 __device__ __forceinline__ void decode_finish(float* merge, const float (&o)[ND][4], const float (&m_run)[2], const float (&l_run)[2],
                                               float* __restrict__ partial, float* __restrict__ stats, size_t part_base,
-                                              int rows, int n_splits, int split, int tid, int stride = 16) {
-    warps_to_merge_area(merge, o, m_run, l_run, tid >> 5, tid & 31, rows, stride);
+                                              int rows, int n_splits, int split, int tid) {
+    warps_to_merge_area(merge, o, m_run, l_run, tid >> 5, tid & 31, rows);
     __syncthreads();
     for (int e = tid; e < rows * D; e += DEC_THREADS) {
         const int g = e / D, d = e - g * D;
         float m, den;
-        const float num = merged_element(merge, g, d, m, den, stride);
+        const float num = merged_element(merge, g, d, m, den);
         const size_t p = part_base + (size_t)g * n_splits + split;
         partial[p * D + d] = num;
         if (d == 0) { stats[2 * p] = m * LN2; stats[2 * p + 1] = den; }
@@ -620,9 +620,6 @@ __device__ __forceinline__ void stamp(int i) {
 
 // cluster: CTAs per cluster along the key ranges (1: none).  n_parts = n_splits / cluster partial sums per query head
 // remain; with one, the first CTA writes the finished rows to `out`, otherwise partial sums for the merge kernel.
-// per_cta (only without clusters): consecutive key ranges one CTA walks, blockIdx.z * per_cta onwards.  Each range is
-// still summed on its own (a fresh running softmax, its own partial sum), so the result is the same to the last bit
-// however the ranges are dealt out to CTAs; a large batch gets fewer, longer CTAs that way.
 __global__ void __launch_bounds__(DEC_THREADS, 3)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_cache,
@@ -630,11 +627,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const int* __restrict__ block_table, int table_width, const int* __restrict__ dec_req,
                        const int* __restrict__ q_start, const int* __restrict__ ctx_len, float* __restrict__ partial,
                        float* __restrict__ stats, int hq, int hkv, int page_size, float scale, int window, int split_size,
-                       int cluster, int n_parts, int per_cta, int row0, int* __restrict__ error) {
+                       int cluster, int n_parts, int row0, int* __restrict__ error) {
     CISR_TRACE_SCOPE(TRACE_ATTN_DECODE_TMA);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024-byte aligned
-    float* merge = reinterpret_cast<float*>(ring);                   // reused after a range's loop: [4][16][D + 2]
+    float* merge = reinterpret_cast<float*>(ring);                   // reused after the loop: [4][16][D + 2]
     bf16* Qs = reinterpret_cast<bf16*>(ring + 4 * (size_t)TMA_TILE_BYTES);         // [16][LDS]
     uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * LDS);     // [4]: a warp's tile has landed
     int* failed = reinterpret_cast<int*>(full + 4);
@@ -644,107 +641,69 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     pdl_trigger();
     const int group = hq / hkv;
     const int rows = min(16, group - row0);
-    int* pages = reinterpret_cast<int*>(gathered + (cluster > 1 ? (size_t)cluster * rows * ((D + cluster - 1) / cluster + 2) : 0));   // block table entries of the CTA's key ranges
-    const int slot = blockIdx.x, kvh = blockIdx.y;
+    int* pages = reinterpret_cast<int*>(gathered + (cluster > 1 ? (size_t)cluster * rows * ((D + cluster - 1) / cluster + 2) : 0));   // block table entries of the key range
+    const int slot = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int req = dec_req[slot];
     const int tok = q_start[req];
     const int ctx = ctx_len[req];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int* table = block_table + (size_t)req_slot[req] * table_width;
-    const size_t part_base = ((size_t)slot * hq + (size_t)kvh * group + row0) * n_parts;
-    unsigned char* stage = ring + (size_t)warp * TMA_TILE_BYTES;     // this warp's stage and its barrier
-    uint64_t* bar = full + warp;
-    const int box_rows = min(page_size, TK), boxes = TK / box_rows;
-    const float scale2 = scale * LOG2E;
-    const unsigned char* Ks = stage;
-    unsigned char* Vs = stage + NSUB * SUB_BYTES;
-    // A CTA that walks several ranges keeps the merge area apart from the stages ([4][rows][D + 2] floats behind the page
-    // list), so that the next range's first tiles are on their way while this range is merged and written out.
-    const int first_split = blockIdx.z * per_cta;
-    const int last_split = min(first_split + per_cta, n_parts * cluster);
-    const bool walking = per_cta > 1;
-    const int span_lo = first_split * split_size, span_hi = min(last_split * split_size, ctx);
-    const int span_first_page = span_lo / page_size;
-    const int span_pages = span_lo < span_hi ? (span_hi - 1) / page_size - span_first_page + 1 : 0;
-    const int merge_stride = walking ? rows : 16;
-    if (walking) merge = reinterpret_cast<float*>(pages + ((per_cta * split_size / page_size + 8 + 3) & ~3));
 
-    for (int i = tid; i < span_pages; i += DEC_THREADS) pages[i] = table[span_first_page + i];
+    int lo = split * split_size;                                     // a multiple of TK (checked by the launcher)
+    const int hi = min(lo + split_size, ctx);
+    if (window > 0) lo = max(lo, ctx - window);
+    const size_t part_base = ((size_t)slot * hq + (size_t)kvh * group + row0) * n_parts;
+    const bool empty = lo >= hi;              // nothing in this range (the same for every thread)
+    if (empty && cluster == 1) {              // the merge skips a zero denominator
+        pdl_wait();
+        for (int g = tid; g < rows; g += DEC_THREADS) {
+            const size_t p = part_base + (size_t)g * n_parts + split;
+            stats[2 * p] = -INFINITY; stats[2 * p + 1] = 0.f;
+        }
+        return;
+    }
+    float o[ND][4];
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < ND; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    if (tid == 0) *failed = 0;
+
+    if (!empty) {
+    const int base = lo & ~(TK - 1);          // tiles start on multiples of TK keys, so a tile is whole pages (or part of one)
+    const int n_tiles = (hi - base + TK - 1) / TK;
+    const int first_page = base / page_size;
+    for (int i = tid; i <= (hi - 1) / page_size - first_page; i += DEC_THREADS) pages[i] = table[first_page + i];
     if (tid == 0) {
-        *failed = 0;
         for (int w = 0; w < 4; ++w) mbar_init(full + w, 1);
         mbar_init_fence();
     }
-    __syncthreads();                          // the page list and the barriers are ready
+    __syncthreads();
     STAMP(1);
-    float o[ND][4];
-    float m_run[2], l_run[2];
-    uint32_t qf[KD][4];
-    bool waited = false;          // on the kernel before this one (once per CTA)
-    bool have_q = false;          // the query fragments are in registers (once per CTA)
-    bool fetched = false;         // this warp's first tile of the coming range is already requested
-    unsigned uses = 0;            // tiles this warp has received so far: the parity of its barrier
-    bool empty = true;
-    int split = first_split, lo = 0, hi = 0;
 
-    // Tile t of the range that starts at `base` into this warp's stage: lane b fetches box b (K or V, 64-column half,
-    // run of box_rows keys).
-    auto fetch = [&](int base, int hi, int t) {
+    // Tile t into this warp's stage: lane b fetches box b (K or V, 64-column half, run of box_rows keys).
+    unsigned char* stage = ring + (size_t)warp * TMA_TILE_BYTES;
+    uint64_t* bar = full + warp;
+    const int box_rows = min(page_size, TK), boxes = TK / box_rows;
+    auto fetch = [&](int t) {
         if (lane == 0) mbar_expect_tx(bar, (uint32_t)TMA_TILE_BYTES);
         __syncwarp();
         for (int b = lane; b < 2 * NSUB * boxes; b += 32) {
             const int i = b % boxes, sub = (b / boxes) % NSUB, is_v = b / (boxes * NSUB);
             const int kpos = base + t * TK + i * box_rows;
-            const int page = kpos < hi ? pages[kpos / page_size - span_first_page] : -1;
+            const int page = kpos < hi ? pages[kpos / page_size - first_page] : -1;
             const int row = page < 0 ? cache_rows : (page * hkv + kvh) * page_size + kpos % page_size;
             tma_load_2d(stage + (is_v * NSUB + sub) * SUB_BYTES + i * box_rows * 128, is_v ? &map_v : &map_k, sub * 64, row, bar);
         }
     };
-
-    for (; split < last_split; ++split) {
-    lo = split * split_size;                                         // a multiple of TK (checked by the launcher)
-    hi = min(lo + split_size, ctx);
-    if (window > 0) lo = max(lo, ctx - window);
-    empty = lo >= hi;                         // nothing in this range (the same for every thread)
-    if (empty && cluster == 1) {              // the merge skips a zero denominator
-        if (!waited) { pdl_wait(); waited = true; }
-        for (int g = tid; g < rows; g += DEC_THREADS) {
-            const size_t p = part_base + (size_t)g * n_parts + split;
-            stats[2 * p] = -INFINITY; stats[2 * p + 1] = 0.f;
-        }
-        continue;
-    }
-    m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
-#pragma unroll
-    for (int i = 0; i < ND; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-
-    if (!empty) {
-    const int base = lo & ~(TK - 1);          // tiles start on multiples of TK keys, so a tile is whole pages (or part of one)
-    const int n_tiles = (hi - base + TK - 1) / TK;
-    const int first_page = span_first_page;   // the page list starts at the CTA's first range
-
     // Older keys do not come from the kernel before this one, only the newest (position ctx - 1) does.  Every warp's
-    // first tile is requested now (unless the range before already did); in the tile that holds the newest key that
-    // one row arrives stale if this is before the wait below, and is fetched again, by ordinary loads, after it.
+    // first tile is requested now; in the tile that holds the newest key that one row arrives stale and is fetched
+    // again, by ordinary loads, once the kernel before has finished.
     const int newest = hi == ctx ? n_tiles - 1 : -1;
-    if (!fetched && warp < n_tiles) fetch(base, hi, warp);
-    fetched = false;
+    if (warp < n_tiles) fetch(warp);
     STAMP(2);
-    if (!waited) {
-        pdl_wait();
-        CISR_TRACE_WAITED();
-        waited = true;
-    }
+    pdl_wait();
+    CISR_TRACE_WAITED();
     STAMP(3);
-    const bool load_q = !have_q;
-    if (load_q) {
-        for (int c = tid; c < 16 * CHUNKS; c += DEC_THREADS) {
-            const int r = c / CHUNKS, ch = c - r * CHUNKS;
-            const bool ok = r < rows;
-            cp_async16(Qs + r * LDS + ch * 8, q + ((size_t)tok * hq + kvh * group + row0 + (ok ? r : 0)) * D + ch * 8, ok);
-        }
-        cp_async_commit();
-    }
     uint4 newest_k = make_uint4(0, 0, 0, 0), newest_v = newest_k;
     if (warp == newest && lane < NSUB * 8) {
         const int pos = ctx - 1, page = pages[pos / page_size - first_page];
@@ -754,25 +713,30 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             newest_v = __ldcg(reinterpret_cast<const uint4*>(v_cache + at));
         }
     }
-    if (load_q) {
-        cp_async_wait<0>();
-        __syncthreads();                                             // the query rows are in shared memory
-        STAMP(4);
-#pragma unroll
-        for (int kk = 0; kk < KD; ++kk)
-            ldmatrix_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
-        have_q = true;
+    for (int c = tid; c < 16 * CHUNKS; c += DEC_THREADS) {
+        const int r = c / CHUNKS, ch = c - r * CHUNKS;
+        const bool ok = r < rows;
+        cp_async16(Qs + r * LDS + ch * 8, q + ((size_t)tok * hq + kvh * group + row0 + (ok ? r : 0)) * D + ch * 8, ok);
     }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();                                                 // the query rows are in shared memory
+    STAMP(4);
 
-    bool lost = false;
+    uint32_t qf[KD][4];
+#pragma unroll
+    for (int kk = 0; kk < KD; ++kk)
+        ldmatrix_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
+    const float scale2 = scale * LOG2E;
+    const unsigned char* Ks = stage;
+    unsigned char* Vs = stage + NSUB * SUB_BYTES;
+
     for (int t = warp, it = 0; t < n_tiles; t += 4, ++it) {
-        if (!__all_sync(0xffffffffu, mbar_wait(bar, uses & 1))) {    // the lanes agree on whether the wait ran out
+        if (!__all_sync(0xffffffffu, mbar_wait(bar, it & 1))) {      // the lanes agree on whether the wait ran out
             if (lane == 0) { atomicExch(error, 3); *failed = 1; }
-            mbar_wait(bar, uses & 1);    // one more bounded chance for the copy to land before the stage is given up
-            lost = true;
+            mbar_wait(bar, it & 1);      // one more bounded chance for the copy to land before the stage is given up
             break;
         }
-        ++uses;
         if (it == 0) STAMP(5);
         const int k0 = base + t * TK;
         if (it == 0 && t == newest) {             // the newest key's row over the stale one the early copy brought
@@ -857,35 +821,19 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
         }
         __syncwarp();                                                // every lane has read the stage
-        if (t + 4 < n_tiles) fetch(base, hi, t + 4);
+        if (t + 4 < n_tiles) fetch(t + 4);
     }
-    if (walking && split + 1 < last_split) {
-        // this warp's stage is free: request its first tile of the next range before this range is merged and written
-        int nlo = (split + 1) * split_size;
-        const int nhi = min(nlo + split_size, ctx);
-        if (window > 0) nlo = max(nlo, ctx - window);
-        if (nlo < nhi) {
-            const int nbase = nlo & ~(TK - 1);
-            if (warp < (nhi - nbase + TK - 1) / TK) fetch(nbase, nhi, warp);
-            fetched = true;
-        }
-    }
-    (void)lost;
-    } else if (!waited) {
+    } else {
         pdl_wait();
-        waited = true;
     }
-    __syncthreads();          // every warp is done with its stage (the stages become the merge area), or with the merge area of the range before
+    __syncthreads();          // every warp is done with its stage: the stages become the merge area
     STAMP(6);
     if (cluster == 1) {
         if (*failed) return;  // a copy never arrived; the host reads the error flag
-        decode_finish(merge, o, m_run, l_run, partial, stats, part_base, rows, n_parts, split, tid, merge_stride);
+        decode_finish(merge, o, m_run, l_run, partial, stats, part_base, rows, n_parts, split, tid);
         STAMP(7);
-        continue;
+        return;
     }
-    break;                    // with clusters a CTA has one range: the exchange below
-    }
-    if (cluster == 1) return;
 
     // All-to-all over the cluster: CTA r finishes output columns [r * cols, (r + 1) * cols) of every query row, so each
     // CTA sends every other CTA that slice of its rows (and the rows' max and denominator).  A CTA without keys, or
@@ -1061,7 +1009,7 @@ CISR_EXPORT int cisr_attn_decode_tma_ok(int page_size, int split_size) {
 }
 
 #if HEAD_DIM % 64 == 0
-namespace { int* g_error = nullptr; bool g_clusters = false; int g_last_launches = 0; int g_ranges_per_cta = 0; }
+namespace { int* g_error = nullptr; bool g_clusters = false; int g_last_launches = 0; }
 
 // `error_flag`: one zeroed int in device memory that a kernel sets when a wait on a copy ran out.
 CISR_EXPORT int cisr_attn_tma_init(int* error_flag) {
@@ -1127,31 +1075,14 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
         break;
     }
     const int n_parts = n_splits / cluster;
-    // Without clusters a CTA may walk several consecutive ranges (each still summed on its own, so the result does not
-    // change): as many as it takes to bring the grid down to about three CTAs per SM, in powers of two.  Such a CTA
-    // holds the page entries of all its ranges and a merge area of its own ([4][rows][D + 2] floats).
-    int per_cta = 1;
-    if (cluster == 1) {
-        static int sms = 0;
-        if (!sms) { int device = 0; cudaGetDevice(&device); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device); }
-        if (g_ranges_per_cta > 0) per_cta = g_ranges_per_cta;
-        else while (per_cta < n_splits && (long long)n_dec * hkv * ((n_splits + per_cta - 1) / per_cta) > 3ll * sms) per_cta *= 2;
-        if (per_cta > n_splits) per_cta = n_splits;
-        while (per_cta > 1) {
-            const size_t need = TMA_SMEM_FIXED + sizeof(int) * (((size_t)per_cta * split_size / page_size + 8 + 3) & ~(size_t)3) +
-                                sizeof(float) * 4 * (size_t)rows_max * (D + 2);
-            if (need <= SMEM_CAP) { smem = need; break; }
-            per_cta /= 2;                     // tiny pages and very many ranges: fewer ranges per CTA
-        }
-    }
     cudaStream_t s = (cudaStream_t)stream;
     g_last_launches = (group + 15) / 16 + (((n_parts == 1 && cluster > 1) || !merge) ? 0 : 1);
     for (int row0 = 0; row0 < group; row0 += 16) {
-        status = launch_kernel_cluster(attn_decode_tma_kernel, dim3(n_dec, hkv, (n_splits + per_cta - 1) / per_cta), dim3(DEC_THREADS), smem, s,
-                                       g_pdl, cluster, map_k, map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
+        status = launch_kernel_cluster(attn_decode_tma_kernel, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), smem, s, g_pdl, cluster,
+                                       map_k, map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                        (int)cache_rows, req_slot, block_table, table_width,
                                        dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale, window, split_size,
-                                       cluster, n_parts, per_cta, row0, g_error);
+                                       cluster, n_parts, row0, g_error);
         if (status) return status;
     }
     if ((n_parts == 1 && cluster > 1) || !merge) return 0;
@@ -1165,10 +1096,6 @@ CISR_EXPORT int cisr_attn_trace_read(void* host, int bytes) { return (int)cudaMe
 
 // Kernels launched by the last cisr_attn_decode_tma call (the merge kernel is left out when one cluster covers all ranges).
 CISR_EXPORT int cisr_attn_decode_tma_launches() { return g_last_launches; }
-
-// Key ranges one CTA walks when no clusters are used: 0 lets the launcher choose (about three CTAs per SM), n > 0 fixes
-// it (tests compare 1, 2 and more: the output must be the same to the last bit).
-CISR_EXPORT void cisr_attn_set_ranges_per_cta(int n) { g_ranges_per_cta = n < 0 ? 0 : n; }
 
 // 0 turns the clusters off (every key range then writes its partial sum and the merge kernel runs).
 CISR_EXPORT void cisr_attn_set_clusters(int on) { g_clusters = on != 0; }

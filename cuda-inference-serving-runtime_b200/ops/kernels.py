@@ -230,15 +230,6 @@ def set_clusters(on: bool) -> None:
             lib.cisr_attn_set_clusters(int(on))
 
 
-def set_decode_ranges_per_cta(n: int) -> None:
-    """How many consecutive key ranges one CTA of the tensor-map decode attention walks: 0 lets the launcher choose (it
-    aims at about three CTAs per SM), n > 0 fixes it.  Each range is summed on its own whatever the choice, so the output
-    is the same to the last bit; tests use this to check exactly that."""
-    for lib in _attention_libs.values():
-        if lib._tensor_maps:
-            lib.cisr_attn_set_ranges_per_cta(int(n))
-
-
 def _error_flag() -> torch.Tensor:
     """One int on the device that a kernel sets when one of its bounded waits ran out."""
     flag = _error_state.get("flag")

@@ -19,8 +19,10 @@ from .linear import as_tensor, linear, linear_to_stream, norm_fusable
 
 
 # Keys per range of the split decode attention.  Ranges are [i * DECODE_RANGE, (i + 1) * DECODE_RANGE) in absolute
-# positions whatever else is in the batch, so the order in which a request's keys are summed depends only on its own
-# length: 256 keys are one tile for each of a CTA's four warps at head size 64, two at head size 128.
+# positions whatever else is in the step, so the order in which a request's keys are summed depends on its own length
+# alone: 256 keys are one tile for each of a CTA's four warps at head size 64, two at head size 128.  A large batch
+# would rather have fewer, longer ranges (at 64 requests of 4096 tokens the step is a twentieth slower for it); that is
+# the price of a sum that does not change with the neighbours.
 DECODE_RANGE = 256
 CLUSTER_MAX = 16           # key ranges of one request and head that one thread-block cluster can merge
 

@@ -177,3 +177,36 @@ def test_repeated_step_shapes_replay_from_a_graph_with_new_contents(model_dir, d
     report = stepper.graphs.report()
     assert report["shape_entries"] == 2 and report["hits"] >= 4
     assert sorted(g.replays for g in stepper.graphs.shapes.values()) == [2, 4]
+
+
+@pytest.mark.parametrize("dtype", ["float32"])
+def test_steps_of_one_shape_queued_behind_a_busy_device_keep_their_own_metadata(model_dir, dtype):
+    """Steps of a repeated shape run from one captured graph whose metadata sits in one pinned buffer.  When the host
+    queues several such steps without reading anything in between (prompt portions with nothing wanted) while the
+    device is still busy, a step's copy of that buffer has not run yet when the host prepares the next step: the
+    buffer may only be rewritten once its copy has left it, or earlier steps run with later steps' positions, pages
+    and tokens.  The device is kept busy by a spin kernel here so that the host does run ahead."""
+    from cisr_b200 import Model, StepEntry, Stepper
+
+    cfg, weights, path = model_dir
+    model = Model.from_pretrained(path, dtype=dtype)
+    stepper = Stepper(model, n_pages=64, page_size=8, max_slots=4, graph=True)
+    tokens = {k: tm.random_tokens(cfg, 61, 20 + i) for i, k in enumerate("abcd")}
+    reference = {k: replay.plain_logits(cfg, weights, t) for k, t in tokens.items()}
+    for k in tokens:
+        stepper.create(k)
+    # every request in portions of 12 tokens: the shape (12,) repeats, so from its second appearance it is a graph
+    stepper.step([StepEntry("a", tokens["a"][:12], [])])
+    stepper.step([StepEntry("b", tokens["b"][:12], [])])
+    torch.cuda.synchronize()
+    torch.cuda._sleep(int(0.2 * 1.9e9))              # about a tenth of a second of device time
+    order = [("c", 0), ("d", 0), ("a", 12), ("b", 12), ("c", 12), ("d", 12), ("a", 24), ("b", 24), ("c", 24), ("d", 24),
+             ("a", 36), ("b", 36), ("c", 36), ("d", 36), ("a", 48), ("b", 48), ("c", 48), ("d", 48)]
+    for k, at in order:                              # all queued while the device still spins
+        stepper.step([StepEntry(k, tokens[k][at:at + 12], [])])
+    assert stepper.graphs.report()["shape_entries"] >= 1
+    got = {}
+    for k in tokens:                                 # the last token of each: its logits depend on everything before
+        got[(k, 60)] = stepper.step([StepEntry(k, [tokens[k][60]], [0])]).cpu().numpy()[0].copy()
+    replay.compare(got, tokens, reference, dtype)
+    stepper.cache.check()

@@ -719,16 +719,6 @@ def test_decode_attention_of_a_request_does_not_depend_on_its_neighbours(dtype):
 
     alone = run([0])
     assert torch.isfinite(alone).all()
-    if dtype == torch.bfloat16:
-        # the tensor-map kernel deals several ranges to one CTA when the batch is large; each range is still summed on its
-        # own, so however they are dealt out the output is the same to the last bit
-        everyone = run([0, 1, 2, 3])
-        for per_cta in (1, 2, 3, 8, 64):
-            k.set_decode_ranges_per_cta(per_cta)
-            try:
-                assert torch.equal(run([0, 1, 2, 3]), everyone), per_cta
-            finally:
-                k.set_decode_ranges_per_cta(0)
     assert torch.equal(run([1, 0])[1], alone[0])                 # beside a short request
     assert torch.equal(run([0, 2, 3, 1])[0], alone[0])           # beside a long one: twelve ranges instead of three
     assert torch.equal(run([3, 2])[0], run([3])[0])              # 257 keys: the second range holds one key
