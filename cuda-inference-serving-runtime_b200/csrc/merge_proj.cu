@@ -24,8 +24,6 @@
 // columns; everything else keeps the separate merge kernel and the weight-streaming products.
 //
 // Parity: kernels/ops.cu:72-86 (merge_attention) followed by the output projection of runtime/model.py:114-115.
-#include <stdlib.h>
-
 #include "common.cuh"
 
 namespace {
@@ -41,7 +39,6 @@ struct MergeProjArgs {
     int hq; int dim; int heads_per_cta;
     const bf16* w; int n;                                          // [n, hq * dim]
     float* out;                                                    // [tokens, n]
-    int late_trigger;                                              // let the next kernel start only once the products are done
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -138,7 +135,7 @@ __global__ void __launch_bounds__(THREADS) merge_proj_kernel(const MergeProjArgs
         if (in_k && ok_lo) wl[i] = load_weights(row_lo + i * 32);
         if (in_k && ok_hi) wh[i] = load_weights(row_hi + i * 32);
     }
-    if (!a.late_trigger) pdl_trigger();
+    pdl_trigger();
     pdl_wait();
     CISR_TRACE_WAITED();
 
@@ -343,9 +340,6 @@ CISR_EXPORT int cisr_merge_proj(const float* partial, const float* stats, int n_
     MergeProjArgs a;
     a.partial = partial; a.stats = stats; a.n_splits = n_splits; a.dec_req = dec_req; a.q_start = q_start; a.n_dec = n_dec;
     a.hq = hq; a.dim = dim; a.heads_per_cta = per; a.w = (const bf16*)w; a.n = n; a.out = out;
-    static int late = -1;
-    if (late < 0) { const char* e = getenv("CISR_MERGE_PROJ_LATE"); late = e && e[0] == '1'; }
-    a.late_trigger = late;
     const int ranks = (hq + per - 1) / per;
     cudaStream_t s = (cudaStream_t)stream;
     return n_dec <= 8 ? launch<1>(a, ranks, s) : launch<2>(a, ranks, s);

@@ -37,7 +37,9 @@ enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ROPE = 2 };
 #ifndef SKINNY_KS
 #define SKINNY_KS 8
 #endif
-constexpr int MAXC = SKINNY_MAXC;     // chunks of 32 k whose weights a warp holds in registers at once
+// Chunks of 32 k whose weights a warp holds in registers at once: SKINNY_MAXC, or half of it where that covers the
+// warp's whole share of K (kernels this brief pay for every instruction they fetch, also for the predicated-off ones).
+constexpr int MAXC_FULL = SKINNY_MAXC, MAXC_HALF = (SKINNY_MAXC + 1) / 2;
 bool g_pdl = false;
 
 struct SkinnyArgs {
@@ -138,7 +140,7 @@ __device__ void stage_tokens(const SkinnyArgs& a, bf16* hs, int ldh, const float
     }
 }
 
-template <int MT, int EPI>
+template <int MT, int EPI, int MAXC>
 __global__ void __launch_bounds__(512) skinny_kernel(const SkinnyArgs a) {
     CISR_TRACE_SCOPE(EPI == EPI_ROPE ? TRACE_SKINNY_ROPE : EPI == EPI_SWIGLU ? TRACE_SKINNY_SWIGLU : TRACE_SKINNY_PLAIN);
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -296,6 +298,17 @@ __global__ void __launch_bounds__(512) skinny_kernel(const SkinnyArgs a) {
     }
 }
 
+template <int MT, int EPI, int MAXC>
+int launch_sized(const SkinnyArgs& a, int grid, size_t smem, cudaStream_t s) {
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_kernel<MT, EPI, MAXC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    return launch_kernel(skinny_kernel<MT, EPI, MAXC>, dim3(grid), dim3(32 * a.rt * a.ks), smem, s, g_pdl, a);
+}
+
 template <int MT, int EPI>
 int launch_epilogue(SkinnyArgs& a, cudaStream_t s) {
     int grid;
@@ -314,13 +327,9 @@ int launch_epilogue(SkinnyArgs& a, cudaStream_t s) {
     const size_t sums_bytes = sizeof(float) * (size_t)(MT * 8) * a.k;
     a.sums_in_smem = !a.act && smem + sums_bytes <= 100 * 1024;   // keep two CTAs per SM
     if (a.sums_in_smem) smem += sums_bytes;
-    static size_t configured = 48 * 1024;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(skinny_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = smem;
-    }
-    return launch_kernel(skinny_kernel<MT, EPI>, dim3(grid), dim3(32 * a.rt * a.ks), smem, s, g_pdl, a);
+    const int per_warp = ((a.k + 31) / 32 + a.ks - 1) / a.ks;         // chunks of K each warp multiplies
+    if (per_warp <= MAXC_HALF) return launch_sized<MT, EPI, MAXC_HALF>(a, grid, smem, s);
+    return launch_sized<MT, EPI, MAXC_FULL>(a, grid, smem, s);
 }
 
 template <int MT>

@@ -380,7 +380,7 @@ MERGE_PROJ_MAX_BYTES = 8 << 20     # larger output projections are bandwidth-bou
 def merge_out_proj_ok(n_dec: int, hq: int, dim: int, w: torch.Tensor) -> bool:
     """Whether `merge_out_proj` takes the shape: bfloat16 weights [N, hq * dim] of a latency-bound size, at most 16 tokens,
     head slices of at most 256 columns in at most 16 CTAs; and thread-block clusters in the attention kernel off."""
-    return (w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] == hq * dim and w.numel() * 2 < MERGE_PROJ_MAX_BYTES
+    return (0 < n_dec <= 16 and w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] == hq * dim and w.numel() * 2 < MERGE_PROJ_MAX_BYTES
             and not _cluster_state["on"] and os.environ.get("CISR_MERGE_PROJ", "1") != "0"
             and _merge_proj().cisr_merge_proj_heads_per_cta(n_dec, hq, dim, w.shape[1]) > 0)
 
