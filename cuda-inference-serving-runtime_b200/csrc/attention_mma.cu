@@ -722,6 +722,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     cp_async_wait<0>();
     __syncthreads();                                                 // the query rows are in shared memory
     STAMP(4);
+    CISR_TRACE_MARK(0);
 
     uint32_t qf[KD][4];
 #pragma unroll
@@ -737,7 +738,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             mbar_wait(bar, it & 1);      // one more bounded chance for the copy to land before the stage is given up
             break;
         }
-        if (it == 0) STAMP(5);
+        if (it == 0) { STAMP(5); CISR_TRACE_MARK(1); }
         const int k0 = base + t * TK;
         if (it == 0 && t == newest) {             // the newest key's row over the stale one the early copy brought
             if (lane < NSUB * 8) {
@@ -828,6 +829,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     __syncthreads();          // every warp is done with its stage: the stages become the merge area
     STAMP(6);
+    CISR_TRACE_MARK(2);
     if (cluster == 1) {
         if (*failed) return;  // a copy never arrived; the host reads the error flag
         decode_finish(merge, o, m_run, l_run, partial, stats, part_base, rows, n_parts, split, tid);

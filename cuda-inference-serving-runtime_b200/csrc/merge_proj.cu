@@ -39,6 +39,7 @@ struct MergeProjArgs {
     int hq; int dim; int heads_per_cta;
     const bf16* w; int n;                                          // [n, hq * dim]
     float* out;                                                    // [tokens, n]
+    int accumulate;                                                // out += the product (out is the residual stream)
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -144,6 +145,14 @@ __global__ void __launch_bounds__(THREADS) merge_proj_kernel(const MergeProjArgs
     // (One element per thread is requested ahead and the code stays short: a kernel this brief pays for every
     // instruction-cache line it touches.)
     const int pairs = a.n_dec * heads, total = pairs * a.dim;
+    // adding into `out` (the residual stream): what the thread's first output element holds now is requested with them
+    const int per_out = (FT + ranks - 1) / ranks;
+    float* first_out = nullptr;
+    float there = 0.f;
+    if (a.accumulate && tid < per_out * a.n_dec) {
+        const int fr = tid / a.n_dec, i = tid - fr * a.n_dec, row = rank * per_out + fr, f = blockIdx.x * FT + row;
+        if (row < FT && f < a.n) { first_out = a.out + (size_t)a.q_start[a.dec_req[i]] * a.n + f; there = *first_out; }
+    }
     float pre[SB];
     {
         const int e = tid;
@@ -271,7 +280,9 @@ __global__ void __launch_bounds__(THREADS) merge_proj_kernel(const MergeProjArgs
         if (row >= FT || f >= a.n) continue;
         float sum = 0.f;
         for (int c = 0; c < ranks; ++c) sum += part[((size_t)c * per + fr) * mw + i];       // in the order of the CTAs
-        a.out[(size_t)a.q_start[a.dec_req[i]] * a.n + f] = sum;
+        float* dst = a.out + (size_t)a.q_start[a.dec_req[i]] * a.n + f;
+        if (a.accumulate) sum += dst == first_out ? there : *dst;
+        *dst = sum;
     }
 }
 
@@ -334,12 +345,12 @@ CISR_EXPORT int cisr_merge_proj_heads_per_cta(int n_dec, int hq, int dim, int k)
 // out[q_start[dec_req[i]], :] (float [tokens, n]) = merge over the key ranges of request i's partial sums, times w^T.
 // Returns -2 for shapes it does not take (the caller then runs the merge kernel and the product apart).
 CISR_EXPORT int cisr_merge_proj(const float* partial, const float* stats, int n_splits, const int* dec_req, const int* q_start,
-                                int n_dec, int hq, int dim, const void* w, int n, int k, float* out, void* stream) {
+                                int n_dec, int hq, int dim, const void* w, int n, int k, float* out, int accumulate, void* stream) {
     const int per = cisr_merge_proj_heads_per_cta(n_dec, hq, dim, k);
     if (!per || n <= 0 || n_splits <= 0 || (((uintptr_t)w) & 15) || (k % 8)) return -2;
     MergeProjArgs a;
     a.partial = partial; a.stats = stats; a.n_splits = n_splits; a.dec_req = dec_req; a.q_start = q_start; a.n_dec = n_dec;
-    a.hq = hq; a.dim = dim; a.heads_per_cta = per; a.w = (const bf16*)w; a.n = n; a.out = out;
+    a.hq = hq; a.dim = dim; a.heads_per_cta = per; a.w = (const bf16*)w; a.n = n; a.out = out; a.accumulate = accumulate != 0;
     const int ranks = (hq + per - 1) / per;
     cudaStream_t s = (cudaStream_t)stream;
     return n_dec <= 8 ? launch<1>(a, ranks, s) : launch<2>(a, ranks, s);

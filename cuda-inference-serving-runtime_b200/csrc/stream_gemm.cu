@@ -47,6 +47,7 @@ struct StreamArgs {
     const float* cos_t; const float* sin_t; int rot_half; int interleaved; bf16* q_out; bf16* k_cache; bf16* v_cache;
     const int* positions; const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size;
     int hq; int hkv; int dim;
+    int accumulate;                                // PLAIN: out += product
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -305,7 +306,10 @@ stream_kernel(const __grid_constant__ CUtensorMap map_w, const StreamArgs a, int
             for (int e = tid; e < a.block_rows * a.m; e += 32 * CONSUMERS) {
                 const int mrow = e / a.block_rows, lr = e - mrow * a.block_rows;
                 const int f = block * a.block_rows + lr;
-                if (f < a.n) a.out_f32[(size_t)mrow * a.n + f] = summed(lr, mrow);
+                if (f < a.n) {
+                    float* dst = a.out_f32 + (size_t)mrow * a.n + f;
+                    *dst = a.accumulate ? *dst + summed(lr, mrow) : summed(lr, mrow);
+                }
             }
         } else if (usable && EPI == EPI_SWIGLU) {
             const int feats = a.block_rows / 2;                    // a row tile is 8 gate rows then their 8 up rows
@@ -456,7 +460,7 @@ CISR_EXPORT int cisr_stream_gemm(const void* w, int n, int k, const void* act, c
                                  const float* sin_t, int rot_half, int interleaved, void* q_out, void* k_cache,
                                  void* v_cache, const int* positions, const int* token_req, const int* req_slot,
                                  const int* block_table, int table_width, int page_size, int hq, int hkv, int dim,
-                                 void* stream) {
+                                 int accumulate, void* stream) {
     if (m <= 0) return 0;
     if (!g_encode || !g_error) return -13;
     if (m > 16 || k % 8 || k <= 0 || n <= 0 || ((uintptr_t)w & 15)) return -2;
@@ -468,7 +472,7 @@ CISR_EXPORT int cisr_stream_gemm(const void* w, int n, int k, const void* act, c
     StreamArgs a;
     a.n = n; a.k = k; a.act = (const bf16*)act; a.x = x; a.delta = delta; a.norm_w = norm_w;
     a.norm_w_bf16 = norm_w_dtype == CISR_BF16; a.eps = eps; a.x_out = x_out; a.rows = rows; a.m = m;
-    a.block_rows = 0; a.n_blocks = 0; a.stages = 0;
+    a.block_rows = 0; a.n_blocks = 0; a.stages = 0; a.accumulate = accumulate != 0 && epilogue == EPI_PLAIN;
     a.out_f32 = out_f32; a.out_bf16 = (bf16*)out_bf16; a.inter = inter; a.cos_t = cos_t; a.sin_t = sin_t;
     a.rot_half = rot_half; a.interleaved = interleaved; a.q_out = (bf16*)q_out; a.k_cache = (bf16*)k_cache;
     a.v_cache = (bf16*)v_cache; a.positions = positions; a.token_req = token_req; a.req_slot = req_slot;

@@ -35,15 +35,29 @@ RING_SLOTS = 4
 
 
 @contextlib.contextmanager
-def no_collection():
-    """No automatic garbage collection inside: destroying an older CUDA graph (a captured step of a stepper that is no
+def capturing(graph: "torch.cuda.CUDAGraph", pool=None):
+    """Capture what runs inside into `graph`, on a stream of its own.  `pool`: the memory pool its buffers come from; the
+    graphs of one stepper share one (they replay one after the other on one stream, and each keeps what it returns
+    referenced), so a later capture reuses the intermediate buffers of the earlier ones instead of asking the driver
+    for its own.
+
+    No automatic garbage collection inside: destroying an older CUDA graph (a captured step of a stepper that is no
     longer referenced, found by a collection that an allocation happens to trigger) is not permitted while a stream is
-    capturing and would invalidate the capture."""
-    gc.collect()
+    capturing and would invalidate the capture.  And none of torch.cuda.graph's housekeeping before it (a full
+    collection and an emptied allocator cache per capture: about a tenth of a second with a large cache pool resident,
+    which a server pays whenever a new batch or context bucket appears in the middle of its work)."""
     was_enabled = gc.isenabled()
     gc.disable()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
     try:
-        yield
+        with torch.cuda.stream(stream):
+            graph.capture_begin(pool=pool)
+            try:
+                yield
+            finally:
+                graph.capture_end()
+        torch.cuda.current_stream().wait_stream(stream)
     finally:
         if was_enabled:
             gc.enable()
@@ -111,6 +125,7 @@ class DecodeGraph:
             for name, arr in plan.arrays.items():
                 self.h(f"plan{i}.{name}")[:np.asarray(arr).size] = np.asarray(arr, dtype=np.int32).reshape(-1)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.pool = None                  # the memory pool to capture into (the owner of the graphs shares one among them)
         self.logits: Optional[torch.Tensor] = None
         self.tokens = torch.zeros(rows, dtype=torch.int32, device=device)
         # every replay also leaves its tokens, and the kernels' error flag, in the next slot of a small ring, so the host
@@ -201,20 +216,22 @@ class DecodeGraph:
             kernels.decode_advance(self.d("token_ids"), self.d("positions"), self.d("ctx_len"), self.d("counter"),
                                    self.tokens, self.d("live"), ring=self.ring, step_index=self.step_index)
 
-    def capture(self) -> None:
-        """Warm up once outside the graph (library set-up, kernel attributes), then capture."""
-        stream = torch.cuda.Stream()
-        stream.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(stream):
-            self._run(advance=False)
-        torch.cuda.current_stream().wait_stream(stream)
-        torch.cuda.synchronize()
+    def capture(self, warm_up: bool = True) -> None:
+        """Warm up once outside the graph (library set-up, kernel attributes), then capture.  `warm_up=False`: a graph
+        for the same number of rows was captured before, so the same kernels have run already."""
+        if warm_up:
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                self._run(advance=False)
+            torch.cuda.current_stream().wait_stream(stream)
+            torch.cuda.synchronize()
         before = dict(kernels.LAUNCHES)
         self.graph = torch.cuda.CUDAGraph()
         pdl = os.environ.get("CISR_PDL", "1") != "0"
         kernels.set_pdl(pdl)        # inside the graph a kernel may fetch its weights while the one before it still runs
         try:
-            with no_collection(), torch.cuda.graph(self.graph):
+            with capturing(self.graph, self.pool):
                 self._run(advance=True)
         finally:
             kernels.set_pdl(False)
@@ -247,6 +264,7 @@ class ShapeGraph:
         ints = 4 * tokens + 8 * len(q_lens) + plan_ints + n_rows * 8 + 2 * capacity * max(1, len(cache.page_groups)) + 256
         self.static = StaticMeta(stepper.model.device, ints, capacity, ctx_bucket)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.pool = None
         self.logits: Optional[torch.Tensor] = None
         self.replays = 0
         self.launches = {"own": 0, "library": 0}
@@ -271,7 +289,7 @@ class ShapeGraph:
             self.graph = torch.cuda.CUDAGraph()
             kernels.set_pdl(os.environ.get("CISR_PDL", "1") != "0")
             try:
-                with no_collection(), torch.cuda.graph(self.graph):
+                with capturing(self.graph, self.pool):
                     self._run(ctx, update_views)
             finally:
                 kernels.set_pdl(False)
@@ -290,6 +308,8 @@ class DecodeGraphs:
         self.shapes: "OrderedDict[tuple, ShapeGraph]" = OrderedDict()
         self.seen: Dict[tuple, int] = {}
         self.hits = self.misses = self.evictions = 0
+        self.pool = torch.cuda.graph_pool_handle() if torch.cuda.is_available() else None
+        self.warmed_rows: set = set()
 
     def get(self, n_rows: int, max_ctx: int) -> Tuple[DecodeGraph, bool]:
         key = (bucket_of(n_rows), context_bucket_of(max_ctx))
@@ -300,11 +320,19 @@ class DecodeGraphs:
             return graph, False
         self.misses += 1
         graph = DecodeGraph(self.stepper, *key)
+        graph.pool = self.pool
         self.graphs[key] = graph
         while len(self.graphs) > self.capacity:
             self.graphs.popitem(last=False)
             self.evictions += 1
         return graph, True
+
+    def first_of_its_rows(self, graph: DecodeGraph) -> bool:
+        """Whether no graph of this many rows was captured here before (then its kernels have not all run yet, and the
+        capture is preceded by a plain run).  Asked once per graph, right before its capture."""
+        first = graph.rows not in self.warmed_rows
+        self.warmed_rows.add(graph.rows)
+        return first
 
     def shape(self, q_lens: Tuple[int, ...], n_rows: int, max_decode_ctx: int) -> Optional[ShapeGraph]:
         """The graph of a step shape, from the second time the shape is seen (a shape seen once is not worth a capture)."""
@@ -321,6 +349,7 @@ class DecodeGraphs:
             self.seen.clear()
         self.misses += 1
         graph = ShapeGraph(self.stepper, q_lens, n_rows, key[2])
+        graph.pool = self.pool
         self.shapes[key] = graph
         while len(self.shapes) > self.capacity:
             self.shapes.popitem(last=False)

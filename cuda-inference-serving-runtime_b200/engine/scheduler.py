@@ -38,7 +38,7 @@ RESERVE_MODES = ("full", "lazy")
 ENDED = ("finished", "cancelled")
 
 
-@dataclass
+@dataclass(eq=False)                     # a request is itself, not its fields: membership tests and removals go by identity
 class Request:
     key: str
     prompt: list

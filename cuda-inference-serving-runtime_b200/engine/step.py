@@ -197,7 +197,7 @@ class Stepper:
                    extra.get("seed", 0), extra.get("counter", 0), updates)
         graph.upload()
         if fresh:
-            graph.capture()
+            graph.capture(warm_up=self.graphs.first_of_its_rows(graph))
         self._before_replay(graph)
         graph.replay()
         commit_step(cache, entries)

@@ -156,7 +156,22 @@ def compile_library(source_name: str, defines: Optional[Mapping[str, object]] = 
     os.replace(tmp, target)
     if verbose:
         print(f"[cisr_b200] built {target.name} in {time.time() - start:.1f} s", file=sys.stderr, flush=True)
+    _drop_superseded(target)
     return target
+
+
+def _drop_superseded(target: Path) -> None:
+    """Earlier builds of the same source with the same definitions (another digest: an edited source) are never loaded
+    again; remove them so the build folder holds one library per kernel.  A process that still has one open keeps it
+    (the file lives until it is closed)."""
+    stem, _, digest = target.stem.rpartition("_")
+    for other in target.parent.glob(f"{stem}_*.so"):
+        rest = other.stem[len(stem) + 1:]
+        if other != target and len(rest) == len(digest) and all(c in "0123456789abcdef" for c in rest):
+            try:
+                other.unlink()
+            except OSError:
+                pass
 
 
 def load_library(source_name: str, defines: Optional[Mapping[str, object]] = None, extra: Sequence[str] = ()) -> ctypes.CDLL:

@@ -35,7 +35,14 @@ def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current stream's handle.  Every launch asks for it, so it takes the short way where torch has one (a tenth of
+    the time of building a Stream object, which showed in steps that launch hundreds of kernels from the host)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -386,15 +393,16 @@ def merge_out_proj_ok(n_dec: int, hq: int, dim: int, w: torch.Tensor) -> bool:
 
 
 def merge_out_proj(partial: torch.Tensor, stats: torch.Tensor, n_splits: int, dec_req: torch.Tensor, q_start: torch.Tensor,
-                   n_dec: int, hq: int, dim: int, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+                   n_dec: int, hq: int, dim: int, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
     """out[row of request i] (float [tokens, N]) = (log-sum-exp merge of request i's key ranges, rounded to bfloat16) @ w^T:
-    the merge kernel and the output projection of a decode step in one launch of a thread-block cluster."""
+    the merge kernel and the output projection of a decode step in one launch of a thread-block cluster.  With
+    `accumulate` the product is added to what `out` holds (the residual stream)."""
     _need(partial, torch.float32, "partial"); _need(stats, torch.float32, "stats"); _need(w, torch.bfloat16, "w", 2)
     _need(out, torch.float32, "out", 2); _need(dec_req, torch.int32, "dec_req", 1); _need(q_start, torch.int32, "q_start", 1)
     if partial.numel() < n_dec * hq * n_splits * dim or stats.numel() < n_dec * hq * n_splits * 2 or out.shape[1] != w.shape[0]:
         raise KernelError("merge_out_proj: shapes disagree")
     status = _merge_proj().cisr_merge_proj(_p(partial), _p(stats), n_splits, _p(dec_req), _p(q_start), n_dec, hq, dim, _p(w),
-                                           w.shape[0], w.shape[1], _p(out), _stream())
+                                           w.shape[0], w.shape[1], _p(out), int(bool(accumulate)), _stream())
     _check(status, "merge_out_proj")
     return out
 
@@ -557,7 +565,8 @@ def skinny_ok(tokens: int, w: torch.Tensor) -> bool:
 def skinny_gemm(w: torch.Tensor, tokens: int, *, act: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None,
                 delta: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
                 x_out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None, epilogue: int = EPI_PLAIN,
-                out: Optional[torch.Tensor] = None, rope: Optional[dict] = None, kind: str = "auto") -> None:
+                out: Optional[torch.Tensor] = None, rope: Optional[dict] = None, kind: str = "auto",
+                accumulate: bool = False) -> None:
     """out = prologue(input) @ w^T with a fused epilogue; see csrc/skinny_gemm.cu and csrc/stream_gemm.cu.
 
     `kind`: "latency" (skinny_gemm.cu: a CTA per 16 output rows, weights straight to registers), "stream"
@@ -566,7 +575,7 @@ def skinny_gemm(w: torch.Tensor, tokens: int, *, act: Optional[torch.Tensor] = N
 
     Input is either `act` (bfloat16 [tokens, K]) or the norm prologue (`x`, optional `delta`, `norm_w`, `eps`,
     optional `x_out` receiving x + delta, optional `rows` picking rows of x).  PLAIN writes float `out`
-    [tokens, N]; SWIGLU writes bfloat16 `out` [tokens, N / 2]; ROPE takes the `rope` dict (cos, sin, rot_half,
+    [tokens, N], or with `accumulate` adds the product to what `out` holds (the residual stream); SWIGLU writes bfloat16 `out` [tokens, N / 2]; ROPE takes the `rope` dict (cos, sin, rot_half,
     interleaved, q_out, k_cache, v_cache, positions, token_req, req_slot, block_table, page_size, hq, hkv, dim).
     """
     _need(w, torch.bfloat16, "w", 2)
@@ -611,7 +620,9 @@ def skinny_gemm(w: torch.Tensor, tokens: int, *, act: Optional[torch.Tensor] = N
             int(bool(r.get("interleaved", False))), _p(r.get("q_out")), _p(r.get("k_cache")), _p(r.get("v_cache")),
             _p(r.get("positions")), _p(r.get("token_req")), _p(r.get("req_slot")), _p(r.get("block_table")),
             r["block_table"].shape[1] if rope else 0, int(r.get("page_size", 0)), int(r.get("hq", 0)), int(r.get("hkv", 0)),
-            int(r.get("dim", 0)), _stream())
+            int(r.get("dim", 0)), int(bool(accumulate)), _stream())
+    if accumulate and epilogue != EPI_PLAIN:
+        raise KernelError("skinny_gemm: only the plain epilogue adds into its output")
     if kind not in ("auto", "latency", "stream"):
         raise KernelError(f"unknown kind {kind!r}")
     if kind == "stream" or (kind == "auto" and tokens <= STREAM_MAX_TOKENS and w.numel() * 2 >= STREAM_MIN_BYTES):
@@ -797,7 +808,7 @@ _DESCRIBE = {
     "attn_prefill": lambda q, out, k_cache, *rest, **kw: (int(q.shape[0]), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2])),
     "attn_decode": lambda q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, *rest, **kw:
         (int(n_dec), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2]), bool(kw.get("merge", True))),
-    "merge_out_proj": lambda partial, stats, n_splits, dec_req, q_start, n_dec, hq, dim, w, out:
+    "merge_out_proj": lambda partial, stats, n_splits, dec_req, q_start, n_dec, hq, dim, w, out, **kw:
         (int(n_dec), int(w.shape[0]), int(w.shape[1]), int(n_splits)),
     "sample": lambda logits, *rest, **kw: (int(logits.shape[0]), int(logits.shape[1])),
     "decode_advance": lambda *a, **kw: (),

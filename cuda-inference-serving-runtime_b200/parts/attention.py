@@ -15,7 +15,7 @@ import torch
 from ..config.spec import CacheUse
 from ..ops import kernels
 from .base import MIXERS, POSITIONS, Mixer, TensorNeed, build_part, register
-from .linear import as_tensor, linear, linear_to_stream, norm_fusable
+from .linear import stream_target, as_tensor, linear, linear_to_stream, norm_fusable
 
 
 # Keys per range of the split decode attention.  Ranges are [i * DECODE_RANGE, (i + 1) * DECODE_RANGE) in absolute
@@ -162,6 +162,11 @@ class GQAAttention(Mixer):
                                 ctx.ctx_len, partial, stats, hq, hkv, cache.page_size, self.scale, self.window,
                                 DECODE_RANGE, n_splits, merge=not fused)
             if fused:
+                x = stream_target(h0, tokens, self.hidden)
+                if x is not None:     # straight into the residual stream
+                    kernels.merge_out_proj(partial, stats, n_splits, plan["dec_req"], ctx.q_start, n_decode, hq, dim, self.o, x,
+                                           accumulate=True)
+                    return None
                 projected = torch.empty((tokens, self.hidden), dtype=torch.float32, device=device)
                 return kernels.merge_out_proj(partial, stats, n_splits, plan["dec_req"], ctx.q_start, n_decode, hq, dim, self.o, projected)
         return linear_to_stream(out.view(tokens, hq * dim), self.o, h0)

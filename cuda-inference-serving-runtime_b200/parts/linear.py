@@ -38,17 +38,33 @@ def as_tensor(h) -> torch.Tensor:
     return h.materialize_once() if isinstance(h, PendingNorm) else h
 
 
+def stream_target(h, tokens: int, width: int):
+    """The residual stream's own tensor, when a product may add its result to it in place: `h` is the part's input as a
+    `PendingNorm` that is resolved by now (the norm has run, here or inside a product, so `h.stream.x` holds x + the
+    output before and nothing is pending), float, contiguous and [tokens, width].  Otherwise None."""
+    from .base import PendingNorm
+    if not (isinstance(h, PendingNorm) and h.resolved and h.stream.pending is None):
+        return None
+    x = h.stream.x
+    if x.dtype != torch.float32 or x.shape != (tokens, width) or not x.is_contiguous():
+        return None
+    return x
+
+
 def linear_to_stream(a: torch.Tensor, w: torch.Tensor, h):
     """The last product of a sub-block, whose result the block adds to the residual stream: returns the float
     product for the block to add, or None after adding it to the stream in place.
 
-    In place needs the stream's current tensor, which a part has when its input came as a `PendingNorm` that is
-    resolved by now (the norm has run, so `h.stream.x` already holds x + the output before), and a product kernel
-    with the add as its epilogue (the tcgen05 product).  The sum is the same single float add per element that the
-    next norm would otherwise make, so the logits do not change with the path."""
-    from .base import PendingNorm
-    if (isinstance(h, PendingNorm) and h.resolved and h.stream.pending is None and kernels.tcgen05_ok(a, w)
-            and h.stream.x.dtype == torch.float32 and h.stream.x.shape == (a.shape[0], w.shape[0]) and h.stream.x.is_contiguous()):
-        kernels.gemm_tcgen05(a, w, h.stream.x, accumulate=True)
-        return None
+    In place needs the stream's current tensor (`stream_target`) and a product kernel with the add as its epilogue:
+    the weight-streaming kernels for few tokens, the tcgen05 product for many.  The sum is the same single float add
+    per element that the next norm would otherwise make, so the logits do not change with the path; the norm after
+    it then reads one tensor instead of two."""
+    x = stream_target(h, a.shape[0], w.shape[0])
+    if x is not None and a.shape[0] > 0:
+        if kernels.skinny_ok(a.shape[0], w) and a.dtype == torch.bfloat16:
+            kernels.skinny_gemm(w, a.shape[0], act=a, epilogue=kernels.EPI_PLAIN, out=x, accumulate=True)
+            return None
+        if kernels.tcgen05_ok(a, w):
+            kernels.gemm_tcgen05(a, w, x, accumulate=True)
+            return None
     return linear(a, w)

@@ -34,3 +34,14 @@ def test_an_edit_to_an_included_file_renames_the_library(tmp_path, monkeypatch):
         before = build.library_path("top.cu", {"D": 1})
         (tmp_path / edited).write_text(text)
         assert build.library_path("top.cu", {"D": 1}) != before, edited
+
+
+def test_a_new_build_removes_the_superseded_ones_of_the_same_kernel_only(tmp_path):
+    keep = ["libcisr_gemm_0123456789abcdef.so", "libcisr_gemm_cisr_trace1_0123456789abcdef.so", "libcisr_gemm_wide_0123456789abcdef.so",
+            "libcisr_attention_head_dim128_0123456789abcdef.so"]
+    drop = ["libcisr_gemm_fedcba9876543210.so", "libcisr_gemm_00000000aaaaaaaa.so"]
+    for name in keep + drop + ["libcisr_attention_head_dim16_0123456789abcdef.so", "libcisr_attention_head_dim16_ffffffffffffffff.so"]:
+        (tmp_path / name).write_bytes(b"")
+    build._drop_superseded(tmp_path / "libcisr_gemm_0123456789abcdef.so")
+    build._drop_superseded(tmp_path / "libcisr_attention_head_dim16_ffffffffffffffff.so")
+    assert sorted(p.name for p in tmp_path.iterdir()) == sorted(keep + ["libcisr_attention_head_dim16_ffffffffffffffff.so"])

@@ -23,6 +23,23 @@ def close(a, b, atol, rtol, what=""):
     torch.testing.assert_close(a.double().cpu(), b.double().cpu(), atol=atol, rtol=rtol, msg=lambda m: f"{what}: {m}")
 
 
+def product_rounding_sigma(a, w):
+    """An upper bound on the standard deviation of (bfloat16-rounded a) @ w^T around a @ w^T, per output element, for
+    float64 `a` [m, k] and `w` [n, k].  Rounding a_k to eight significant bits moves it by at most half a unit in the
+    last place, uniformly: a standard deviation of 2^-8 / sqrt(3) times the power of two below |a_k|, so at most that
+    times |a_k| itself, wherever in the computation of `a` the rounding happens (before or after a common factor).
+    The errors are independent, so the variance of a sum is the sum of (2^-8 a_k w_k)^2 / 3."""
+    return (2.0 ** -8 / 3 ** 0.5) * torch.sqrt((a * a) @ (w * w).T)
+
+
+def within(out, ref, bound, what):
+    """|out - ref| <= bound element by element (all float64 on the CPU), with the worst offender in the message."""
+    excess = (out.double().cpu() - ref).abs() - bound
+    worst = int(excess.argmax())
+    assert excess.max() <= 0, (f"{what}: element {worst} is off by {float((out.double().cpu() - ref).abs().flatten()[worst]):.3e}, "
+                               f"bound {float(bound.flatten()[worst]):.3e}")
+
+
 @pytest.mark.parametrize("hidden", [10, 64, 130, 576, 5000])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(hidden, dtype):
@@ -447,6 +464,11 @@ def test_skinny_gemm_plain(m, n, kk, kind):
     out = torch.full((m, n), float("nan"), device=dev())
     k.skinny_gemm(w.to(dev()), m, act=a.to(dev()), epilogue=k.EPI_PLAIN, out=out, kind=kind)
     close(out, a.double() @ w.double().T, 2e-5 * math.sqrt(kk), 1e-5, "skinny plain")
+    # the residual form: the product added to what the output holds, one float add per element
+    stream = (10 * torch.randn(m, n, generator=g)).float()
+    added = stream.clone().to(dev())
+    k.skinny_gemm(w.to(dev()), m, act=a.to(dev()), epilogue=k.EPI_PLAIN, out=added, kind=kind, accumulate=True)
+    assert torch.equal(added.cpu(), stream + out.cpu())
     if m <= k.SKINNY_NORM_MAX_TOKENS:
         x = torch.randn(m + 3, kk, generator=g) * 2
         delta = torch.randn(m + 3, kk, generator=g)
@@ -455,8 +477,11 @@ def test_skinny_gemm_plain(m, n, kk, kind):
         out2 = torch.full((m, n), float("nan"), device=dev())
         k.skinny_gemm(w.to(dev()), m, x=x.to(dev()), delta=delta.to(dev()), norm_w=nw.to(dev()), eps=1e-5, rows=rows.to(dev()),
                       epilogue=k.EPI_PLAIN, out=out2, kind=kind)
-        h = pl.rms_norm((x + delta).double()[rows.long()], nw.double(), 1e-5).to(torch.bfloat16).double()
-        close(out2, h @ w.double().T, 2e-2, 2e-2, "skinny plain with norm prologue")
+        # the kernel may round the normed row to bfloat16 before or after the row's common factor 1 / rms: six standard
+        # deviations of either rounding around the unrounded product
+        h = pl.rms_norm((x + delta).double()[rows.long()], nw.double(), 1e-5)
+        ref = h @ w.double().T
+        within(out2, ref, 6 * product_rounding_sigma(h, w.double()) + 1e-5 * (1 + ref.abs()), "skinny plain with norm prologue")
 
 
 @pytest.mark.parametrize("m", [1, 7, 16, 40])
@@ -472,7 +497,8 @@ def test_skinny_gemm_swiglu_and_residual_output(m, inter, kk, kind):
     delta = torch.randn(m, kk, generator=g)
     nw = (1 + 0.1 * torch.randn(kk, generator=g)).to(torch.bfloat16)
     act = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=dev())
-    h = pl.rms_norm((x + delta).double(), nw.double(), 2e-6).to(torch.bfloat16)
+    exact = pl.rms_norm((x + delta).double(), nw.double(), 2e-6)
+    h = exact.to(torch.bfloat16)
     if m <= k.SKINNY_NORM_MAX_TOKENS:
         x_out = torch.full_like(x, float("nan")).to(dev())
         xd = x.to(dev())
@@ -482,9 +508,15 @@ def test_skinny_gemm_swiglu_and_residual_output(m, inter, kk, kind):
         assert torch.equal(xd.cpu(), x)                                   # the input stream is not touched
     else:
         k.skinny_gemm(w.to(dev()), m, act=h.to(dev()), epilogue=k.EPI_SWIGLU, out=act, kind=kind)
-    gu = h.double() @ w.double().T
-    ref = gu[:, :inter] / (1 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
-    close(act, ref, 2e-2, 2e-2, "skinny swiglu")
+    # gate and up within six standard deviations of the activations' rounding (wherever in the norm it happens), carried
+    # through silu(g) * u (|silu'| <= 1.1), plus the output's own rounding to bfloat16
+    gu = exact @ w.double().T
+    sigma = product_rounding_sigma(exact, w.double())
+    gate, up = gu[:, :inter], gu[:, inter:]
+    silu = gate / (1 + torch.exp(-gate))
+    ref = silu * up
+    bound = 6 * (1.1 * up.abs() * sigma[:, :inter] + silu.abs() * sigma[:, inter:]) + 2.0 ** -8 * ref.abs() + 1e-4
+    within(act, ref, bound, "skinny swiglu")
 
 
 def plain_rotated_projection(hbf, w, positions, token_req, req_slot, table, page, n_pages, hq, hkv, dim, rot, interleaved, theta):
@@ -765,3 +797,8 @@ def test_merge_and_output_projection_in_one_launch(d, hq, hkv, n_out, n_dec):
     k.merge_out_proj(outs[False][1], outs[False][2], n_splits, i32(range(n_dec)), i32(rows), n_dec, hq, d, w, projected)
     ref = merged.double().reshape(n_dec, hq * d) @ w.double().T
     close(projected, ref, 2e-6 * float(ref.abs().max()) + 1e-6, 1e-5, "merge + output projection")
+    # the residual form: added to the rows of a stream that has more rows than the step has decoding requests' tokens
+    stream = 10 * torch.randn(n_dec, n_out, generator=g)
+    added = stream.clone().to(dev())
+    k.merge_out_proj(outs[False][1], outs[False][2], n_splits, i32(range(n_dec)), i32(rows), n_dec, hq, d, w, added, accumulate=True)
+    assert torch.equal(added.cpu(), stream + projected.cpu())
