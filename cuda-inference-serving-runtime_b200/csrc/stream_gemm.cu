@@ -5,13 +5,16 @@
 //
 //   * persistent: one CTA per SM walks "row blocks" (32, 64 or 128 weight rows by all of K); the tokens are staged
 //     (and normalised) once per CTA, not once per 16 rows
-//   * the weights stream through a ring of 16 KB stages in shared memory, filled by tensor-map copies
-//     (cp.async.bulk.tensor.2d, 128-byte swizzle): a stage is eight tiles of 16 rows x 64 k, one per consumer warp,
-//     fetched as one box per k-slice (or two, where a block's rows lie in two places).
-//     A producer warp keeps the ring full (about 140 KB on the way per SM) and starts before the wait on the previous
+//   * the weights stream through a ring of stages in shared memory, filled by tensor-map copies (cp.async.bulk.tensor,
+//     128-byte swizzle).  Where K is whole 64-column groups the groups are one more dimension of the tensor map
+//     ([64][rows][groups], strides {row, 128 bytes}) and a stage is ONE box: all the block's rows by sixteen k-slices'
+//     worth of 32 KB (36 KB where nine groups are a whole block).  The copy engine's cost is per request: 4 KB boxes
+//     stream at 2 TB/s, 16 KB boxes at 5 to 6, and a short launch gains again from 32 KB.  Otherwise a stage is
+//     eight tiles of 16 rows x 64 k, fetched as one box per k-slice.
+//     A producer warp keeps the ring full (up to 200 KB on the way per SM) and starts before the wait on the previous
 //     kernel: weights do not depend on it
-//   * eight consumer warps: warp w takes box w of every stage: row tile w % RT of the block and k-slice w / RT of the
-//     stage (RT = rows / 16), with ldmatrix for the weights (A operand of mma.sync.m16n8k16) and the tokens as the
+//   * eight consumer warps: warp w takes row tile w % RT of the block and the k-slices w / RT, w / RT + 8 / RT, ... of
+//     every stage (RT = rows / 16), with ldmatrix for the weights (A operand of mma.sync.m16n8k16) and the tokens as the
 //     8-wide N.  The k-slices of a row tile are added through shared memory in a fixed order, then the epilogue runs
 //     while the producer already fetches the next block
 //   * SWIGLU: a row tile is 8 gate rows and the 8 up rows of the same features (two 8-row boxes); ROPE: a block is the
@@ -48,6 +51,8 @@ struct StreamArgs {
     const int* positions; const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size;
     int hq; int hkv; int dim;
     int accumulate;                                // PLAIN: out += product
+    int grouped;                                   // the tensor map's last dimension counts 64-column groups: a stage is one box
+    int stage_groups; int stage_bytes;             // k-slices (64 columns each) per stage, and the stage's size
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -172,7 +177,7 @@ stream_kernel(const __grid_constant__ CUtensorMap map_w, const StreamArgs a, int
     extern __shared__ unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024-byte aligned
     const int S = a.stages, ldh = a.k + 8;
-    uint64_t* full = reinterpret_cast<uint64_t*>(ring + (size_t)S * STAGE_BYTES);   // [S]: a stage's boxes have landed
+    uint64_t* full = reinterpret_cast<uint64_t*>(ring + (size_t)S * a.stage_bytes); // [S]: a stage's boxes have landed
     uint64_t* empty = full + S;                                                      // [S]: the consumers are done with it
     int* abort_flag = reinterpret_cast<int*>(empty + S);
     float* red = reinterpret_cast<float*>(abort_flag + 4);                           // [CONSUMERS][16][MT * 8]
@@ -183,7 +188,8 @@ stream_kernel(const __grid_constant__ CUtensorMap map_w, const StreamArgs a, int
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int RT = a.block_rows / 16, KSUB = CONSUMERS / RT;      // row tiles of a block, k-slices of a stage
     const int k_boxes = (a.k + 63) / 64;
-    const int k_stages = (k_boxes + KSUB - 1) / KSUB;             // stages per block
+    const int SG = a.stage_groups;                                // k-slices of a stage: KSUB at a time, one per consumer warp
+    const int k_stages = (k_boxes + SG - 1) / SG;                 // stages per block
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, CONSUMERS); }
         *abort_flag = 0;
@@ -204,14 +210,29 @@ stream_kernel(const __grid_constant__ CUtensorMap map_w, const StreamArgs a, int
                     if (lane == 0) { atomicExch(error, 4); *(volatile int*)abort_flag = 1; }
                 }
                 if (*(volatile int*)abort_flag) continue;          // nothing more is requested; the loops still end
-                unsigned char* stage = ring + (size_t)s * STAGE_BYTES;
-                if (lane == 0) mbar_expect_tx(full + s, (uint32_t)STAGE_BYTES);
+                unsigned char* stage = ring + (size_t)s * a.stage_bytes;
+                if (lane == 0) mbar_expect_tx(full + s, (uint32_t)a.stage_bytes);
                 __syncwarp();
                 // One copy per k-slice: all row tiles of the block in one box.  Where a block's rows lie in two places
                 // the tensor map has a dimension for that: [2 halves][inter rows][K] for the stacked gate and up
                 // matrices, [heads][2 halves][D / 2 rows][K] for the stacked heads, and the box takes both halves.
                 // Few large boxes keep the copy engine's per-request cost low.  A box beyond K or N is all zeros.
-                if (lane < KSUB) {
+                if (a.grouped) {
+                    // K in whole 64-column groups: the groups are one more dimension of the tensor map, and the stage's
+                    // k-slices arrive as ONE box [k-slices][rows][64 columns] (the copy engine's cost is per request:
+                    // a 16 KB box streams at nearly three times the rate of four 4 KB boxes)
+                    if (lane == 0) {
+                        const int half = a.block_rows / 2, g0 = ks * SG;
+                        if (EPI == EPI_SWIGLU) {
+                            tma_load_4d(stage, &map_w, 0, block * half, 0, g0, full + s);
+                        } else if (EPI == EPI_ROPE) {
+                            const int per_head = a.dim / a.block_rows, h = block / per_head, p = block - h * per_head;
+                            tma_load_5d(stage, &map_w, 0, p * half, 0, h, g0, full + s);
+                        } else {
+                            tma_load_3d(stage, &map_w, 0, block * a.block_rows, g0, full + s);
+                        }
+                    }
+                } else if (lane < KSUB) {
                     const int sub = lane, kc = (ks * KSUB + sub) * 64, half = a.block_rows / 2;
                     unsigned char* dst = stage + sub * a.block_rows * 128;
                     if (EPI == EPI_SWIGLU) {
@@ -262,8 +283,9 @@ stream_kernel(const __grid_constant__ CUtensorMap map_w, const StreamArgs a, int
             if (*(volatile int*)abort_flag) continue;
             // the k-slice's region holds the block's rows in the order they were fetched: SWIGLU all gate rows then all
             // up rows (a tile's rows 0-7 and 8-15 lie half a region apart), otherwise tile after tile
-            const unsigned char* region = ring + (size_t)s * STAGE_BYTES + (size_t)sub * a.block_rows * 128;
-            const int k0 = (ks * KSUB + sub) * 64;                 // beyond K: the box is zeros and so are the tokens read as 0
+            for (int slice = sub; slice < SG; slice += KSUB) {     // this warp's k-slices of the stage
+            const unsigned char* region = ring + (size_t)s * a.stage_bytes + (size_t)slice * a.block_rows * 128;
+            const int k0 = (ks * SG + slice) * 64;                 // beyond K: the box is zeros and so are the tokens read as 0
             if (k0 < a.k) {
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
@@ -282,6 +304,7 @@ stream_kernel(const __grid_constant__ CUtensorMap map_w, const StreamArgs a, int
                         mma_bf16(acc[mt], w4, b0, b1);
                     }
                 }
+            }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty + s);
@@ -388,11 +411,23 @@ int launch(StreamArgs& a, const void* w, cudaStream_t s) {
                          sizeof(bf16) * (size_t)a.m * (a.k + 8) +
                          (EPI == EPI_ROPE ? sizeof(float) * 2 * (size_t)a.m * a.rot_half : 0);
     const size_t budget = 224 * 1024;
-    if (fixed + 3 * (STAGE_BYTES + 16) > budget) return -2;       // rows too long for shared memory: not this kernel's
-    a.stages = (int)((budget - fixed) / (STAGE_BYTES + 16));
+    // K in whole 64-column groups: a stage is one box of several k-slices per consumer warp, 32 KB (or 36 KB where that
+    // is a whole block of nine groups): the copy engine's cost is per request, and short launches in particular
+    // stream faster in few large requests.  Otherwise one box per k-slice and one k-slice per consumer warp: 16 KB.
+    a.grouped = a.k % 64 == 0;
+    const int ksub = CONSUMERS / (a.block_rows / 16), groups = (a.k + 63) / 64;
+    a.stage_groups = ksub;
+    if (a.grouped) {
+        a.stage_groups = groups == 2 * ksub + 1 && a.block_rows == 32 ? groups : 2 * ksub;
+        if (a.stage_groups > groups) a.stage_groups = groups > ksub ? groups : ksub;
+    }
+    a.stage_bytes = a.stage_groups * a.block_rows * 128;
+    if (fixed + 3 * ((size_t)a.stage_bytes + 16) > budget) { a.stage_groups = ksub; a.stage_bytes = STAGE_BYTES; }
+    if (fixed + 3 * ((size_t)a.stage_bytes + 16) > budget) return -2;       // rows too long for shared memory: not this kernel's
+    a.stages = (int)((budget - fixed) / ((size_t)a.stage_bytes + 16));
     if (a.stages > 12) a.stages = 12;
     if (const char* forced = getenv("CISR_STREAM_STAGES")) { const int st = atoi(forced); if (st >= 2 && st < a.stages) a.stages = st; }
-    const size_t smem = fixed + (size_t)a.stages * (STAGE_BYTES + 16);
+    const size_t smem = fixed + (size_t)a.stages * ((size_t)a.stage_bytes + 16);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(stream_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
@@ -400,31 +435,40 @@ int launch(StreamArgs& a, const void* w, cudaStream_t s) {
         configured = true;
     }
     CUtensorMap map_w;
-    int status;
-    if (EPI == EPI_PLAIN) {
+    int status = 0;
+        if (EPI == EPI_PLAIN && !a.grouped) {
         status = cached_map(&map_w, w, a.n, a.k, a.block_rows, 64);
     } else {
-        // the block's rows lie in two places: one more dimension for the halves (see the producer)
+        // More dimensions than the matrix has: the 64-column groups of K as the last one (`grouped`), and where a block's
+        // rows lie in two places one for the halves (see the producer)
         static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
-        const MapKey key{w, a.n, a.k, a.block_rows, EPI};
+        const MapKey key{w, a.n, a.k, a.block_rows, EPI + 16 * a.grouped + 64 * a.stage_groups};
         auto it = maps.find(key);
-        status = 0;
         if (it == maps.end()) {
             if (maps.size() > 4096) maps.clear();
             CUtensorMap map;
             const cuuint64_t row_bytes = (cuuint64_t)a.k * sizeof(bf16);
             const cuuint32_t half = (cuuint32_t)a.block_rows / 2;
-            if (EPI == EPI_SWIGLU) {
-                const cuuint64_t dims[3] = {(cuuint64_t)a.k, (cuuint64_t)a.inter, 2};
-                const cuuint64_t strides[2] = {row_bytes, row_bytes * a.inter};
-                const cuuint32_t box[3] = {64, half, 2};
-                status = make_map_nd(&map, w, 3, dims, strides, box);
+            const cuuint64_t inner = a.grouped ? 64 : (cuuint64_t)a.k, groups = (cuuint64_t)a.k / 64;
+            cuuint64_t dims[5], strides[4];
+            cuuint32_t box[5];
+            int rank;
+            if (EPI == EPI_PLAIN) {
+                dims[0] = inner; dims[1] = (cuuint64_t)a.n; strides[0] = row_bytes; box[0] = 64; box[1] = (cuuint32_t)a.block_rows;
+                rank = 2;
+            } else if (EPI == EPI_SWIGLU) {
+                dims[0] = inner; dims[1] = (cuuint64_t)a.inter; dims[2] = 2;
+                strides[0] = row_bytes; strides[1] = row_bytes * a.inter;
+                box[0] = 64; box[1] = half; box[2] = 2;
+                rank = 3;
             } else {
-                const cuuint64_t dims[4] = {(cuuint64_t)a.k, (cuuint64_t)a.dim / 2, 2, (cuuint64_t)(a.hq + 2 * a.hkv)};
-                const cuuint64_t strides[3] = {row_bytes, row_bytes * (a.dim / 2), row_bytes * a.dim};
-                const cuuint32_t box[4] = {64, half, 2, 1};
-                status = make_map_nd(&map, w, 4, dims, strides, box);
+                dims[0] = inner; dims[1] = (cuuint64_t)a.dim / 2; dims[2] = 2; dims[3] = (cuuint64_t)(a.hq + 2 * a.hkv);
+                strides[0] = row_bytes; strides[1] = row_bytes * (a.dim / 2); strides[2] = row_bytes * a.dim;
+                box[0] = 64; box[1] = half; box[2] = 2; box[3] = 1;
+                rank = 4;
             }
+            if (a.grouped) { dims[rank] = groups; strides[rank - 1] = 128; box[rank] = (cuuint32_t)a.stage_groups; ++rank; }
+            status = make_map_nd(&map, w, rank, dims, strides, box);
             if (!status) it = maps.emplace(key, map).first;
         }
         if (!status) map_w = it->second;

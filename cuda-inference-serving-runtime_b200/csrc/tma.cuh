@@ -50,7 +50,7 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
                  ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
 }
 
-// The same for tensors seen with three or four dimensions (c0 innermost); the box lands as [c3][c2][c1][c0].
+// The same for tensors seen with three to five dimensions (c0 innermost); the box lands as [c4][c3][c2][c1][c0].
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
@@ -58,6 +58,11 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar)) : "memory");
 }
 
 // ---------------------------------------------------------------- host side
@@ -90,10 +95,12 @@ int make_map(CUtensorMap* map, const void* base, long long rows, int cols, int b
     return r == CUDA_SUCCESS ? 0 : -20 - (int)r;
 }
 
-// A bfloat16 tensor of `rank` dimensions (2 to 4): dims and box in elements, innermost first; strides in bytes for
-// dimensions 1 .. rank - 1 (multiples of 16).  128-byte swizzle, so box[0] * 2 bytes <= 128.
+// A bfloat16 tensor of `rank` dimensions (2 to 5): dims and box in elements, innermost first; strides in bytes for
+// dimensions 1 .. rank - 1 (multiples of 16; they need not grow with the dimension: a row-major matrix whose rows are
+// cut into 64-column groups is [64][rows][groups] with strides {row, 128 bytes}).  128-byte swizzle, so box[0] * 2
+// bytes <= 128.
 int make_map_nd(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box) {
-    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, elem,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
