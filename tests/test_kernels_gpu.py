@@ -413,9 +413,19 @@ def test_greedy_sampling_takes_the_lowest_index_on_ties():
     logits[2, 0] = 60.0
     got = sample_tokens(logits).cpu().tolist()
     assert got[:3] == [300, 999, 0] and got[3:] == logits[3:].argmax(dim=-1).cpu().tolist()
+    # a vocabulary that several CTAs share per row (and whose rows do not all start on a 16-byte boundary): ties and
+    # maxima in different CTAs' shares, at their edges
+    vocab = 40001
+    logits = torch.randn(6, vocab, device=dev())
+    logits[0, 39999] = logits[0, 100] = 50.0
+    logits[1, vocab - 1] = 60.0
+    logits[2, 13336] = logits[2, 13335] = 55.0
+    logits[3, 26672] = 52.0
+    got = sample_tokens(logits).cpu().tolist()
+    assert got[:4] == [100, vocab - 1, 13335, 26672] and got[4:] == logits[4:].argmax(dim=-1).cpu().tolist()
 
 
-@pytest.mark.parametrize("vocab", [5, 301, 49152])
+@pytest.mark.parametrize("vocab", [5, 301, 40001, 49152, 128256])
 def test_temperature_sampling_is_an_inverse_cdf_of_softmax(vocab):
     from cisr_b200.sampling import sample_tokens, uniform
     g = torch.Generator().manual_seed(vocab)
