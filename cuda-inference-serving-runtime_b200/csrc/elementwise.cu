@@ -17,6 +17,12 @@ template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab) {
     CISR_TRACE_SCOPE(TRACE_EMBEDDING);
+    // Under programmatic dependent launch the kernels after this one may start (and fetch their weights) while it runs.
+    // It waits for the kernel before it although it reads nothing of it: a later kernel's wait on this one then also
+    // covers everything before (the block table update at the head of a step).
+    pdl_trigger();
+    pdl_wait();
+    CISR_TRACE_WAITED();
     const int row = blockIdx.x;
     int id = ids[row];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // host validates; clamp keeps a bad id from reading outside
@@ -30,10 +36,8 @@ CISR_EXPORT int cisr_embedding(const void* table, int table_dtype, const int* id
     if (tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == CISR_BF16)
-        embedding_kernel<<<tokens, 128, 0, s>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab);
-    else
-        embedding_kernel<<<tokens, 128, 0, s>>>((const float*)table, ids, out, hidden, vocab);
-    return launch_status();
+        return launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, s, g_pdl, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
+    return launch_kernel(embedding_kernel<float>, dim3(tokens), dim3(128), 0, s, g_pdl, (const float*)table, ids, out, hidden, vocab);
 }
 
 // ---------------------------------------------------------------- residual add + RMSNorm
@@ -175,6 +179,10 @@ CISR_EXPORT int cisr_swiglu(const float* gate_up, void* out, int out_dtype, int 
 __global__ void rotary_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                     float* __restrict__ cos_out, float* __restrict__ sin_out, int half, int total) {
     CISR_TRACE_SCOPE(TRACE_ROTARY_TABLE);
+    // No early start for the kernels after this one: the fused q/k/v kernels read these tables before their own wait
+    // on their predecessor, so whatever runs between this kernel and them must not start before the tables are written.
+    pdl_wait();          // nothing of the kernel before is read, but the chain of waits must not break (see embedding_kernel)
+    CISR_TRACE_WAITED();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const int t = i / half, f = i - t * half;
@@ -188,8 +196,8 @@ CISR_EXPORT int cisr_rotary_tables(const int* positions, const double* inv_freq,
                                    int tokens, int half, void* stream) {
     const int total = tokens * half;
     if (total <= 0) return 0;
-    rotary_table_kernel<<<(total + 127) / 128, 128, 0, (cudaStream_t)stream>>>(positions, inv_freq, cos_out, sin_out, half, total);
-    return launch_status();
+    return launch_kernel(rotary_table_kernel, dim3((total + 127) / 128), dim3(128), 0, (cudaStream_t)stream, g_pdl, positions, inv_freq,
+                         cos_out, sin_out, half, total);
 }
 
 // ---------------------------------------------------------------- rotation + cache write
@@ -290,6 +298,8 @@ CISR_EXPORT int cisr_page_copy(void* pool, const int* pairs, int n_pairs, int n_
 
 // ---------------------------------------------------------------- block table updates
 // table[idx[i]] = val[i]; the host sends one value per entry, so the order does not matter.
+// Launched plainly, and it never lets its successors start early: kernels further down the step read the table before
+// their own wait on their predecessor, which is safe only because nothing after this kernel starts before it is done.
 __global__ void table_update_kernel(int* __restrict__ table, const int* __restrict__ idx, const int* __restrict__ val, int n) {
     CISR_TRACE_SCOPE(TRACE_TABLE_UPDATE);
     const int i = blockIdx.x * blockDim.x + threadIdx.x;

@@ -114,8 +114,24 @@ class Model:
                             dtype=self.dtype, device=self.device)
 
     # ---------------------------------------------------------------- forward
+    def step_beginners(self) -> list:
+        """The parts of the layers that run, in run order, whose class has a `begin_step` of its own."""
+        found = getattr(self, "_step_beginners", None)
+        if found is None:
+            from ..parts.base import Part
+            found, seen = [], set()
+            for entry in self.spec.run:
+                for part in self.layers[entry.layer].parts().values():
+                    if id(part) not in seen and getattr(type(part), "begin_step", Part.begin_step) is not Part.begin_step:
+                        seen.add(id(part))
+                        found.append(part)
+            self._step_beginners = found
+        return found
+
     def forward(self, ctx, cache: CacheManager) -> torch.Tensor:
         """Run the step's tokens through every run entry; float logits [wanted rows, vocab]."""
+        for part in self.step_beginners():
+            part.begin_step(ctx)
         stream = ResidualStream(self.embedding.forward(ctx.token_ids))
         for index, entry in enumerate(self.spec.run):
             self.layers[entry.layer].forward(stream, ctx, cache.binding(index, reads_from=entry.cache_of))

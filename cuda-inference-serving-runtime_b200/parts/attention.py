@@ -102,6 +102,9 @@ class GQAAttention(Mixer):
             info={"n_tiles": len(tile_req), "n_wide": len(wide_req), "n_decode": len(dec_req),
                   "n_splits": decode_ranges(longest)})
 
+    def begin_step(self, ctx) -> None:
+        self.position.rotation(ctx)          # the rotation tables of the step, shared by every layer with the same encoding
+
     def forward(self, h, ctx, cache):
         h0 = h                    # as it came: the pending norm, through which the output may go straight into the stream
         tokens = ctx.n_tokens

@@ -48,6 +48,11 @@ class Part:
         """Build jobs (source, defines, extra flags) of the kernel libraries this part launches."""
         return []
 
+    def begin_step(self, ctx) -> None:
+        """Called once per step for every part of the model, before the embedding: work that needs the step's metadata
+        only (position tables) is launched here, ahead of the layers, instead of inside the first layer that uses it.
+        What it makes goes to `ctx.shared`, where the part finds it again."""
+
     def plan_key(self) -> Optional[tuple]:
         """None: the part needs nothing but the step context.  Otherwise a hashable key naming the launch plan it
         derives from a step's shape (`step_plan`); parts with equal keys share one plan per step, which the engine
