@@ -620,7 +620,12 @@ __device__ __forceinline__ void stamp(int i) {
 
 // cluster: CTAs per cluster along the key ranges (1: none).  n_parts = n_splits / cluster partial sums per query head
 // remain; with one, the first CTA writes the finished rows to `out`, otherwise partial sums for the merge kernel.
-__global__ void __launch_bounds__(DEC_THREADS, 3)
+// STAGES: tiles a warp has on the way at once (each in its own 16 KB stage).  With one, a warp whose share is two tiles
+// (ranges of 256 keys at head size 128) requests the second only after the first is used; with two, both are requested
+// before the wait on the kernel before, at twice the shared memory: for launches of no more CTAs than the device has
+// SMs, where that memory is idle anyway.  The sums are the same either way.
+template <int STAGES>
+__global__ void __launch_bounds__(DEC_THREADS, STAGES == 1 ? 3 : 1)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_cache,
                        const bf16* __restrict__ v_cache, int cache_rows, const int* __restrict__ req_slot,
@@ -632,9 +637,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     extern __shared__ unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024-byte aligned
     float* merge = reinterpret_cast<float*>(ring);                   // reused after the loop: [4][16][D + 2]
-    bf16* Qs = reinterpret_cast<bf16*>(ring + 4 * (size_t)TMA_TILE_BYTES);         // [16][LDS]
-    uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * LDS);     // [4]: a warp's tile has landed
-    int* failed = reinterpret_cast<int*>(full + 4);
+    bf16* Qs = reinterpret_cast<bf16*>(ring + 4 * STAGES * (size_t)TMA_TILE_BYTES);   // [16][LDS]
+    uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * LDS);     // [4][STAGES]: a warp's tile has landed
+    int* failed = reinterpret_cast<int*>(full + 4 * STAGES);
     float* gathered = reinterpret_cast<float*>(failed + 4);          // [cluster][rows][D / cluster + 2]: this CTA's share of the cluster's results
 
     STAMP(0);
@@ -674,17 +679,17 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int first_page = base / page_size;
     for (int i = tid; i <= (hi - 1) / page_size - first_page; i += DEC_THREADS) pages[i] = table[first_page + i];
     if (tid == 0) {
-        for (int w = 0; w < 4; ++w) mbar_init(full + w, 1);
+        for (int w = 0; w < 4 * STAGES; ++w) mbar_init(full + w, 1);
         mbar_init_fence();
     }
     __syncthreads();
     STAMP(1);
 
     // Tile t into this warp's stage: lane b fetches box b (K or V, 64-column half, run of box_rows keys).
-    unsigned char* stage = ring + (size_t)warp * TMA_TILE_BYTES;
-    uint64_t* bar = full + warp;
     const int box_rows = min(page_size, TK), boxes = TK / box_rows;
-    auto fetch = [&](int t) {
+    auto fetch = [&](int t, int slot) {
+        unsigned char* stage = ring + (size_t)(warp * STAGES + slot) * TMA_TILE_BYTES;
+        uint64_t* bar = full + warp * STAGES + slot;
         if (lane == 0) mbar_expect_tx(bar, (uint32_t)TMA_TILE_BYTES);
         __syncwarp();
         for (int b = lane; b < 2 * NSUB * boxes; b += 32) {
@@ -699,13 +704,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     // first tile is requested now; in the tile that holds the newest key that one row arrives stale and is fetched
     // again, by ordinary loads, once the kernel before has finished.
     const int newest = hi == ctx ? n_tiles - 1 : -1;
-    if (warp < n_tiles) fetch(warp);
+#pragma unroll
+    for (int i = 0; i < STAGES; ++i)
+        if (warp + 4 * i < n_tiles) fetch(warp + 4 * i, i);
+    const bool newest_early = newest >= 0 && newest / 4 < STAGES;    // the newest key's tile was requested before the wait
     STAMP(2);
     pdl_wait();
     CISR_TRACE_WAITED();
     STAMP(3);
     uint4 newest_k = make_uint4(0, 0, 0, 0), newest_v = newest_k;
-    if (warp == newest && lane < NSUB * 8) {
+    if (newest_early && warp == (newest & 3) && lane < NSUB * 8) {
         const int pos = ctx - 1, page = pages[pos / page_size - first_page];
         if (page >= 0) {
             const size_t at = (((size_t)page * hkv + kvh) * page_size + pos % page_size) * D + lane * 8;
@@ -729,18 +737,22 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     for (int kk = 0; kk < KD; ++kk)
         ldmatrix_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
     const float scale2 = scale * LOG2E;
-    const unsigned char* Ks = stage;
-    unsigned char* Vs = stage + NSUB * SUB_BYTES;
 
     for (int t = warp, it = 0; t < n_tiles; t += 4, ++it) {
-        if (!__all_sync(0xffffffffu, mbar_wait(bar, it & 1))) {      // the lanes agree on whether the wait ran out
+        const int slot = it % STAGES;
+        const uint32_t parity = (uint32_t)(it / STAGES) & 1;
+        unsigned char* stage = ring + (size_t)(warp * STAGES + slot) * TMA_TILE_BYTES;
+        uint64_t* bar = full + warp * STAGES + slot;
+        const unsigned char* Ks = stage;
+        unsigned char* Vs = stage + NSUB * SUB_BYTES;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar, parity))) {      // the lanes agree on whether the wait ran out
             if (lane == 0) { atomicExch(error, 3); *failed = 1; }
-            mbar_wait(bar, it & 1);      // one more bounded chance for the copy to land before the stage is given up
+            mbar_wait(bar, parity);      // one more bounded chance for the copy to land before the stage is given up
             break;
         }
         if (it == 0) { STAMP(5); CISR_TRACE_MARK(1); }
         const int k0 = base + t * TK;
-        if (it == 0 && t == newest) {             // the newest key's row over the stale one the early copy brought
+        if (newest_early && t == newest) {        // the newest key's row over the stale one the early copy brought
             if (lane < NSUB * 8) {
                 const int r = ctx - 1 - k0;
                 *reinterpret_cast<uint4*>(stage + swizzled(r, lane)) = newest_k;
@@ -822,7 +834,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
         }
         __syncwarp();                                                // every lane has read the stage
-        if (t + 4 < n_tiles) fetch(t + 4);
+        if (t + 4 * STAGES < n_tiles) fetch(t + 4 * STAGES, slot);
     }
     } else {
         pdl_wait();
@@ -1042,13 +1054,19 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
     const int group = hq / hkv, rows_max = group < 16 ? group : 16;
     const size_t smem_plain = TMA_SMEM_FIXED + sizeof(int) * ((size_t)split_size / page_size + 8);
     constexpr size_t SMEM_CAP = 110 * 1024;  // two CTAs per SM at the very least; the usual need is below 72 KB (three)
+    constexpr size_t SMEM_CAP_DEEP = 200 * 1024;
     if (smem_plain > SMEM_CAP) return -3;
     static bool configured = false;
+    static int sms = 0;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_CAP);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_CAP);
         if (e != cudaSuccess) return (int)e;
-        cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);   // clusters of more than 8
+        e = cudaFuncSetAttribute(attn_decode_tma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_CAP_DEEP);
+        if (e != cudaSuccess) return (int)e;
+        cudaFuncSetAttribute(attn_decode_tma_kernel<1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);   // clusters of more than 8
         cudaGetLastError();
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 0;
         configured = true;
     }
     // the largest cluster size that divides the number of ranges, fits shared memory and can be resident
@@ -1067,7 +1085,7 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
             attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)c;
             config.attrs = attr; config.numAttrs = 1;
             int n = 0;
-            const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, attn_decode_tma_kernel, &config);
+            const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, attn_decode_tma_kernel<1>, &config);
             cudaGetLastError();
             resident[c] = (e == cudaSuccess && n >= 1) ? 1 : -1;
         }
@@ -1079,12 +1097,22 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
     const int n_parts = n_splits / cluster;
     cudaStream_t s = (cudaStream_t)stream;
     g_last_launches = (group + 15) / 16 + (((n_parts == 1 && cluster > 1) || !merge) ? 0 : 1);
+    // a warp's share of a range is more than one tile, and the launch leaves most of the device's shared memory idle
+    const size_t smem_deep = smem + 4 * (size_t)TMA_TILE_BYTES;
+    const bool deep = cluster == 1 && split_size > 4 * TK && (long long)n_dec * hkv * n_splits <= sms && smem_deep <= SMEM_CAP_DEEP;
     for (int row0 = 0; row0 < group; row0 += 16) {
-        status = launch_kernel_cluster(attn_decode_tma_kernel, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), smem, s, g_pdl, cluster,
-                                       map_k, map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
-                                       (int)cache_rows, req_slot, block_table, table_width,
-                                       dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale, window, split_size,
-                                       cluster, n_parts, row0, g_error);
+        if (deep)
+            status = launch_kernel_cluster(attn_decode_tma_kernel<2>, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), smem_deep, s, g_pdl, 1,
+                                           map_k, map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
+                                           (int)cache_rows, req_slot, block_table, table_width,
+                                           dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale, window, split_size,
+                                           1, n_parts, row0, g_error);
+        else
+            status = launch_kernel_cluster(attn_decode_tma_kernel<1>, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), smem, s, g_pdl, cluster,
+                                           map_k, map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
+                                           (int)cache_rows, req_slot, block_table, table_width,
+                                           dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale, window, split_size,
+                                           cluster, n_parts, row0, g_error);
         if (status) return status;
     }
     if ((n_parts == 1 && cluster > 1) || !merge) return 0;

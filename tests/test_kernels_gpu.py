@@ -731,12 +731,15 @@ def test_tensor_maps_of_one_launch_survive_an_eviction_between_them():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_decode_attention_of_a_request_does_not_depend_on_its_neighbours(dtype):
+@pytest.mark.parametrize("d,hq,hkv", [(64, 6, 2), (128, 8, 8)])
+def test_decode_attention_of_a_request_does_not_depend_on_its_neighbours(dtype, d, hq, hkv):
     """Key ranges are cut at fixed absolute positions and empty ranges add exactly nothing, so a request's output is the
-    same to the last bit alone, beside short requests, and beside a much longer one (which brings more ranges)."""
+    same to the last bit alone, beside short requests, and beside a much longer one (which brings more ranges).  At head
+    size 128 a warp's share of a range is two tiles: a launch of few CTAs requests both ahead, a launch of more CTAs
+    than the device has SMs one after the other, and that must not show either."""
     k = kernels()
     from cisr_b200.parts.attention import DECODE_RANGE, decode_ranges
-    d, hq, hkv, page = 64, 6, 2, 16
+    page = 16
     lens = [700, 40, 3000, 257]
     i32 = lambda a: torch.as_tensor(np.asarray(list(a), dtype=np.int32), device=dev())
     g = torch.Generator().manual_seed(9)
@@ -762,6 +765,11 @@ def test_decode_attention_of_a_request_does_not_depend_on_its_neighbours(dtype):
 
     alone = run([0])
     assert torch.isfinite(alone).all()
+    pages0 = torch.as_tensor(table[0, :-(-lens[0] // page)].astype(np.int64), device=dev())
+    keys = kc[pages0].permute(0, 2, 1, 3).reshape(-1, hkv, d)[:lens[0]].double().cpu()
+    values = vc[pages0].permute(0, 2, 1, 3).reshape(-1, hkv, d)[:lens[0]].double().cpu()
+    queries = torch.zeros(lens[0], hq, d, dtype=torch.float64); queries[-1] = q_all[0].double().cpu()
+    close(alone[0], pl.causal_attention(queries, keys, values, None)[-1], *ATT_TOL[dtype], "decode attention of one request")
     assert torch.equal(run([1, 0])[1], alone[0])                 # beside a short request
     assert torch.equal(run([0, 2, 3, 1])[0], alone[0])           # beside a long one: twelve ranges instead of three
     assert torch.equal(run([3, 2])[0], run([3])[0])              # 257 keys: the second range holds one key
