@@ -69,6 +69,21 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
         o[d] = from_float<OT>(row_cache[d] * scale * to_float(weight[d]));
 }
 
+// Four weights and four outputs at a time (the row and the weights start on 16-byte boundaries, hidden % 4 == 0).
+__device__ __forceinline__ float4 load_weights4(const float* w, int d4) { return reinterpret_cast<const float4*>(w)[d4]; }
+__device__ __forceinline__ float4 load_weights4(const __nv_bfloat16* w, int d4) {
+    const uint2 raw = reinterpret_cast<const uint2*>(w)[d4];
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+__device__ __forceinline__ void store4(float* o, int d4, float4 v) { reinterpret_cast<float4*>(o)[d4] = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* o, int d4, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo); raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(o)[d4] = raw;
+}
+
 // The same with 16-byte accesses, for widths that are multiples of 4.
 template <typename WT, typename OT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta,
@@ -99,8 +114,14 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __res
     const float total = block_sum(sq, scratch);
     const float scale = rsqrtf(total / (float)hidden + eps);
     OT* o = out + (size_t)r * hidden;
+    const bool wide = !(((uintptr_t)weight | (uintptr_t)o) & 15) && (hidden * sizeof(OT)) % 16 == 0;   // the same for the whole block
     for (int d = threadIdx.x; d < h4; d += blockDim.x) {
         const float4 v = cache4[d];
+        if (wide) {
+            const float4 w = load_weights4(weight, d);
+            store4(o, d, make_float4(v.x * scale * w.x, v.y * scale * w.y, v.z * scale * w.z, v.w * scale * w.w));
+            continue;
+        }
         const float w0 = to_float(weight[4 * d]), w1 = to_float(weight[4 * d + 1]);
         const float w2 = to_float(weight[4 * d + 2]), w3 = to_float(weight[4 * d + 3]);
         o[4 * d] = from_float<OT>(v.x * scale * w0);
@@ -108,6 +129,64 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __res
         o[4 * d + 2] = from_float<OT>(v.z * scale * w2);
         o[4 * d + 3] = from_float<OT>(v.w * scale * w3);
     }
+}
+
+// A warp per row, the row in registers (V float4 per lane: widths up to 128 V), four rows per CTA: no shared memory
+// and no barrier, every load of a lane in flight before the first is used, 8- or 16-byte stores.  Steps of many tokens
+// spend a tenth of their time in this kernel, and a CTA per 576-wide row with scalar stores took 7 us for what the
+// memory system moves in 2.
+constexpr int NORM_WARPS = 4;
+template <typename WT, typename OT, int V>
+__global__ void __launch_bounds__(32 * NORM_WARPS)
+add_rmsnorm_warp_kernel(float* __restrict__ x, const float* __restrict__ delta, const WT* __restrict__ weight,
+                        OT* __restrict__ out, const int* __restrict__ rows, int n_rows, int hidden, float eps, int write_back) {
+    CISR_TRACE_SCOPE(TRACE_ADD_RMSNORM);
+    pdl_trigger();
+    pdl_wait();          // x and delta come from the kernels before
+    CISR_TRACE_WAITED();
+    const int lane = threadIdx.x & 31, r = blockIdx.x * NORM_WARPS + (threadIdx.x >> 5), h4 = hidden >> 2;
+    if (r >= n_rows) return;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    float4* xr = reinterpret_cast<float4*>(x + src);
+    const float4* dr = delta ? reinterpret_cast<const float4*>(delta + src) : nullptr;
+    float4 v[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int d = lane + 32 * i;
+        v[i] = d < h4 ? xr[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float sq = 0.f;
+    if (dr) {
+        float4 dv[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const int d = lane + 32 * i;
+            dv[i] = d < h4 ? dr[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            v[i].x += dv[i].x; v[i].y += dv[i].y; v[i].z += dv[i].z; v[i].w += dv[i].w;
+            if (write_back && lane + 32 * i < h4) xr[lane + 32 * i] = v[i];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) sq += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    const float scale = rsqrtf(warp_sum(sq) / (float)hidden + eps);
+    OT* o = out + (size_t)r * hidden;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int d = lane + 32 * i;
+        if (d >= h4) continue;
+        const float4 w = load_weights4(weight, d);
+        store4(o, d, make_float4(v[i].x * scale * w.x, v[i].y * scale * w.y, v[i].z * scale * w.z, v[i].w * scale * w.w));
+    }
+}
+
+template <typename WT, typename OT, int V>
+static int add_rmsnorm_warp_launch(float* x, const float* delta, const void* w, void* out, const int* rows, int n_rows,
+                                   int hidden, float eps, int write_back, cudaStream_t s) {
+    return launch_kernel(add_rmsnorm_warp_kernel<WT, OT, V>, dim3((n_rows + NORM_WARPS - 1) / NORM_WARPS), dim3(32 * NORM_WARPS), 0, s,
+                         g_pdl, x, delta, (const WT*)w, (OT*)out, rows, n_rows, hidden, eps, write_back);
 }
 
 template <typename WT, typename OT>
@@ -120,6 +199,14 @@ static int add_rmsnorm_launch(float* x, const float* delta, const void* w, void*
         if (e != cudaSuccess) return (int)e;
     }
     const bool vec = (hidden & 3) == 0 && !(((uintptr_t)x | (uintptr_t)delta) & 15);
+    // rows of up to 2048 floats whose weights and outputs are aligned too: a warp per row
+    if (vec && hidden <= 2048 && !(((uintptr_t)w | (uintptr_t)out) & 15) && (hidden * sizeof(OT)) % 16 == 0) {
+        const int per_lane = (hidden / 4 + 31) / 32;
+        if (per_lane <= 2) return add_rmsnorm_warp_launch<WT, OT, 2>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, s);
+        if (per_lane <= 5) return add_rmsnorm_warp_launch<WT, OT, 5>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, s);
+        if (per_lane <= 8) return add_rmsnorm_warp_launch<WT, OT, 8>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, s);
+        return add_rmsnorm_warp_launch<WT, OT, 16>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, s);
+    }
     if (smem > 48 * 1024 && vec) {
         cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_vec_kernel<WT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;

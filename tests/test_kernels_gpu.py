@@ -40,7 +40,7 @@ def within(out, ref, bound, what):
                                f"bound {float(bound.flatten()[worst]):.3e}")
 
 
-@pytest.mark.parametrize("hidden", [10, 64, 130, 576, 5000])
+@pytest.mark.parametrize("hidden", [10, 64, 130, 200, 576, 1000, 2048, 4096, 5000])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(hidden, dtype):
     k = kernels()
