@@ -55,6 +55,9 @@ __device__ __forceinline__ void store_bf16x32(bf16* dst, const float (&v)[32], i
     }
 }
 
+// Columns of tensor memory for two accumulators of `bn` columns: allocations are powers of two.
+__host__ __device__ constexpr int tmem_columns(int bn) { return 2 * bn <= 32 ? 32 : 2 * bn <= 64 ? 64 : 2 * bn <= 128 ? 128 : 2 * bn <= 256 ? 256 : 512; }
+
 template <int BN, int STAGES>
 struct Smem {
     static constexpr size_t A_BYTES = (size_t)BM * BK * sizeof(bf16);
@@ -193,7 +196,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         mbar_init_fence();
     }
     if (warp == 1) {    // one warp allocates two accumulators' columns of tensor memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_columns(BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tcgen05_fence_before();
@@ -288,7 +291,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (!ok && lane == 0) atomicExch(error, 1);
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_columns(BN)) : "memory");
 }
 
 // ---------------------------------------------------------------- host side
@@ -315,7 +318,7 @@ int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tcgen05_kernel<BN, STAGES, EPI>, 192, S::TOTAL);
         per_sm = per_sm < 1 ? 1 : per_sm;
-        if (per_sm * 2 * BN > 512) per_sm = 512 / (2 * BN);      // tensor memory: 512 columns per SM
+        if (per_sm * tmem_columns(BN) > 512) per_sm = 512 / tmem_columns(BN);      // tensor memory: 512 columns per SM
         slots = sms * per_sm;
     }
     const int tiles_m = (m + BM - 1) / BM, total = tiles_m * tiles_n;
@@ -386,8 +389,17 @@ CISR_EXPORT int cisr_gemm_tcgen05_swiglu(const void* a, const void* w, void* out
     if (!operands_ok(a, w, k)) return -2;
     Epilogue ep = {};
     ep.out_bf16 = (bf16*)out; ep.inter = inter;
-    if (wide_tiles(m, (inter + 127) / 128))
+    if (wide_tiles(m, (inter + 127) / 128)) {
+        // 128 x 256 tiles, or 128 x 192 where their last round would be much emptier: 192 tiles of 256 columns on 148 SMs
+        // are two rounds for 1.3 rounds of work, 256 tiles of 192 columns are two rounds of three quarters the length
+        static int sms = 0;
+        if (!sms) { int device = 0; cudaGetDevice(&device); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device); if (sms <= 0) sms = 148; }
+        const long long tiles_m = (m + BM - 1) / BM;
+        const long long rounds256 = (tiles_m * ((inter + 127) / 128) + sms - 1) / sms, rounds192 = (tiles_m * ((inter + 95) / 96) + sms - 1) / sms;
+        if (rounds192 * 192 * 10 <= rounds256 * 256 * 9)
+            return launch<192, 4, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 95) / 96, (cudaStream_t)stream);
         return launch<256, 4, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 127) / 128, (cudaStream_t)stream);
+    }
     const int deep = few_tiles(m, inter, 64);
     if (deep == 64) return launch<64, 8, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 31) / 32, (cudaStream_t)stream);
     if (deep == 128) return launch<128, 6, EPI_SWIGLU>(a, w, ep, m, 2 * inter, k, (inter + 63) / 64, (cudaStream_t)stream);
