@@ -409,3 +409,108 @@ def test_toy_routed_experts_position_norm_and_arrangement(dtype, tmp_path):
         replay.compare(got, requests, reference, dtype)
         pool = stepper.cache.page_groups[0].pool
         assert pool.n_free == pool.n_pages
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# A toy architecture of the engine's own parts whose second layer attends to a window of keys: its pages have a pool
+# of their own and go back to it as the window passes them, also while decode steps come from captured graphs (the
+# block-table entries of the passed pages are cleared by the update kernel at the head of the captured step).
+W_WINDOW, W_LAYERS = 40, 2
+W_CFG = {"hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 112,
+         "vocab_size": 131, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "num_hidden_layers": W_LAYERS, "tie_word_embeddings": True}
+W_CONFIG = dict(W_CFG, architectures=["ToyWindowedForCausalLM"], window=W_WINDOW, max_len=512)
+
+
+def register_windowed_toy():
+    from cisr_b200.config import ARCHITECTURES, LayerSpec, ModelSpec, PartSpec, RunEntry, register_architecture
+
+    if "ToyWindowedForCausalLM" in ARCHITECTURES:
+        return
+
+    class WindowedConfig:
+        def __init__(self, raw):
+            self.raw = raw
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(dict(raw))
+
+        def to_dict(self):
+            return dict(self.raw)
+
+        def to_spec(self):
+            r = self.raw
+            norm = PartSpec("rms_norm", {"size": r["hidden_size"], "eps": r["rms_norm_eps"]})
+            def attention(window):
+                return PartSpec("gqa_attention", {"hidden_size": r["hidden_size"], "num_heads": r["num_attention_heads"],
+                                                  "num_kv_heads": r["num_key_value_heads"], "head_dim": r["head_dim"], "window": window,
+                                                  "scale": r["head_dim"] ** -0.5,
+                                                  "position": PartSpec("rotary_half", {"theta": r["rope_theta"], "dim": r["head_dim"]})})
+            ffn = PartSpec("swiglu", {"hidden_size": r["hidden_size"], "intermediate_size": r["intermediate_size"]})
+            names = {"mixer": "self_attn.", "mixer_norm": "input_layernorm.", "feed_forward": "mlp.", "feed_forward_norm": "post_attention_layernorm."}
+            layers = tuple(LayerSpec(prefix=f"model.layers.{i}.", mixer=attention(None if i == 0 else r["window"]), mixer_norm=norm,
+                                     feed_forward=ffn, feed_forward_norm=norm, names=names) for i in range(r["num_hidden_layers"]))
+            return ModelSpec(hidden_size=r["hidden_size"], vocab_size=r["vocab_size"], max_positions=r["max_len"],
+                             embedding=PartSpec("token_embedding", {"vocab_size": r["vocab_size"], "hidden_size": r["hidden_size"]}),
+                             embedding_prefix="model.embed_tokens.", layers=layers, run=tuple(RunEntry(layer=i) for i in range(len(layers))),
+                             final_norm=norm, final_norm_prefix="model.norm.",
+                             head=PartSpec("linear_head", {"vocab_size": r["vocab_size"], "hidden_size": r["hidden_size"],
+                                                           "tied_to": "model.embed_tokens.weight"}), head_prefix="lm_head.")
+
+    register_architecture("ToyWindowedForCausalLM", WindowedConfig)
+
+
+def windowed_plain_forward(weights, tokens):
+    """plain_llama's layer with the window handed to the second layer's attention."""
+    w = {k: v.double() for k, v in weights.items()}
+    positions = torch.arange(len(tokens))
+    x = pl.embed(w["model.embed_tokens.weight"], tokens)
+    for layer in range(W_LAYERS):
+        p = f"model.layers.{layer}."
+        h = pl.rms_norm(x, w[p + "input_layernorm.weight"], W_CFG["rms_norm_eps"])
+        x = x + pl.attention_block(h, w, p, positions, W_CFG, window=None if layer == 0 else W_WINDOW)
+        h = pl.rms_norm(x, w[p + "post_attention_layernorm.weight"], W_CFG["rms_norm_eps"])
+        x = x + pl.swiglu_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return pl.rms_norm(x, w["model.norm.weight"], W_CFG["rms_norm_eps"]) @ w["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_window_group_inside_captured_decode_steps(dtype, tmp_path):
+    import tiny_models as tm
+    from cisr_b200 import Model, StepEntry, Stepper
+
+    register_windowed_toy()
+    weights = {k: torch.from_numpy(v) if isinstance(v, np.ndarray) else v for k, v in tm.make_weights(W_CFG, 77, scale=0.08, bf16_exact=True).items()}
+    (tmp_path / "config.json").write_text(json.dumps(W_CONFIG))
+    save_file({k: v.contiguous() for k, v in weights.items()}, str(tmp_path / "model.safetensors"))
+    model = Model.from_pretrained(tmp_path, dtype=dtype)
+    rng = np.random.default_rng(5)
+    requests = {rid: [int(t) for t in rng.integers(0, W_CFG["vocab_size"], n)] for rid, n in (("a", 150), ("b", 97), ("c", 61))}
+    reference = {rid: windowed_plain_forward(weights, tokens).numpy() for rid, tokens in requests.items()}
+    page = 8
+    stepper = Stepper(model, n_pages=64, page_size=page, max_slots=4, graph=True)
+    groups = stepper.cache.page_groups
+    assert len(groups) == 2 and sorted(g.use.window or 0 for g in groups) == [0, W_WINDOW]
+    windowed = next(g for g in groups if g.use.window)
+    got = {}
+    prompt = {"a": 30, "b": 20, "c": 9}                       # the rest of each request is decoded, one token per step, from graphs
+    for rid, tokens in requests.items():
+        stepper.create(rid)
+        logits = stepper.step([StepEntry(rid, tokens[:prompt[rid]], list(range(prompt[rid])))]).cpu().numpy()
+        for i in range(prompt[rid]):
+            got[(rid, i)] = logits[i]
+    longest = max(len(t) for t in requests.values())
+    for at in range(longest):
+        entries = [StepEntry(rid, [tokens[prompt[rid] + at]], [0]) for rid, tokens in requests.items() if prompt[rid] + at < len(tokens)]
+        if not entries:
+            break
+        logits = stepper.step(entries).cpu().numpy()
+        for row, e in enumerate(entries):
+            got[(e.key, prompt[e.key] + at)] = logits[row]
+        # the windowed layer never holds more pages per request than its window spans
+        assert windowed.pool.n_used <= len(entries) * (-(-W_WINDOW // page) + 1) + (len(requests) - len(entries)) * (-(-W_WINDOW // page) + 1)
+    assert stepper.graphs.report()["hits"] > 50
+    replay.compare(got, requests, reference, dtype)
+    for rid in requests:
+        stepper.release(rid)
+    assert all(g.pool.n_free == g.pool.n_pages for g in groups)
