@@ -776,8 +776,8 @@ def test_decode_attention_of_a_request_does_not_depend_on_its_neighbours(dtype, 
 
 
 @pytest.mark.parametrize("d,hq,hkv,n_out", [(64, 9, 3, 576), (64, 32, 8, 200), (48, 5, 1, 240), (16, 2, 2, 64), (128, 4, 2, 96), (32, 16, 16, 130)])
-@pytest.mark.parametrize("n_dec", [1, 8, 11, 16])
-def test_merge_and_output_projection_in_one_launch(d, hq, hkv, n_out, n_dec):
+@pytest.mark.parametrize("n_dec,longest", [(1, 1400), (8, 1400), (11, 1400), (16, 1400), (3, 5000), (8, 9000), (2, 20000)])
+def test_merge_and_output_projection_in_one_launch(d, hq, hkv, n_out, n_dec, longest):
     """The cluster kernel that merges the key ranges and projects (merge_proj.cu) against the merge kernel followed by
     a float64 product: the merged rows must be the merge kernel's bfloat16 values exactly (a single differing bit in one
     of them would be a hundred times the bound), and the K-slices must add up to the whole product."""
@@ -786,8 +786,9 @@ def test_merge_and_output_projection_in_one_launch(d, hq, hkv, n_out, n_dec):
     page = 16
     i32 = lambda a: torch.as_tensor(np.asarray(list(a), dtype=np.int32), device=dev())
     g = torch.Generator().manual_seed(d * hq + n_dec)
-    lens = [int(x) for x in torch.randint(1, 1500, (n_dec,), generator=g)]
-    lens[0] = 1400
+    # up to 16 key ranges: one batch of loads per element; up to 32: a second batch; beyond: the path through shared memory
+    lens = [int(x) for x in torch.randint(1, longest + 100, (n_dec,), generator=g)]
+    lens[0] = longest
     n_pages = sum(-(-n // page) for n in lens)
     kc = torch.randn(n_pages, hkv, page, d, generator=g).to(torch.bfloat16).to(dev())
     vc = torch.randn(n_pages, hkv, page, d, generator=g).to(torch.bfloat16).to(dev())
