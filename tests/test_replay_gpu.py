@@ -158,3 +158,41 @@ def test_fork_shares_a_prefix_and_copies_on_write(tmp_path_factory):
     for i, rid in enumerate(("x", "y")):
         ref = replay.plain_logits(cfg, weights, prefix + tails[rid])[21:]
         replay.compare({(rid, 21 + j): logits[9 * i + j] for j in range(9)}, None, {rid: np.concatenate([np.zeros((21, ref.shape[1])), ref])}, "float32")
+
+
+_long = {}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_context_beyond_sixteen_key_ranges(dtype, tmp_path_factory):
+    """One request of 4,400 tokens at the head geometry of the fast kernels: its prompt in portions of 2,048 (prompt
+    attention over up to thirty-two earlier key tiles), then forty tokens decoded from graphs beside a short request
+    (eighteen key ranges of 256: the merge takes a second batch of partial sums; the context bucket changes on the way)."""
+    from cisr_b200 import Model, StepEntry, Stepper
+
+    cfg = dict(tm.TINY_D, max_position_embeddings=4608)
+    if "weights" not in _long:
+        _long["weights"] = tm.make_weights(cfg, 41, scale=0.05, bf16_exact=True)
+        _long["tokens"] = tm.random_tokens(cfg, 4400, 9)
+        _long["short"] = tm.random_tokens(cfg, 70, 10)
+        _long["reference"] = {"long": replay.plain_logits(cfg, _long["weights"], _long["tokens"]),
+                              "short": replay.plain_logits(cfg, _long["weights"], _long["short"])}
+    weights, tokens, short = _long["weights"], _long["tokens"], _long["short"]
+    model = Model.from_pretrained(tm.write_model_dir(tmp_path_factory.mktemp(f"long_{dtype}"), cfg, weights), dtype=dtype)
+    stepper = Stepper(model, n_pages=4608 // 16 + 8, page_size=16, max_slots=2, graph=True)
+    got = {}
+    stepper.create("long"); stepper.create("short")
+    prompt = 4360
+    for at in range(0, prompt, 2048):
+        portion = tokens[at:min(at + 2048, prompt)]
+        want = sorted({0, len(portion) // 2, len(portion) - 1})
+        logits = stepper.step([StepEntry("long", portion, want)]).cpu().numpy()
+        for row, i in enumerate(want):
+            got[("long", at + i)] = logits[row]
+    logits = stepper.step([StepEntry("short", short[:30], [29])]).cpu().numpy()
+    got[("short", 29)] = logits[0]
+    for i in range(40):
+        logits = stepper.step([StepEntry("long", [tokens[prompt + i]], [0]), StepEntry("short", [short[30 + i]], [0])]).cpu().numpy()
+        got[("long", prompt + i)], got[("short", 30 + i)] = logits[0], logits[1]
+    assert stepper.graphs.report()["hits"] >= 30
+    replay.compare(got, {"long": tokens, "short": short}, _long["reference"], dtype)
