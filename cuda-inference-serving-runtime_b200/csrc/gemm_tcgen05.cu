@@ -69,7 +69,9 @@ struct Smem {
 // The epilogue of one output tile for one thread: `row` is the thread's output row, `lane_base` the tensor-memory
 // address of its lane in the tile's accumulator, n0 the tile's first column (feature).
 template <int BN, int EPI>
-__device__ __forceinline__ void epilogue_tile(const Epilogue& ep, uint32_t lane_base, int row, int m, int n, int n0) {
+// `pos`, `page` (ROPE): the row's position and the cache page it is written to, looked up by the caller while the tile
+// was still being accumulated (-1: a padding row, or a row beyond the step).
+__device__ __forceinline__ void epilogue_tile(const Epilogue& ep, uint32_t lane_base, int row, int m, int n, int n0, int pos, int page) {
     if (EPI == EPI_PLAIN) {
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
@@ -117,11 +119,6 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, uint32_t lane_
     } else {
         // whole heads of the stacked q, k, v projection: BN / dim heads per tile, rotation pairs (i, i + dim / 2)
         const int dim = ep.dim, half = dim / 2;
-        int pos = 0, page = -1;
-        if (row < m) {
-            pos = ep.positions[row];
-            page = ep.block_table[(size_t)ep.req_slot[ep.token_req[row]] * ep.table_width + pos / ep.page_size];
-        }
 #pragma unroll 1
         for (int h0 = 0; h0 < BN; h0 += dim) {
             const int hh = (n0 + h0) / dim;                        // head index in the stacked projection
@@ -278,11 +275,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
             const int acc = it & 1;
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
+            const int row = m0 + quarter * 32 + lane;
+            // ROPE: where the row's key and value go hangs on four dependent loads of step metadata; they run while
+            // the tile is still being accumulated instead of after it
+            int pos = 0, page = -1;
+            if (EPI == EPI_ROPE && row < m) {
+                pos = ep.positions[row];
+                page = ep.block_table[(size_t)ep.req_slot[ep.token_req[row]] * ep.table_width + pos / ep.page_size];
+            }
             ok = mbar_wait(acc_full + acc, (it >> 1) & 1);
             if (!ok) break;
             tcgen05_fence_after();
             const uint32_t lane_base = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-            epilogue_tile<BN, EPI>(ep, lane_base, m0 + quarter * 32 + lane, m, n, n0);
+            epilogue_tile<BN, EPI>(ep, lane_base, row, m, n, n0, pos, page);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(acc_empty + acc)) : "memory");
